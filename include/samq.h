@@ -1,0 +1,183 @@
+/*
+ * samq.h — C ABI of the B200 (sm_100a) W8A8 quantized-linear engine.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream handle
+ * (passed as void*, i.e. a cudaStream_t / CUstream), allocates nothing, never
+ * synchronises, never throws and returns an int status: 0 on success, a
+ * negative SAMQ_ERR_* value otherwise.  samq_last_error_string() returns a
+ * thread-local description of the last failure on the calling thread.
+ *
+ * The reference project exposes its native path as a pybind11 torch extension
+ * named `qgemm` (quant/qgemm/kernels/bindings.cpp:98-134) with three calls:
+ * `sym_quant`, `matmul` and `sym_dequant`.  The functions below replace those
+ * three calls (and the PyTorch fake-quant functions of
+ * RTN_quantization/per_tensor_channel_group.py that the model path really
+ * runs) with real int8 arithmetic.  Each declaration cites what it replaces.
+ *
+ * Conventions (same as the reference's native code, quant/qgemm/include/gemm_int8.h:5-9):
+ *   A / X  : [M, K] row-major, K contiguous ("K-major")
+ *   W      : [N, K] row-major, K contiguous (i.e. the nn.Linear weight as stored)
+ *   C / Y  : [M, N] row-major
+ */
+#ifndef SAMQ_H_
+#define SAMQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define SAMQ_OK                 0
+#define SAMQ_ERR_BAD_ARG       -1   /* null pointer, negative size, unknown enum      */
+#define SAMQ_ERR_UNSUPPORTED   -2   /* shape / dtype / granularity not implemented    */
+#define SAMQ_ERR_ALIGNMENT     -3   /* pointer or leading dimension not aligned       */
+#define SAMQ_ERR_CUDA          -4   /* a CUDA runtime / driver call failed            */
+#define SAMQ_ERR_WORKSPACE     -5   /* workspace missing or too small                 */
+#define SAMQ_ERR_TOO_LARGE     -6   /* size beyond a fixed built-in limit             */
+
+/* ---- enums -------------------------------------------------------------- */
+/* element type of a floating tensor */
+#define SAMQ_F16   0
+#define SAMQ_BF16  1
+#define SAMQ_F32   2
+/* GEMM output type additionally allows the raw accumulators */
+#define SAMQ_I32   3
+
+/* quantization granularity.  For activations these are the reference strings
+ * "per_token" | "per_tensor" | "per_group_token"
+ * (RTN_quantization/per_tensor_channel_group.py:130-140); for weights
+ * "per_channel" | "per_tensor" | "per_group" (:178-192).  A weight row is a
+ * "token" of the same arithmetic, so one enum serves both. */
+#define SAMQ_GRAN_ROW     0   /* per_token   / per_channel : scale[M]        */
+#define SAMQ_GRAN_TENSOR  1   /* per_tensor                : scale[1]        */
+#define SAMQ_GRAN_GROUP   2   /* per_group_token/per_group : scale[M, K/g]   */
+
+/* epilogue activation */
+#define SAMQ_ACT_NONE  0
+#define SAMQ_ACT_GELU  1      /* exact erf GELU (torch.nn.GELU default)       */
+
+/* online Hadamard modes of quarot/utils.py:253-289 */
+#define SAMQ_HAD_NONE     0
+#define SAMQ_HAD_FULL     1   /* online_full_had : transform over the whole last dim        */
+#define SAMQ_HAD_PARTIAL  2   /* online_partial_had : transform across the head axis,
+                                 last dim viewed as [K/had_dim, had_dim]                     */
+
+/* Description of the transform applied before quantization.
+ *
+ * mode FULL over n = K columns follows quarot/hadamard_utils.py:59-80
+ * (`matmul_hadU`): n = had_k * 2^p; an in-place Walsh–Hadamard butterfly with
+ * strides 1,2,4,... over each contiguous chunk of 2^p columns, then the
+ * explicit had_k x had_k (+-1) matrix `hadk` mixes the had_k chunks, then a
+ * division by sqrtf(n).  had_k == 1 means n is a power of two and `hadk` is
+ * ignored.  All arithmetic is fp32 on the up-cast input, rounded once to the
+ * tensor dtype (the `fp32_had` branch of quarot/utils.py:258-259).
+ *
+ * mode PARTIAL follows quarot/utils.py:263-289: the last dim is viewed as
+ * [heads = K / had_dim, had_dim] and the transform (size `heads`) runs over
+ * the head axis for every position inside a head, scaled by 1/sqrt(heads).
+ *
+ * `signs` (optional, [K] int8 of +-1) multiplies column j by signs[j] before
+ * the transform: x @ random_hadamard_matrix(n) == hadU(x * signs)
+ * (quarot/hadamard_utils.py:86-94; quarot/model_utils.py:146-152,235-240). */
+typedef struct samq_hadamard_spec {
+    int32_t       mode;      /* SAMQ_HAD_*                                         */
+    int32_t       had_k;     /* 1, 12, 20, 28, 36, 40, ... (size of `hadk`)        */
+    const float*  hadk;      /* device, [had_k, had_k] row-major, or NULL          */
+    int32_t       had_dim;   /* PARTIAL only: width of one head                    */
+    const int8_t* signs;     /* device, [K] of +-1, or NULL                        */
+} samq_hadamard_spec;
+
+/* ---- library ------------------------------------------------------------ */
+
+/* Library version, major*10000 + minor*100 + patch.  No reference counterpart
+ * (the pybind module has no version attribute). */
+int samq_version(void);
+
+/* Thread-local message for the last non-zero status returned on this thread. */
+const char* samq_last_error_string(void);
+
+/* Number of bytes of zero-initialised-by-the-call workspace the given
+ * quantization call needs (0 for ROW and GROUP; 256 for TENSOR, which holds
+ * the running absolute maximum).  The caller allocates it. */
+size_t samq_quant_workspace_bytes(int granularity);
+
+/* ---- K1: activation / weight quantization -------------------------------
+ *
+ * Replaces `qgemm.sym_quant` (quant/qgemm/kernels/bindings.cpp:29-48,
+ * quant.cu:11-61) plus the torch absmax that feeds it, and restates on the GPU
+ *   quantize_activation_per_token_absmax            per_tensor_channel_group.py:53-61
+ *   quantize_activation_per_tensor_absmax           :64-72
+ *   quantize_activation_per_group_absmax_token_dim  :74-93
+ *   quantize_weight_per_channel_absmax              :5-12
+ *   quantize_weight_per_tensor_absmax               :14-21
+ *   quantize_weight_per_group_absmax_input_features :23-50
+ * stopping before the final `mul_(scales)`:
+ *     s = max(absmax, 1e-5) / 127          (in the tensor dtype)
+ *     q = round_half_even(x / s)           (quotient rounded to the tensor dtype first)
+ * Optional steps before the absmax, in this order:
+ *     x <- x / divisor[col]   (SmoothQuant divisor, RTN_quantization/Smooth.py:39-40),
+ *     x <- hadamard(x * signs) (see samq_hadamard_spec), each rounded once to the dtype.
+ *
+ * x        : [M, K] of `dtype`, row stride `ldx` elements
+ * q_out    : [M, K] int8 codes, saturated to [-127, 127], or NULL
+ * scale_out: fp32 copy of the dtype-rounded scale: [M] | [1] | [M, K/group], or NULL
+ * fq_out   : [M, K] of `dtype`, the fake-quantized value q*s exactly as the
+ *            reference function returns it (no saturation), or NULL
+ * tx_out   : [M, K] of `dtype`, the transformed but unquantized input, or NULL
+ * workspace: see samq_quant_workspace_bytes(); may be NULL when that is 0.
+ * Hadamard is only combined with SAMQ_GRAN_ROW. */
+int samq_act_quant_i8(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                      const void* divisor, const samq_hadamard_spec* had,
+                      int granularity, int group_size,
+                      int8_t* q_out, float* scale_out, void* fq_out, void* tx_out,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same arithmetic applied to a weight [N, K] (rows = output channels).  Kept as
+ * its own symbol because the reference names the weight quantizers separately
+ * (per_tensor_channel_group.py:5-50). scale_out: [N] | [1] | [N, K/group]. */
+int samq_weight_quant_i8(const void* w, int dtype, int64_t N, int64_t K, int64_t ldw,
+                         int granularity, int group_size,
+                         int8_t* q_out, float* scale_out, void* fq_out,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- K2: int8 GEMM with fused dequant epilogue ---------------------------
+ *
+ * Replaces `qgemm.matmul` + `qgemm.sym_dequant`
+ * (quant/qgemm/kernels/bindings.cpp:7-26,51-91; gemm.cu:6-45; quant.cu:64-97),
+ * the orphan `matmul_i8_host` (quant/qgemm/kernels/gemm_int8.cu:4-39) and the
+ * float `F.linear` of W8A8Linear.forward (per_tensor_channel_group.py:157-162):
+ *
+ *   acc[m,n] = sum_k A[m,k] * W[n,k]                      (int32, exact)
+ *   y[m,n]   = act( float(acc) * a_scale[m] * w_scale[n] + bias[n] ) + residual[m,n]
+ *
+ * computed with tcgen05.mma kind::i8 into tensor memory.  With grouped scales
+ * (either operand) the int32 partial sum of each group of `group_size`
+ * columns of K is scaled on its own and the products are summed in fp32.
+ *
+ * A        : [M, K] int8, row stride lda bytes (lda % 16 == 0, base 16-byte aligned)
+ * W        : [N, K] int8, row stride ldw bytes (same alignment rule)
+ * a_scale  : fp32 [M] (ROW) | [1] (TENSOR) | [M, K/group] (GROUP); NULL = 1.0
+ * w_scale  : fp32 [N] (ROW) | [1] (TENSOR) | [N, K/group] (GROUP); NULL = 1.0
+ * bias     : [N] of `out_dtype` (fp32 when out_dtype is I32/F32), or NULL
+ * residual : [M, N] of `out_dtype`, row stride ldr elements, or NULL
+ * out      : [M, N] of out_dtype (F16 | BF16 | F32 | I32), row stride ldo elements.
+ *            With SAMQ_I32 the raw accumulators are stored and scales, bias,
+ *            activation and residual must all be absent.
+ * status   : optional device int32; the kernel writes a non-zero code there if
+ *            one of its bounded waits ran out (it then returns early instead
+ *            of hanging). The caller reads it after synchronising. */
+int samq_gemm_i8(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
+                 int64_t M, int64_t N, int64_t K,
+                 const float* a_scale, int a_gran,
+                 const float* w_scale, int w_gran, int group_size,
+                 const void* bias, const void* residual, int64_t ldr,
+                 int activation, void* out, int out_dtype, int64_t ldo,
+                 int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAMQ_H_ */

@@ -1,0 +1,102 @@
+"""ctypes binding of libsamq.so (declarations: include/samq.h).
+
+The library is the only compute path of this package: if it is missing or does not load,
+importing a compute function raises — there is no PyTorch or CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int8, c_int32, c_int64, c_size_t, c_void_p
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "libsamq.so")
+
+# enums of include/samq.h
+F16, BF16, F32, I32 = 0, 1, 2, 3
+GRAN_ROW, GRAN_TENSOR, GRAN_GROUP = 0, 1, 2
+ACT_NONE, ACT_GELU = 0, 1
+HAD_NONE, HAD_FULL, HAD_PARTIAL = 0, 1, 2
+
+EXPORTED_SYMBOLS = (
+    "samq_version",
+    "samq_last_error_string",
+    "samq_quant_workspace_bytes",
+    "samq_act_quant_i8",
+    "samq_weight_quant_i8",
+    "samq_gemm_i8",
+)
+
+
+class HadamardSpec(Structure):
+    """Mirror of ``samq_hadamard_spec``."""
+
+    _fields_ = [
+        ("mode", c_int32),
+        ("had_k", c_int32),
+        ("hadk", c_void_p),
+        ("had_dim", c_int32),
+        ("signs", c_void_p),
+    ]
+
+
+class SamqError(RuntimeError):
+    """A C-ABI call returned a non-zero status (the reference's bindings raise RuntimeError
+    from torch::check*/TORCH_CHECK, quant/qgemm/kernels/bindings.cpp:9-17,87)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"samq error {code}: {message}")
+        self.code = code
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load libsamq.so once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m sam_quantization_b200.build` "
+            "(there is no fallback path)")
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.samq_version.restype = c_int
+    lib.samq_version.argtypes = []
+    lib.samq_last_error_string.restype = c_char_p
+    lib.samq_last_error_string.argtypes = []
+    lib.samq_quant_workspace_bytes.restype = c_size_t
+    lib.samq_quant_workspace_bytes.argtypes = [c_int]
+    lib.samq_act_quant_i8.restype = c_int
+    lib.samq_act_quant_i8.argtypes = [
+        c_void_p, c_int, c_int64, c_int64, c_int64,      # x, dtype, M, K, ldx
+        c_void_p, POINTER(HadamardSpec),                 # divisor, had
+        c_int, c_int,                                    # granularity, group_size
+        c_void_p, c_void_p, c_void_p, c_void_p,          # q, scale, fq, tx
+        c_void_p, c_size_t, c_void_p,                    # workspace, bytes, stream
+    ]
+    lib.samq_weight_quant_i8.restype = c_int
+    lib.samq_weight_quant_i8.argtypes = [
+        c_void_p, c_int, c_int64, c_int64, c_int64,
+        c_int, c_int,
+        c_void_p, c_void_p, c_void_p,
+        c_void_p, c_size_t, c_void_p,
+    ]
+    lib.samq_gemm_i8.restype = c_int
+    lib.samq_gemm_i8.argtypes = [
+        c_void_p, c_int64, c_void_p, c_int64,            # A, lda, W, ldw
+        c_int64, c_int64, c_int64,                       # M, N, K
+        c_void_p, c_int, c_void_p, c_int, c_int,         # a_scale, a_gran, w_scale, w_gran, group
+        c_void_p, c_void_p, c_int64,                     # bias, residual, ldr
+        c_int, c_void_p, c_int, c_int64,                 # activation, out, out_dtype, ldo
+        c_void_p, c_void_p,                              # status, stream
+    ]
+    _lib = lib
+    return lib
+
+
+def check(code: int) -> None:
+    if code != 0:
+        msg = load().samq_last_error_string()
+        raise SamqError(code, msg.decode("utf-8", "replace") if msg else "")

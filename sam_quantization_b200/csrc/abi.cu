@@ -1,0 +1,84 @@
+// extern "C" surface of libsamq: argument checks, thread-local error text and dispatch
+// into the kernels.  Declarations and the reference interfaces they replace: include/samq.h.
+#include "common.cuh"
+#include <string.h>
+
+namespace samq {
+
+char* error_buffer() {
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(error_buffer(), 512, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int act_quant_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                       const void* divisor, const samq_hadamard_spec* had,
+                       int gran, int group_size, int8_t* q, float* scale, void* fq, void* tx,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+int gemm_i8_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
+                     int64_t M, int64_t N, int64_t K,
+                     const float* a_scale, int a_gran, const float* w_scale, int w_gran, int group_size,
+                     const void* bias, const void* residual, int64_t ldr, int activation,
+                     void* out, int out_dtype, int64_t ldo, int32_t* status, void* stream);
+
+int gemm_i8_grouped_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
+                             int64_t M, int64_t N, int64_t K,
+                             const float* a_scale, int a_gran, const float* w_scale, int w_gran, int group_size,
+                             const void* bias, const void* residual, int64_t ldr, int activation,
+                             void* out, int out_dtype, int64_t ldo, int32_t* status, void* stream);
+
+}  // namespace samq
+
+extern "C" {
+
+int samq_version(void) { return 100; }   // 0.1.0
+
+const char* samq_last_error_string(void) { return samq::error_buffer(); }
+
+size_t samq_quant_workspace_bytes(int granularity) {
+    return granularity == SAMQ_GRAN_TENSOR ? 256 : 0;
+}
+
+int samq_act_quant_i8(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                      const void* divisor, const samq_hadamard_spec* had,
+                      int granularity, int group_size,
+                      int8_t* q_out, float* scale_out, void* fq_out, void* tx_out,
+                      void* workspace, size_t workspace_bytes, void* stream)
+{
+    return samq::act_quant_dispatch(x, dtype, M, K, ldx, divisor, had, granularity, group_size,
+                                    q_out, scale_out, fq_out, tx_out, workspace, workspace_bytes, stream);
+}
+
+int samq_weight_quant_i8(const void* w, int dtype, int64_t N, int64_t K, int64_t ldw,
+                         int granularity, int group_size,
+                         int8_t* q_out, float* scale_out, void* fq_out,
+                         void* workspace, size_t workspace_bytes, void* stream)
+{
+    return samq::act_quant_dispatch(w, dtype, N, K, ldw, nullptr, nullptr, granularity, group_size,
+                                    q_out, scale_out, fq_out, nullptr, workspace, workspace_bytes, stream);
+}
+
+int samq_gemm_i8(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
+                 int64_t M, int64_t N, int64_t K,
+                 const float* a_scale, int a_gran,
+                 const float* w_scale, int w_gran, int group_size,
+                 const void* bias, const void* residual, int64_t ldr,
+                 int activation, void* out, int out_dtype, int64_t ldo,
+                 int32_t* status, void* stream)
+{
+    if (a_gran == SAMQ_GRAN_GROUP || w_gran == SAMQ_GRAN_GROUP)
+        return samq::gemm_i8_grouped_dispatch(A, lda, W, ldw, M, N, K, a_scale, a_gran, w_scale, w_gran, group_size,
+                                              bias, residual, ldr, activation, out, out_dtype, ldo, status, stream);
+    return samq::gemm_i8_dispatch(A, lda, W, ldw, M, N, K, a_scale, a_gran, w_scale, w_gran, group_size,
+                                  bias, residual, ldr, activation, out, out_dtype, ldo, status, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,520 @@
+// K1 — dynamic symmetric int8 quantization of activations (and weights) on B200.
+//
+// GPU restatement of the reference's absmax quantizers
+// (RTN_quantization/per_tensor_channel_group.py:5-93) that produces the int8
+// codes and the scale instead of the fake-quantized float tensor, optionally
+// preceded by a SmoothQuant divisor (RTN_quantization/Smooth.py:39-40) and by
+// the online Hadamard transforms of quarot/utils.py:253-289 /
+// quarot/hadamard_utils.py:59-80.
+//
+// All kernels are bound by HBM bandwidth: a row of K fp16 values is read once
+// with 16-byte loads, kept in registers (or, for the Hadamard path, in shared
+// memory), and written once as K int8 codes plus one fp32 scale:
+// 3K + 4 algorithmic bytes per row.
+#include "common.cuh"
+
+namespace samq {
+
+// ---------------------------------------------------------------------------
+// 16-byte vector helpers
+// ---------------------------------------------------------------------------
+template <typename T> struct Vec16 { uint4 raw; };
+
+template <typename T>
+__device__ __forceinline__ void unpack(const uint4& raw, float (&f)[Elem<T>::kPerVec]);
+
+template <> __device__ __forceinline__ void unpack<__half>(const uint4& raw, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+template <> __device__ __forceinline__ void unpack<__nv_bfloat16>(const uint4& raw, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+template <> __device__ __forceinline__ void unpack<float>(const uint4& raw, float (&f)[4]) {
+    f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y);
+    f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 pack(const float (&f)[Elem<T>::kPerVec]);
+
+template <> __device__ __forceinline__ uint4 pack<__half>(const float (&f)[8]) {
+    uint4 r; __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    return r;
+}
+template <> __device__ __forceinline__ uint4 pack<__nv_bfloat16>(const float (&f)[8]) {
+    uint4 r; __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return r;
+}
+template <> __device__ __forceinline__ uint4 pack<float>(const float (&f)[4]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+}
+
+// streaming (evict-first) 16-byte global load: every row is read exactly once
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+
+template <int N> struct PackedCodes;
+template <> struct PackedCodes<8> { typedef uint2 type; };
+template <> struct PackedCodes<4> { typedef uint32_t type; };
+
+template <int N>
+__device__ __forceinline__ typename PackedCodes<N>::type pack_codes(const float (&q)[N]);
+template <> __device__ __forceinline__ uint2 pack_codes<8>(const float (&q)[8]) {
+    uint32_t w[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v |= (uint32_t)(uint8_t)saturate_i8(q[4 * h + i]) << (8 * i);
+        w[h] = v;
+    }
+    return make_uint2(w[0], w[1]);
+}
+template <> __device__ __forceinline__ uint32_t pack_codes<4>(const float (&q)[4]) {
+    uint32_t v = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v |= (uint32_t)(uint8_t)saturate_i8(q[i]) << (8 * i);
+    return v;
+}
+
+// ---------------------------------------------------------------------------
+// Row kernel: one warp owns one row and keeps it in registers.
+//   GRAN ROW    : scale from the row's absolute maximum
+//   GRAN GROUP  : `lanes_per_group` adjacent lanes (a power of two <= 32) share a scale
+//   GRAN TENSOR : the absolute maximum was reduced by absmax_kernel into *tensor_absmax
+// ---------------------------------------------------------------------------
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+quant_rows_vec_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
+                      const T* __restrict__ divisor, int gran, int lanes_per_group,
+                      const float* __restrict__ tensor_absmax,
+                      int8_t* __restrict__ q_out, float* __restrict__ scale_out,
+                      T* __restrict__ fq_out, T* __restrict__ tx_out)
+{
+    constexpr int E = Elem<T>::kPerVec;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= M) return;
+    const int nvec = K / E;
+    const T* xr = x + row * ldx;
+
+    uint4 raw[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int v = i * 32 + lane;
+        raw[i] = (v < nvec) ? ld_stream(xr + (int64_t)v * E) : make_uint4(0, 0, 0, 0);
+    }
+
+    float vmax[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int v = i * 32 + lane;
+        float f[E];
+        unpack<T>(raw[i], f);
+        if (divisor != nullptr && v < nvec) {
+            float d[E];
+            uint4 draw = *reinterpret_cast<const uint4*>(divisor + (int64_t)v * E);
+            unpack<T>(draw, d);
+#pragma unroll
+            for (int e = 0; e < E; ++e) f[e] = round_to<T>(__fdiv_rn(f[e], d[e]));
+            raw[i] = pack<T>(f);
+        }
+        float m = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) m = fmaxf(m, fabsf(f[e]));
+        vmax[i] = m;
+    }
+
+    float row_scale = 0.f;
+    if (gran == SAMQ_GRAN_ROW) {
+        float m = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) m = fmaxf(m, vmax[i]);
+        m = warp_max(m);
+        row_scale = scale_from_absmax<T>(m);
+        if (lane == 0 && scale_out != nullptr) scale_out[row] = row_scale;
+    } else if (gran == SAMQ_GRAN_TENSOR) {
+        row_scale = scale_from_absmax<T>(*tensor_absmax);
+        if (row == 0 && lane == 0 && scale_out != nullptr) scale_out[0] = row_scale;
+    }
+
+    const int groups_per_row = (gran == SAMQ_GRAN_GROUP) ? nvec / lanes_per_group : 0;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int v = i * 32 + lane;
+        float s = row_scale;
+        if (gran == SAMQ_GRAN_GROUP) {
+            float m = vmax[i];
+            for (int o = lanes_per_group >> 1; o > 0; o >>= 1)
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            s = scale_from_absmax<T>(m);
+            if (v < nvec && (lane & (lanes_per_group - 1)) == 0 && scale_out != nullptr)
+                scale_out[row * groups_per_row + v / lanes_per_group] = s;
+        }
+        if (v >= nvec) continue;
+        float f[E], q[E];
+        unpack<T>(raw[i], f);
+#pragma unroll
+        for (int e = 0; e < E; ++e) q[e] = quant_value<T>(f[e], s);
+        if (q_out != nullptr)
+            *reinterpret_cast<typename PackedCodes<E>::type*>(q_out + row * K + (int64_t)v * E) = pack_codes<E>(q);
+        if (tx_out != nullptr)
+            *reinterpret_cast<uint4*>(tx_out + row * K + (int64_t)v * E) = raw[i];
+        if (fq_out != nullptr) {
+#pragma unroll
+            for (int e = 0; e < E; ++e) q[e] = q[e] * s;   // rounded to T by pack()
+            *reinterpret_cast<uint4*>(fq_out + row * K + (int64_t)v * E) = pack<T>(q);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Generic kernel: one warp per (row, group) unit, scalar accesses, two passes.
+// Covers every shape the vector kernel does not (odd K, unaligned rows,
+// very long rows, group sizes that are not 8 * 2^j).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_rows_generic_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
+                          const T* __restrict__ divisor, int gran, int group_size,
+                          const float* __restrict__ tensor_absmax,
+                          int8_t* __restrict__ q_out, float* __restrict__ scale_out,
+                          T* __restrict__ fq_out, T* __restrict__ tx_out)
+{
+    const int lane = threadIdx.x & 31;
+    const int span = (gran == SAMQ_GRAN_GROUP) ? group_size : K;
+    const int units_per_row = K / span;
+    const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= M * units_per_row) return;
+    const int64_t row = unit / units_per_row;
+    const int c0 = (int)(unit % units_per_row) * span;
+    const T* xr = x + row * ldx;
+
+    float s;
+    if (gran == SAMQ_GRAN_TENSOR) {
+        s = scale_from_absmax<T>(*tensor_absmax);
+        if (unit == 0 && lane == 0 && scale_out != nullptr) scale_out[0] = s;
+    } else {
+        float m = 0.f;
+        for (int c = c0 + lane; c < c0 + span; c += 32) {
+            float v = Elem<T>::up(xr[c]);
+            if (divisor != nullptr) v = round_to<T>(__fdiv_rn(v, Elem<T>::up(divisor[c])));
+            m = fmaxf(m, fabsf(v));
+        }
+        m = warp_max(m);
+        s = scale_from_absmax<T>(m);
+        if (lane == 0 && scale_out != nullptr) scale_out[unit] = s;
+    }
+    for (int c = c0 + lane; c < c0 + span; c += 32) {
+        float v = Elem<T>::up(xr[c]);
+        if (divisor != nullptr) v = round_to<T>(__fdiv_rn(v, Elem<T>::up(divisor[c])));
+        const float q = quant_value<T>(v, s);
+        if (q_out != nullptr) q_out[row * K + c] = saturate_i8(q);
+        if (tx_out != nullptr) tx_out[row * K + c] = Elem<T>::down(v);
+        if (fq_out != nullptr) fq_out[row * K + c] = Elem<T>::down(q * s);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Per-tensor absolute maximum (first pass of per_tensor quantization).  The
+// result lives in caller-provided scratch memory that the launcher zeroes.
+// Non-negative floats order like their bit patterns, so atomicMax on the
+// integer view is exact.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+absmax_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
+              const T* __restrict__ divisor, float* __restrict__ result)
+{
+    float m = 0.f;
+    const int64_t total = M * (int64_t)K;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / K;
+        const int c = (int)(i - r * K);
+        float v = Elem<T>::up(x[r * ldx + c]);
+        if (divisor != nullptr) v = round_to<T>(__fdiv_rn(v, Elem<T>::up(divisor[c])));
+        m = fmaxf(m, fabsf(v));
+    }
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(result), __float_as_int(m));
+}
+
+// ---------------------------------------------------------------------------
+// Hadamard + quantization kernel: one CTA owns one row held in shared memory
+// as fp32.  Butterflies run in registers, 4 index bits (16 values) per round,
+// so a 4096-wide transform needs three passes over shared memory.
+//
+// The transform axis has length `axis` = had_k * 2^log2_pow and is embedded in
+// the row as   index = (outer * axis + a) * inner + in,
+//   FULL    : inner = 1,       outer = 1, axis = K
+//   PARTIAL : inner = had_dim, outer = 1, axis = K / had_dim  (the head axis)
+// Within the axis, a = k * 2^log2_pow + b: the 2^log2_pow part gets the
+// butterflies (strides 1,2,4,... as matmul_hadU does), the had_k part is mixed
+// by the explicit +-1 matrix.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ int padded(int i) { return i + (i >> 4); }
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+hadamard_quant_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
+                      const T* __restrict__ divisor, const int8_t* __restrict__ signs,
+                      int inner, int axis, int had_k, int log2_pow,
+                      const float* __restrict__ hadk,
+                      int8_t* __restrict__ q_out, float* __restrict__ scale_out,
+                      T* __restrict__ fq_out, T* __restrict__ tx_out)
+{
+    extern __shared__ float sm[];          // padded(K) floats, then had_k*had_k signs, then 32 floats
+    float* hk = sm + padded(K) + 1;
+    float* red = hk + had_k * had_k;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int64_t row = blockIdx.x;
+    const T* xr = x + row * ldx;
+
+    // (a) load, SmoothQuant divisor, sign flip
+    for (int c = tid; c < K; c += nthr) {
+        float v = Elem<T>::up(xr[c]);
+        if (divisor != nullptr) v = round_to<T>(__fdiv_rn(v, Elem<T>::up(divisor[c])));
+        if (signs != nullptr && signs[c] < 0) v = -v;
+        sm[padded(c)] = v;
+    }
+    if (had_k > 1)
+        for (int i = tid; i < had_k * had_k; i += nthr) hk[i] = hadk[i];
+    __syncthreads();
+
+    // (b) butterflies over the power-of-two part of the axis, 4 bits per round
+    const int pow_len = 1 << log2_pow;
+    for (int b = 0; b < log2_pow; b += 4) {
+        const int r = min(4, log2_pow - b);
+        const int R = 1 << r;
+        const int groups = K >> r;
+        const int rest_len = pow_len >> r;               // values of the axis index without the r bits
+        for (int g = tid; g < groups; g += nthr) {
+            // g enumerates (k_chunk, rest, in) with `in` fastest
+            const int in = g % inner;
+            int t = g / inner;
+            const int rest = t % rest_len;
+            const int kc = t / rest_len;                 // chunk of the had_k part (and outer)
+            const int lo = rest & ((1 << b) - 1);
+            const int hi = rest >> b;
+            const int a0 = kc * pow_len + ((hi << (b + r)) | lo);
+            const int base = a0 * inner + in;
+            const int step = inner << b;
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) if (j < R) v[j] = sm[padded(base + j * step)];
+#pragma unroll
+            for (int s = 1; s < 16; s <<= 1) {
+                if (s < R) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if ((j & s) == 0 && j < R) {
+                            const float a = v[j], c = v[j | s];
+                            v[j] = a + c;
+                            v[j | s] = a - c;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) if (j < R) sm[padded(base + j * step)] = v[j];
+        }
+        __syncthreads();
+    }
+
+    // (c) explicit had_k x had_k mix across the chunks
+    if (had_k > 1) {
+        const int cols = pow_len * inner;                // positions inside one chunk
+        // each thread owns whole columns: reads had_k inputs, writes had_k outputs
+        for (int c = tid; c < cols; c += nthr) {
+            float in_v[64];
+            for (int k = 0; k < had_k; ++k) in_v[k] = sm[padded(k * cols + c)];
+            for (int k = 0; k < had_k; ++k) {
+                float acc = 0.f;
+                for (int k2 = 0; k2 < had_k; ++k2) acc += hk[k * had_k + k2] * in_v[k2];
+                sm[padded(k * cols + c)] = acc;
+            }
+        }
+        __syncthreads();
+    }
+
+    // (d) scale by 1/sqrt(axis) with a true division, round once to T, absmax
+    const float root = sqrtf((float)axis);
+    float m = 0.f;
+    for (int c = tid; c < K; c += nthr) {
+        const float v = round_to<T>(__fdiv_rn(sm[padded(c)], root));
+        sm[padded(c)] = v;
+        m = fmaxf(m, fabsf(v));
+    }
+    m = warp_max(m);
+    if ((tid & 31) == 0) red[tid >> 5] = m;
+    __syncthreads();
+    if (tid < 32) {
+        float t = (tid < ((nthr + 31) >> 5)) ? red[tid] : 0.f;
+        t = warp_max(t);
+        if (tid == 0) red[0] = t;
+    }
+    __syncthreads();
+    const float s = scale_from_absmax<T>(red[0]);
+    if (tid == 0 && scale_out != nullptr) scale_out[row] = s;
+
+    // (e) quantize and store
+    for (int c = tid; c < K; c += nthr) {
+        const float v = sm[padded(c)];
+        const float q = quant_value<T>(v, s);
+        if (q_out != nullptr) q_out[row * K + c] = saturate_i8(q);
+        if (tx_out != nullptr) tx_out[row * K + c] = Elem<T>::down(v);
+        if (fq_out != nullptr) fq_out[row * K + c] = Elem<T>::down(q * s);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host launchers
+// ---------------------------------------------------------------------------
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename T>
+static int launch_rows(const T* x, int64_t M, int K, int64_t ldx, const T* divisor,
+                       int gran, int group_size, const float* tensor_absmax,
+                       int8_t* q, float* scale, T* fq, T* tx, cudaStream_t st)
+{
+    constexpr int E = Elem<T>::kPerVec;
+    bool vec_ok = (K % E == 0) && (ldx % E == 0) && aligned16(x) && aligned16(fq) && aligned16(tx) &&
+                  aligned16(divisor) && ((reinterpret_cast<uintptr_t>(q) & 7) == 0) && K <= 40 * 32 * E;
+    int lanes_per_group = 32;
+    if (gran == SAMQ_GRAN_GROUP) {
+        lanes_per_group = group_size / E;
+        const bool pow2 = lanes_per_group > 0 && (lanes_per_group & (lanes_per_group - 1)) == 0;
+        vec_ok = vec_ok && (group_size % E == 0) && pow2 && lanes_per_group <= 32;
+    }
+    if (vec_ok) {
+        const int nv = (K / E + 31) / 32;
+        const int warps = 8;
+        dim3 grid((unsigned)((M + warps - 1) / warps)), block(warps * 32);
+#define SAMQ_LAUNCH_NV(NVAL)                                                               \
+        quant_rows_vec_kernel<T, NVAL><<<grid, block, 0, st>>>(x, M, K, ldx, divisor, gran, \
+            lanes_per_group, tensor_absmax, q, scale, fq, tx)
+        if (nv <= 1) SAMQ_LAUNCH_NV(1);
+        else if (nv <= 2) SAMQ_LAUNCH_NV(2);
+        else if (nv <= 3) SAMQ_LAUNCH_NV(3);
+        else if (nv <= 4) SAMQ_LAUNCH_NV(4);
+        else if (nv <= 5) SAMQ_LAUNCH_NV(5);
+        else if (nv <= 8) SAMQ_LAUNCH_NV(8);
+        else if (nv <= 12) SAMQ_LAUNCH_NV(12);
+        else if (nv <= 16) SAMQ_LAUNCH_NV(16);
+        else if (nv <= 20) SAMQ_LAUNCH_NV(20);
+        else if (nv <= 24) SAMQ_LAUNCH_NV(24);
+        else if (nv <= 32) SAMQ_LAUNCH_NV(32);
+        else SAMQ_LAUNCH_NV(40);
+#undef SAMQ_LAUNCH_NV
+    } else {
+        const int span = (gran == SAMQ_GRAN_GROUP) ? group_size : K;
+        const int64_t units = M * (K / span);
+        const int warps = 8;
+        dim3 grid((unsigned)((units + warps - 1) / warps)), block(warps * 32);
+        quant_rows_generic_kernel<T><<<grid, block, 0, st>>>(x, M, K, ldx, divisor, gran, group_size,
+                                                             tensor_absmax, q, scale, fq, tx);
+    }
+    SAMQ_CUDA_TRY(cudaGetLastError());
+    return SAMQ_OK;
+}
+
+template <typename T>
+static int quant_typed(const T* x, int64_t M, int K, int64_t ldx, const T* divisor,
+                       const samq_hadamard_spec* had, int gran, int group_size,
+                       int8_t* q, float* scale, T* fq, T* tx,
+                       void* workspace, size_t workspace_bytes, cudaStream_t st)
+{
+    if (M == 0) return SAMQ_OK;
+    if (had != nullptr && had->mode != SAMQ_HAD_NONE) {
+        if (gran != SAMQ_GRAN_ROW)
+            return fail(SAMQ_ERR_UNSUPPORTED, "an online Hadamard is only combined with per-token quantization");
+        int inner, axis;
+        if (had->mode == SAMQ_HAD_FULL) { inner = 1; axis = K; }
+        else if (had->mode == SAMQ_HAD_PARTIAL) {
+            if (had->had_dim <= 0 || K % had->had_dim != 0)
+                return fail(SAMQ_ERR_BAD_ARG, "had_dim %d does not divide K=%d", had->had_dim, K);
+            inner = had->had_dim; axis = K / had->had_dim;
+        } else return fail(SAMQ_ERR_BAD_ARG, "unknown hadamard mode %d", had->mode);
+        const int hk = had->had_k;
+        if (hk < 1 || hk > 64 || axis % hk != 0)
+            return fail(SAMQ_ERR_UNSUPPORTED, "had_k=%d must be in [1,64] and divide the transform length %d", hk, axis);
+        const int pw = axis / hk;
+        if ((pw & (pw - 1)) != 0)
+            return fail(SAMQ_ERR_UNSUPPORTED, "transform length %d is not had_k=%d times a power of two", axis, hk);
+        if (hk > 1 && had->hadk == nullptr)
+            return fail(SAMQ_ERR_BAD_ARG, "had_k=%d needs the hadk matrix", hk);
+        int log2_pow = 0; while ((1 << log2_pow) < pw) ++log2_pow;
+        const size_t smem = (size_t)(K + (K >> 4) + 2 + hk * hk + 32) * sizeof(float);
+        if (smem > 200 * 1024) return fail(SAMQ_ERR_TOO_LARGE, "row of K=%d does not fit in shared memory", K);
+        if (smem > 48 * 1024)
+            SAMQ_CUDA_TRY(cudaFuncSetAttribute(hadamard_quant_kernel<T>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        int threads = ((K / 16 + 31) / 32) * 32;
+        threads = threads < 32 ? 32 : (threads > 1024 ? 1024 : threads);
+        hadamard_quant_kernel<T><<<(unsigned)M, threads, smem, st>>>(x, M, K, ldx, divisor, had->signs,
+            inner, axis, hk, log2_pow, had->hadk, q, scale, fq, tx);
+        SAMQ_CUDA_TRY(cudaGetLastError());
+        return SAMQ_OK;
+    }
+    const float* tensor_absmax = nullptr;
+    if (gran == SAMQ_GRAN_TENSOR) {
+        if (workspace == nullptr || workspace_bytes < samq_quant_workspace_bytes(gran))
+            return fail(SAMQ_ERR_WORKSPACE, "per_tensor quantization needs %zu bytes of workspace",
+                        samq_quant_workspace_bytes(gran));
+        SAMQ_CUDA_TRY(cudaMemsetAsync(workspace, 0, sizeof(float), st));
+        const int64_t total = M * (int64_t)K;
+        int blocks = (int)((total + 256 * 8 - 1) / (256 * 8));
+        blocks = blocks < 1 ? 1 : (blocks > 148 * 8 ? 148 * 8 : blocks);
+        absmax_kernel<T><<<blocks, 256, 0, st>>>(x, M, K, ldx, divisor, static_cast<float*>(workspace));
+        SAMQ_CUDA_TRY(cudaGetLastError());
+        tensor_absmax = static_cast<const float*>(workspace);
+    } else if (gran == SAMQ_GRAN_GROUP) {
+        if (group_size <= 0 || K % group_size != 0)
+            return fail(SAMQ_ERR_BAD_ARG, "group_size %d must divide K=%d", group_size, K);
+    } else if (gran != SAMQ_GRAN_ROW) {
+        return fail(SAMQ_ERR_BAD_ARG, "unknown granularity %d", gran);
+    }
+    return launch_rows<T>(x, M, K, ldx, divisor, gran, group_size, tensor_absmax, q, scale, fq, tx, st);
+}
+
+int act_quant_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                       const void* divisor, const samq_hadamard_spec* had,
+                       int gran, int group_size, int8_t* q, float* scale, void* fq, void* tx,
+                       void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (M < 0 || K <= 0 || ldx < K) return fail(SAMQ_ERR_BAD_ARG, "bad shape M=%lld K=%lld ldx=%lld",
+                                                (long long)M, (long long)K, (long long)ldx);
+    if (M > 0 && x == nullptr) return fail(SAMQ_ERR_BAD_ARG, "x is null");
+    if (K > (1 << 20)) return fail(SAMQ_ERR_TOO_LARGE, "K=%lld exceeds 2^20", (long long)K);
+    if (M > 2147483647LL) return fail(SAMQ_ERR_TOO_LARGE, "M=%lld exceeds 2^31-1", (long long)M);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+    case SAMQ_F16:
+        return quant_typed<__half>((const __half*)x, M, (int)K, ldx, (const __half*)divisor, had, gran, group_size,
+                                   q, scale, (__half*)fq, (__half*)tx, workspace, workspace_bytes, st);
+    case SAMQ_BF16:
+        return quant_typed<__nv_bfloat16>((const __nv_bfloat16*)x, M, (int)K, ldx, (const __nv_bfloat16*)divisor, had,
+                                          gran, group_size, q, scale, (__nv_bfloat16*)fq, (__nv_bfloat16*)tx,
+                                          workspace, workspace_bytes, st);
+    case SAMQ_F32:
+        return quant_typed<float>((const float*)x, M, (int)K, ldx, (const float*)divisor, had, gran, group_size,
+                                  q, scale, (float*)fq, (float*)tx, workspace, workspace_bytes, st);
+    default:
+        return fail(SAMQ_ERR_BAD_ARG, "unknown dtype %d", dtype);
+    }
+}
+
+}  // namespace samq

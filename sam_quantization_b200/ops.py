@@ -1,0 +1,253 @@
+"""Tensor-level wrappers over the C ABI (include/samq.h).
+
+Each function takes CUDA tensors, allocates the outputs with torch (the library itself never
+allocates), passes raw pointers plus the current CUDA stream through ctypes and returns the
+outputs.  CPU tensors are rejected: this package has no CPU compute path.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import (ACT_GELU, ACT_NONE, BF16, F16, F32, GRAN_GROUP, GRAN_ROW, GRAN_TENSOR, HAD_FULL,
+                   HAD_NONE, HAD_PARTIAL, I32, HadamardSpec)
+
+_DTYPE_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
+_OUT_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32, torch.int32: I32}
+
+# reference strings (RTN_quantization/per_tensor_channel_group.py:130-140,178-192) -> enum
+ACT_GRANULARITY = {"per_token": GRAN_ROW, "per_tensor": GRAN_TENSOR, "per_group_token": GRAN_GROUP}
+WEIGHT_GRANULARITY = {"per_channel": GRAN_ROW, "per_tensor": GRAN_TENSOR, "per_group": GRAN_GROUP}
+
+
+@dataclass
+class Hadamard:
+    """Online transform applied before quantization (see ``samq_hadamard_spec``).
+
+    mode: "full" (quarot/utils.py:257-261) or "partial" (:263-289)
+    had_k / hadk: the explicit Hadamard factor of ``get_hadK`` (1 / None for powers of two)
+    had_dim: head width for the partial transform
+    signs: optional int8 [K] of +-1 multiplied in before the transform
+    """
+
+    mode: str
+    had_k: int = 1
+    hadk: Optional[torch.Tensor] = None
+    had_dim: int = 0
+    signs: Optional[torch.Tensor] = None
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: sam_quantization_b200 has no CPU compute path")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+_status_words = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 that GEMM kernels raise when one of their bounded waits ran out."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+    return _status_words[key]
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if any GEMM kernel on ``device`` reported a timed-out wait."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = status_word(dev)
+    if int(word.item()) != 0:
+        word.zero_()
+        raise RuntimeError("samq GEMM kernel gave up on a bounded wait (pipeline stalled)")
+
+
+def _as_rows(x: torch.Tensor) -> Tuple[torch.Tensor, int, int, int]:
+    """View x as [M, K] with a row stride; copies only if the last dim is not contiguous."""
+    K = x.shape[-1]
+    if x.dim() == 2 and x.stride(1) == 1 and x.stride(0) >= K:
+        return x, x.shape[0], K, x.stride(0)
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1 or (x2.shape[0] > 1 and x2.stride(0) != K):
+        x2 = x2.contiguous()
+    return x2, x2.shape[0], K, K
+
+
+def _spec(had: Optional[Hadamard], keep: list) -> Optional[HadamardSpec]:
+    if had is None:
+        return None
+    mode = {"full": HAD_FULL, "partial": HAD_PARTIAL, "none": HAD_NONE}[had.mode]
+    hadk = None
+    if had.had_k > 1:
+        if had.hadk is None:
+            raise ValueError("had_k > 1 needs the hadk matrix")
+        hadk = had.hadk.to(dtype=torch.float32).contiguous()
+        _require_cuda(hadk, "hadk")
+        keep.append(hadk)
+    signs = None
+    if had.signs is not None:
+        signs = had.signs.to(dtype=torch.int8).contiguous()
+        _require_cuda(signs, "signs")
+        keep.append(signs)
+    return HadamardSpec(mode, int(had.had_k), 0 if hadk is None else hadk.data_ptr(), int(had.had_dim),
+                        0 if signs is None else signs.data_ptr())
+
+
+def quantize(x: torch.Tensor, granularity: int = GRAN_ROW, group_size: Optional[int] = None,
+             divisor: Optional[torch.Tensor] = None, hadamard: Optional[Hadamard] = None,
+             codes: bool = True, fake_quant: bool = False, transformed: bool = False):
+    """Run K1 on ``x`` ([..., K]; fp16 / bf16 / fp32).
+
+    Returns a dict with the requested outputs: ``q`` int8 [..., K], ``scale`` fp32
+    ([...] | [1] | [..., K/group]), ``fq`` (fake-quantized, x.dtype) and ``tx`` (input after
+    divisor / Hadamard, x.dtype).
+    """
+    _require_cuda(x, "x")
+    if x.dtype not in _DTYPE_CODE:
+        raise TypeError(f"unsupported dtype {x.dtype}")
+    lib = _lib.load()
+    lead = x.shape[:-1]
+    x2, M, K, ldx = _as_rows(x)
+    g = int(group_size) if granularity == GRAN_GROUP else 0
+    if granularity == GRAN_GROUP:
+        if not isinstance(group_size, int):
+            raise AssertionError("group_size must be an integer")
+        if K % g != 0:
+            raise AssertionError(f"Last dimension ({K}) must be divisible by group_size ({g})")
+    out = {}
+    dev = x.device
+    q = torch.empty((M, K), dtype=torch.int8, device=dev) if codes else None
+    if granularity == GRAN_ROW:
+        scale = torch.empty((M,), dtype=torch.float32, device=dev)
+    elif granularity == GRAN_TENSOR:
+        scale = torch.empty((1,), dtype=torch.float32, device=dev)
+    else:
+        scale = torch.empty((M, K // g), dtype=torch.float32, device=dev)
+    fq = torch.empty((M, K), dtype=x.dtype, device=dev) if fake_quant else None
+    tx = torch.empty((M, K), dtype=x.dtype, device=dev) if transformed else None
+    ws_bytes = int(lib.samq_quant_workspace_bytes(granularity))
+    ws = torch.empty((max(ws_bytes, 4) // 4,), dtype=torch.int32, device=dev) if ws_bytes else None
+    keep = []
+    if divisor is not None:
+        divisor = divisor.to(device=dev, dtype=x.dtype).contiguous()
+        if divisor.numel() != K:
+            raise ValueError("divisor must have K elements")
+    spec = _spec(hadamard, keep)
+    with torch.cuda.device(dev):
+        _lib.check(lib.samq_act_quant_i8(
+            _ptr(x2), _DTYPE_CODE[x.dtype], M, K, ldx, _ptr(divisor),
+            ctypes.byref(spec) if spec is not None else None,
+            granularity, g, _ptr(q), _ptr(scale), _ptr(fq), _ptr(tx),
+            _ptr(ws), ws_bytes, _stream()))
+    if codes:
+        out["q"] = q.view(*lead, K)
+    if granularity == GRAN_ROW:
+        out["scale"] = scale.view(*lead)
+    elif granularity == GRAN_TENSOR:
+        out["scale"] = scale
+    else:
+        out["scale"] = scale.view(*lead, K // g)
+    if fake_quant:
+        out["fq"] = fq.view(*lead, K)
+    if transformed:
+        out["tx"] = tx.view(*lead, K)
+    return out
+
+
+def quantize_weight(w: torch.Tensor, granularity: int = GRAN_ROW, group_size: Optional[int] = None,
+                    codes: bool = True, fake_quant: bool = False):
+    """Run K3 (weight quantization) on ``w`` [N, K] through ``samq_weight_quant_i8``."""
+    _require_cuda(w, "w")
+    if w.dim() != 2:
+        raise AssertionError("weight must be 2-D")
+    if w.dtype not in _DTYPE_CODE:
+        raise TypeError(f"unsupported dtype {w.dtype}")
+    lib = _lib.load()
+    w2, N, K, ldw = _as_rows(w)
+    g = int(group_size) if granularity == GRAN_GROUP else 0
+    if granularity == GRAN_GROUP:
+        if not isinstance(group_size, int):
+            raise AssertionError("group_size must be an integer")
+        if K % g != 0:
+            raise AssertionError(f"in_features ({K}) must be divisible by group_size ({g})")
+    dev = w.device
+    q = torch.empty((N, K), dtype=torch.int8, device=dev) if codes else None
+    shape = {GRAN_ROW: (N,), GRAN_TENSOR: (1,), GRAN_GROUP: (N, K // g if g else 1)}[granularity]
+    scale = torch.empty(shape, dtype=torch.float32, device=dev)
+    fq = torch.empty((N, K), dtype=w.dtype, device=dev) if fake_quant else None
+    ws_bytes = int(lib.samq_quant_workspace_bytes(granularity))
+    ws = torch.empty((max(ws_bytes, 4) // 4,), dtype=torch.int32, device=dev) if ws_bytes else None
+    with torch.cuda.device(dev):
+        _lib.check(lib.samq_weight_quant_i8(
+            _ptr(w2), _DTYPE_CODE[w.dtype], N, K, ldw, granularity, g,
+            _ptr(q), _ptr(scale), _ptr(fq), _ptr(ws), ws_bytes, _stream()))
+    out = {"scale": scale}
+    if codes:
+        out["q"] = q
+    if fake_quant:
+        out["fq"] = fq
+    return out
+
+
+def gemm_i8(a_q: torch.Tensor, w_q: torch.Tensor,
+            a_scale: Optional[torch.Tensor] = None, w_scale: Optional[torch.Tensor] = None,
+            a_gran: int = GRAN_ROW, w_gran: int = GRAN_ROW, group_size: int = 0,
+            bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+            activation: int = ACT_NONE, out_dtype: torch.dtype = torch.float16,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Run K2: ``act(dequant(a_q @ w_q.T) + bias) + residual`` -> [..., N] of ``out_dtype``.
+
+    ``out_dtype=torch.int32`` returns the raw accumulators (no scales / bias allowed).
+    """
+    _require_cuda(a_q, "a_q")
+    _require_cuda(w_q, "w_q")
+    if a_q.dtype != torch.int8 or w_q.dtype != torch.int8:
+        raise TypeError("a_q and w_q must be int8")
+    lib = _lib.load()
+    lead = a_q.shape[:-1]
+    a2, M, K, lda = _as_rows(a_q)
+    if w_q.dim() != 2 or w_q.shape[1] != K:
+        raise ValueError(f"w_q must be [N, {K}]")
+    w2, N, _, ldw = _as_rows(w_q)
+    dev = a_q.device
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    else:
+        if out.dtype != out_dtype or out.shape[-1] != N or out.numel() != M * N or not out.is_contiguous():
+            raise ValueError("out has the wrong dtype, shape or layout")
+    param_dtype = torch.float32 if out_dtype in (torch.float32, torch.int32) else out_dtype
+    if bias is not None:
+        bias = bias.reshape(-1).to(device=dev, dtype=param_dtype).contiguous()
+        if bias.numel() != N:
+            raise ValueError("bias must have N elements")
+    ldr = 0
+    if residual is not None:
+        _require_cuda(residual, "residual")
+        if residual.dtype != out_dtype:
+            raise TypeError("residual must have the output dtype")
+        residual, rm, rn, ldr = _as_rows(residual)
+        if rm != M or rn != N:
+            raise ValueError("residual must be [..., N] with the rows of a_q")
+    if a_scale is not None:
+        a_scale = a_scale.to(device=dev, dtype=torch.float32).contiguous()
+    if w_scale is not None:
+        w_scale = w_scale.to(device=dev, dtype=torch.float32).contiguous()
+    with torch.cuda.device(dev):
+        _lib.check(lib.samq_gemm_i8(
+            _ptr(a2), lda, _ptr(w2), ldw, M, N, K,
+            _ptr(a_scale), a_gran, _ptr(w_scale), w_gran, int(group_size or 0),
+            _ptr(bias), _ptr(residual), ldr, activation,
+            _ptr(out), _OUT_CODE[out_dtype], N, _ptr(status_word(dev)), _stream()))
+    return out.view(*lead, N)
