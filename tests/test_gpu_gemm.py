@@ -1,0 +1,140 @@
+"""K2 parity on the GPU: int32 accumulators bit-exact against the CPU oracle, the fused
+epilogue within one rounding step of the output dtype, config 1 against the reference digests."""
+import hashlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TDT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+
+
+def f32(t):
+    return t.detach().float().cpu().numpy()
+
+
+def rand_codes(rng, shape):
+    return rng.integers(-127, 128, size=shape, dtype=np.int8)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (1, 8, 16), (196, 2304, 768), (300, 520, 400),
+                                   (4900, 768, 3072), (4096, 3072, 768), (129, 257 * 8, 1280), (77, 1280, 5120)])
+def test_int32_accumulators_exact(cuda_device, M, N, K):
+    from sam_quantization_b200 import ops
+    rng = np.random.default_rng(M * 7 + N)
+    a, w = rand_codes(rng, (M, K)), rand_codes(rng, (N, K))
+    acc = ops.gemm_i8(torch.from_numpy(a).to(cuda_device), torch.from_numpy(w).to(cuda_device), out_dtype=torch.int32)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert np.array_equal(acc.cpu().numpy(), O.int32_accumulators(a, w))
+
+
+def test_extreme_codes_do_not_overflow(cuda_device):
+    from sam_quantization_b200 import ops
+    M, N, K = 130, 264, 5120
+    a = np.full((M, K), -127, np.int8)
+    w = np.full((N, K), 127, np.int8)
+    w[::2] = -127
+    acc = ops.gemm_i8(torch.from_numpy(a).to(cuda_device), torch.from_numpy(w).to(cuda_device), out_dtype=torch.int32)
+    assert np.array_equal(acc.cpu().numpy(), O.int32_accumulators(a, w))
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("act,use_res,use_bias", [(None, False, True), ("gelu", False, True), (None, True, True),
+                                                  ("gelu", True, False)])
+def test_fused_epilogue(cuda_device, dt, act, use_res, use_bias):
+    from sam_quantization_b200 import ops
+    rng = np.random.default_rng(3)
+    M, N, K = 333, 776, 768
+    a, w = rand_codes(rng, (M, K)), rand_codes(rng, (N, K))
+    sa = (rng.random(M) * 0.05 + 0.001).astype(np.float32)
+    sw = (rng.random(N) * 0.001 + 0.0001).astype(np.float32)
+    bias = O.rnd(rng.standard_normal(N) * 0.5, dt) if use_bias else None
+    res = O.rnd(rng.standard_normal((M, N)), dt) if use_res else None
+    dev = cuda_device
+    y = ops.gemm_i8(torch.from_numpy(a).to(dev), torch.from_numpy(w).to(dev),
+                    torch.from_numpy(sa).to(dev), torch.from_numpy(sw).to(dev),
+                    bias=None if bias is None else torch.from_numpy(bias).to(dev),
+                    residual=None if res is None else torch.from_numpy(res).to(TDT[dt]).to(dev),
+                    activation=1 if act else 0, out_dtype=TDT[dt])
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = O.dequant_epilogue(O.int32_accumulators(a, w), sa, sw, bias, act, res, dt)
+    got = f32(y)
+    ulp = {"f16": 2.0 ** -10, "bf16": 2.0 ** -7, "f32": 2.0 ** -20}[dt]
+    assert np.all(np.abs(got - want) <= ulp * np.maximum(np.abs(want), 1e-2) + 1e-6)
+
+
+def test_per_tensor_scales_and_null_scales(cuda_device):
+    from sam_quantization_b200 import ops
+    rng = np.random.default_rng(4)
+    M, N, K = 64, 256, 256
+    a, w = rand_codes(rng, (M, K)), rand_codes(rng, (N, K))
+    dev = cuda_device
+    y = ops.gemm_i8(torch.from_numpy(a).to(dev), torch.from_numpy(w).to(dev),
+                    torch.tensor([0.01], device=dev), torch.tensor([0.002], device=dev), a_gran=1, w_gran=1,
+                    out_dtype=torch.float32)
+    want = O.int32_accumulators(a, w).astype(np.float32) * np.float32(0.01) * np.float32(0.002)
+    assert np.allclose(f32(y), want, rtol=1e-6)
+    y = ops.gemm_i8(torch.from_numpy(a).to(dev), torch.from_numpy(w).to(dev), out_dtype=torch.float32)
+    assert np.array_equal(f32(y), O.int32_accumulators(a, w).astype(np.float32))
+
+
+def test_bad_arguments(cuda_device):
+    from sam_quantization_b200 import ops
+    from sam_quantization_b200._lib import SamqError
+    dev = cuda_device
+    a = torch.zeros((8, 24), dtype=torch.int8, device=dev)       # K = 24: row stride not 16-byte aligned
+    w = torch.zeros((8, 24), dtype=torch.int8, device=dev)
+    with pytest.raises(SamqError):
+        ops.gemm_i8(a, w, out_dtype=torch.int32)
+    a = torch.zeros((8, 32), dtype=torch.int8, device=dev)
+    w = torch.zeros((8, 32), dtype=torch.int8, device=dev)
+    with pytest.raises(SamqError):                                 # raw accumulators take no scales
+        ops.gemm_i8(a, w, torch.ones(8, device=dev), out_dtype=torch.int32)
+    empty = ops.gemm_i8(torch.zeros((0, 32), dtype=torch.int8, device=dev), w, out_dtype=torch.float16)
+    assert empty.shape == (0, 8)
+
+
+def test_config1_against_reference_digests(cuda_device, golden):
+    """BASELINE config 1 end to end through the C ABI: the fake-quant activations and weights
+    hash to the digests of the reference's outputs; codes, scales and int32 accumulators equal
+    the oracle's; the fp16 layer output is within 1e-2 relative max-abs of the reference's."""
+    from sam_quantization_b200 import ops
+    g = golden("config1")
+    dev = cuda_device
+    gen = torch.Generator().manual_seed(1)
+    M, K, N = 4096, 768, 3072
+    x = torch.randn(M, K, generator=gen)
+    idx = torch.randperm(K, generator=gen)[:max(1, K // 100)]
+    x[:, idx] *= 20
+    w = torch.randn(N, K, generator=gen) * 0.02
+    b = torch.randn(N, generator=gen) * 0.01
+    x16, w16, b16 = x.half(), w.half(), b.half()
+    s, lw, lb, fcs = O.smooth_ln_fcs(np.ones(K, np.float32), np.zeros(K, np.float32), [w16.float().numpy()],
+                                     g["act_scales"], 0.5, "f16")
+    # online SmoothQuant: x / s with the divisor fused into K1 equals the folded LayerNorm scale
+    xs_dev = (x16.to(dev) * torch.from_numpy(lw).half().to(dev))
+    a = ops.quantize(xs_dev, 0, fake_quant=True)
+    assert hashlib.sha256(a["fq"].cpu().numpy().tobytes()).hexdigest() == str(g["fq_x_sha256"])
+    ws = torch.from_numpy(fcs[0]).half().to(dev)
+    wq = ops.quantize_weight(ws, 0, fake_quant=True)
+    assert hashlib.sha256(wq["fq"].cpu().numpy().tobytes()).hexdigest() == str(g["fq_w_sha256"])
+    qx, sx, _ = O.quantize(xs_dev.float().cpu().numpy(), "per_token", "f16")
+    qw, sw, _ = O.quantize(fcs[0], "per_channel", "f16")
+    assert np.array_equal(a["q"].cpu().numpy(), O.saturate_codes(qx))
+    assert np.array_equal(f32(a["scale"]), sx)
+    assert np.array_equal(wq["q"].cpu().numpy(), O.saturate_codes(qw))
+    assert np.array_equal(f32(wq["scale"]), sw)
+    acc = ops.gemm_i8(a["q"], wq["q"], out_dtype=torch.int32)
+    assert np.array_equal(acc.cpu().numpy(), O.int32_accumulators(O.saturate_codes(qx), O.saturate_codes(qw)))
+    y = ops.gemm_i8(a["q"], wq["q"], a["scale"], wq["scale"], bias=b16.to(dev), out_dtype=torch.float16)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = g["y_sample"]
+    got = f32(y)[::97, ::53]
+    assert np.abs(got - want).max() / np.abs(want).max() < 1e-2

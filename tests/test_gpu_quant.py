@@ -1,0 +1,189 @@
+"""K1 / K3 parity on the GPU: int8 codes, scales and fake-quant outputs from the CUDA kernels
+(called through the C ABI) against the reference fixtures and the CPU oracle, bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TDT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+ACT = {"per_token": 0, "per_tensor": 1, "per_group_token": 2}
+
+
+def to_dev(a, dt, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(TDT[dt]).to(dev)
+
+
+def f32(t):
+    return t.detach().float().cpu().numpy()
+
+
+def check_against_oracle(x_np, dt, gran_name, group, dev, divisor=None):
+    from sam_quantization_b200 import ops
+    x = to_dev(x_np, dt, dev)
+    div_t = None if divisor is None else to_dev(divisor, dt, dev)
+    out = ops.quantize(x, ACT[gran_name], group, divisor=div_t, codes=True, fake_quant=True, transformed=True)
+    xin = O.rnd(x_np, dt)
+    if divisor is not None:
+        xin = O._div(xin, O.rnd(divisor, dt), dt)
+    q, s, fq = O.quantize(xin, gran_name, dt, group)
+    assert np.array_equal(out["q"].cpu().numpy(), O.saturate_codes(q))
+    assert np.array_equal(f32(out["scale"]).reshape(-1), np.asarray(s, np.float32).reshape(-1))
+    assert np.array_equal(f32(out["fq"]), fq)
+    assert np.array_equal(f32(out["tx"]), xin)
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16", "f32"])
+def test_quantizers_match_reference_fixtures(cuda_device, golden, dt):
+    from sam_quantization_b200 import ops
+    g = golden("quantizers")
+    x = to_dev(g[f"{dt}/x"], dt, cuda_device)
+    for name, gran, group in (("act_per_token", 0, None), ("act_per_tensor", 1, None), ("act_per_group32", 2, 32)):
+        out = ops.quantize(x, gran, group, fake_quant=True)
+        assert np.array_equal(f32(out["fq"]), g[f"{dt}/{name}"]), name
+    x3 = to_dev(g[f"{dt}/x3"], dt, cuda_device)
+    assert np.array_equal(f32(ops.quantize(x3, 0, fake_quant=True)["fq"]), g[f"{dt}/act3_per_token"])
+    assert np.array_equal(f32(ops.quantize(x3, 2, 16, fake_quant=True)["fq"]), g[f"{dt}/act3_per_group16"])
+    w = to_dev(g[f"{dt}/w"], dt, cuda_device)
+    for name, gran, group in (("w_per_channel", 0, None), ("w_per_tensor", 1, None), ("w_per_group32", 2, 32)):
+        out = ops.quantize_weight(w, gran, group, fake_quant=True)
+        assert np.array_equal(f32(out["fq"]), g[f"{dt}/{name}"]), name
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("K", [768, 1024, 1280, 3072, 4096, 5120])
+def test_per_token_codes_scales_bit_exact(cuda_device, dt, K):
+    rng = np.random.default_rng(K)
+    x = rng.standard_normal((197, K)).astype(np.float32)
+    x[:, rng.permutation(K)[: max(1, K // 100)]] *= 20
+    x[7] = 0
+    check_against_oracle(x, dt, "per_token", None, cuda_device)
+
+
+@pytest.mark.parametrize("dt", ["f16", "f32"])
+@pytest.mark.parametrize("gran,group", [("per_tensor", None), ("per_group_token", 128), ("per_group_token", 64),
+                                        ("per_group_token", 8), ("per_group_token", 384), ("per_group_token", 6)])
+def test_other_granularities_bit_exact(cuda_device, dt, gran, group):
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((61, 768)).astype(np.float32)
+    x[:, 3] *= 20
+    check_against_oracle(x, dt, gran, group, cuda_device)
+
+
+def test_ragged_and_odd_shapes(cuda_device):
+    rng = np.random.default_rng(9)
+    for M, K in [(1, 8), (3, 7), (33, 100), (5, 8200), (2, 12288)]:
+        x = rng.standard_normal((M, K)).astype(np.float32)
+        check_against_oracle(x, "f16", "per_token", None, cuda_device)
+        check_against_oracle(x, "f32", "per_tensor", None, cuda_device)
+
+
+def test_smoothquant_divisor(cuda_device):
+    rng = np.random.default_rng(10)
+    x = rng.standard_normal((64, 768)).astype(np.float32)
+    d = (rng.random(768) * 4 + 0.05).astype(np.float32)
+    for dt in ("f16", "bf16", "f32"):
+        check_against_oracle(x, dt, "per_token", None, cuda_device, divisor=d)
+    check_against_oracle(x[:, :100], "f16", "per_token", None, cuda_device, divisor=d[:100])
+
+
+def test_strided_rows_and_empty(cuda_device):
+    from sam_quantization_b200 import ops
+    rng = np.random.default_rng(11)
+    big = torch.from_numpy(rng.standard_normal((40, 2048)).astype(np.float32)).half().to(cuda_device)
+    view = big[:, 256:1024]                       # row stride 2048, 768 columns
+    out = ops.quantize(view, 0, fake_quant=True)
+    q, s, fq = O.quantize(view.float().cpu().numpy(), "per_token", "f16")
+    assert np.array_equal(out["q"].cpu().numpy(), O.saturate_codes(q))
+    assert np.array_equal(f32(out["scale"]), s)
+    empty = torch.empty((0, 768), dtype=torch.float16, device=cuda_device)
+    out = ops.quantize(empty, 0)
+    assert out["q"].shape == (0, 768) and out["scale"].shape == (0,)
+
+
+def test_leading_dims_kept(cuda_device):
+    from sam_quantization_b200 import ops
+    x = torch.randn(2, 3, 5, 64, device=cuda_device, dtype=torch.float16)
+    out = ops.quantize(x, 0, fake_quant=True)
+    assert out["q"].shape == (2, 3, 5, 64) and out["scale"].shape == (2, 3, 5) and out["fq"].shape == x.shape
+    out = ops.quantize(x, 2, 16)
+    assert out["scale"].shape == (2, 3, 5, 4)
+
+
+def test_bad_arguments_raise(cuda_device):
+    from sam_quantization_b200 import ops
+    from sam_quantization_b200._lib import SamqError
+    x = torch.randn(4, 64, device=cuda_device, dtype=torch.float16)
+    with pytest.raises(AssertionError):
+        ops.quantize(x, 2, 48)
+    with pytest.raises(RuntimeError):
+        ops.quantize(x.cpu(), 0)
+    with pytest.raises(SamqError):
+        ops.quantize(x, 1, hadamard=ops.Hadamard("full"))
+
+
+@pytest.mark.parametrize("n", [16, 64, 1024, 4096])
+def test_full_hadamard_pow2_bit_exact(cuda_device, golden, n):
+    """Power-of-two online Hadamard (fp32 butterflies in the reference's order, one rounding to
+    fp16) then per-token int8: transformed values, codes and scales all exact."""
+    from sam_quantization_b200 import ops
+    g = golden("hadamard")
+    x16 = O.rnd(g[f"hadU/{n}/x"], "f16")
+    x = to_dev(x16, "f16", cuda_device)
+    out = ops.quantize(x, 0, hadamard=ops.Hadamard("full"), fake_quant=True, transformed=True)
+    assert np.array_equal(f32(out["tx"]), g[f"hadU/{n}/y_f16_via_f32"])
+    q, s, fq = O.quantize(g[f"hadU/{n}/y_f16_via_f32"], "per_token", "f16")
+    assert np.array_equal(out["q"].cpu().numpy(), O.saturate_codes(q))
+    assert np.array_equal(f32(out["scale"]), s)
+    assert np.array_equal(f32(out["fq"]), fq)
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16", "f32"])
+def test_full_hadamard_random_rows_with_signs(cuda_device, dt):
+    from sam_quantization_b200 import ops
+    rng = np.random.default_rng(21)
+    for n in (1024, 4096, 256):
+        x = O.rnd(rng.standard_normal((37, n)).astype(np.float32) * 3, dt)
+        signs = (rng.integers(0, 2, n) * 2 - 1).astype(np.int8)
+        had = ops.Hadamard("full", signs=torch.from_numpy(signs).to(cuda_device))
+        out = ops.quantize(to_dev(x, dt, cuda_device), 0, hadamard=had, transformed=True)
+        want = O.hadamard_full_online(x, dt, signs=signs)
+        assert np.array_equal(f32(out["tx"]), want)
+        q, s, _ = O.quantize(want, "per_token", dt)
+        assert np.array_equal(out["q"].cpu().numpy(), O.saturate_codes(q))
+        assert np.array_equal(f32(out["scale"]), s)
+
+
+def test_partial_hadamard_across_heads(cuda_device):
+    from sam_quantization_b200 import ops
+    rng = np.random.default_rng(22)
+    for C, had_dim in ((1024, 64), (1280, 80), (256, 16)):
+        x = O.rnd(rng.standard_normal((50, C)).astype(np.float32), "f16")
+        out = ops.quantize(to_dev(x, "f16", cuda_device), 0, hadamard=ops.Hadamard("partial", had_dim=had_dim),
+                           transformed=True)
+        want = O.hadamard_partial_online(x, had_dim, "f16")
+        assert np.array_equal(f32(out["tx"]), want)
+        q, s, _ = O.quantize(want, "per_token", "f16")
+        assert np.array_equal(out["q"].cpu().numpy(), O.saturate_codes(q))
+
+
+@pytest.mark.parametrize("n", [768, 1280, 3072, 5120, 48])
+def test_full_hadamard_with_explicit_factor(cuda_device, golden, n):
+    """n = had_k * 2^p: the had_k x had_k mix is a small matmul whose fp32 summation order is
+    the BLAS's in the reference, so this boundary is toleranced (a few fp32 ulps before the
+    fp16 rounding), not bit exact."""
+    from sam_quantization_b200 import ops
+    g = golden("hadamard")
+    for k in (12, 40):
+        O.register_hadk(k, g[f"had{k}"])
+    hadk, k = O.get_hadK(n)
+    rng = np.random.default_rng(n)
+    x = O.rnd(rng.standard_normal((9, n)).astype(np.float32), "f16")
+    had = ops.Hadamard("full", had_k=k, hadk=torch.from_numpy(hadk).to(cuda_device))
+    out = ops.quantize(to_dev(x, "f16", cuda_device), 0, hadamard=had, transformed=True)
+    want = O.hadamard_full_online(x, "f16")
+    got = f32(out["tx"])
+    assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max()
+    assert (got != want).mean() < 0.01
