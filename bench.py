@@ -1,0 +1,342 @@
+"""Headline benchmark: SAM ViT-H W8A8 (SmoothQuant) image-encoder throughput in images/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = the whole global batch (64 synthetic 1024x1024 images) through the encoder, sharded by
+image over the N ranks (one process per GPU, no collective on the data path).  Prints one JSON
+line (rank 0).  ``--impl reference`` times the reference's CPU fake-quant path (restated in
+oracle/torch_twin.py, since the reference checkout does not travel) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "sam_vit_h_w8a8_encoder_images_per_s"
+GLOBAL_BATCH = 64
+MEAN = (0.485, 0.456, 0.406)
+STD = (0.229, 0.224, 0.225)
+
+# int8 linear work per image of an encoder: windowed blocks see 25 windows x 196 tokens in qkv /
+# proj and 4096 tokens in the MLP; global blocks see 4096 everywhere.
+ENC = {"vit_b": (768, 12, 4), "vit_l": (1024, 24, 4), "vit_h": (1280, 32, 4)}
+
+
+def linear_ops_per_image(model_type: str) -> float:
+    C, depth, n_global = ENC[model_type]
+    windowed = depth - n_global
+    mac = windowed * (4900 * 4 * C * C + 4096 * 8 * C * C) + n_global * (4096 * 12 * C * C)
+    return 2.0 * mac
+
+
+def synthetic_images(n: int, seed: int, size: int = 1024) -> torch.Tensor:
+    """~U(0,1) images normalised per channel, fp16, on the CPU."""
+    g = torch.Generator().manual_seed(seed)
+    img = torch.rand(n, 3, size, size, generator=g)
+    mean = torch.tensor(MEAN).view(1, 3, 1, 1)
+    std = torch.tensor(STD).view(1, 3, 1, 1)
+    return ((img - mean) / std).to(torch.float16)
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self._stop = index, [], threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower() == "active" for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": float(self.samples[0][1]), "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------
+# model construction (shared by both arms: same seeds, same SmoothQuant folding)
+# ------------------------------------------------------------------------------------------
+
+def build_float_encoder(model_type: str, device, dtype, seed: int = 4):
+    from sam_quantization_b200.sam_encoder import build_encoder
+    return build_encoder(model_type, seed=seed, dtype=dtype, device=device,
+                         attn_dtype=torch.bfloat16 if dtype == torch.float16 else None)
+
+
+def build_quantized_encoder(model_type: str, device, calib_images: int = 8):
+    """ViT encoder, SmoothQuant (alpha 0.5) from `calib_images` synthetic calibration images run
+    through the float model, then W8A8 on every linear (per-channel weights, per-token acts)."""
+    from sam_quantization_b200.RTN_quantization import (W8A8Linear, get_act_scales_sam,
+                                                        replace_linear_with_target_and_quantize, smooth_sam)
+    model = build_float_encoder(model_type, device, torch.float16)
+    calib = (synthetic_images(1, 200 + i).to(device) for i in range(calib_images))
+    with torch.no_grad():
+        scales = get_act_scales_sam(model, calib, num_samples=calib_images)
+    smooth_sam(model, scales, alpha=0.5)
+    replace_linear_with_target_and_quantize(model, W8A8Linear, 8, [], weight_quant="per_channel", act_quant="per_token")
+    return model
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm: the CPU fake-quant path on the host cores
+# ------------------------------------------------------------------------------------------
+
+def cpu_reference_images_per_s(model_type: str, budget_s: float = 25.0):
+    """Times the reference's CPU path (fp32 model, fake-quant W8A8Linear on every linear — the
+    reference's eval never calls .half()) on one 1024x1024 image.  If a whole image would exceed
+    the budget, only the first `n` blocks are run (they all cost the same linear work; the subset
+    always contains a global-attention block when n >= 8) and the time is scaled by depth / n."""
+    from oracle.torch_twin import RefW8A8Linear, replace_linears
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    model = build_float_encoder(model_type, "cpu", torch.float32)
+    replace_linears(model, lambda lin: RefW8A8Linear.from_float(lin, 8))
+    enc = model.image_encoder
+    img = synthetic_images(1, 4).float()
+    depth = len(enc.blocks)
+    with torch.no_grad():
+        x = enc.patch_embed(img) + enc.pos_embed
+        t0 = time.perf_counter()
+        x = enc.blocks[0](x)
+        t_block = time.perf_counter() - t0
+        n = depth if t_block * depth <= budget_s else max(1, min(depth, int(budget_s / max(t_block, 1e-9))))
+        if n >= 8:
+            n = max(n, 8)
+        t0 = time.perf_counter()
+        for blk in enc.blocks[1:n]:
+            x = blk(x)
+        t_rest = time.perf_counter() - t0
+    total = (t_block + t_rest) * depth / n
+    sample = (f"1 image of 1024x1024, fp32 fake-quant twin of the reference's W8A8Linear path, "
+              f"{n} of {depth} blocks timed ({t_block + t_rest:.1f} s)" + ("" if n == depth else f", scaled by {depth}/{n}"))
+    return 1.0 / total, cores, sample
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    sample = ""
+    cores = os.cpu_count() or 1
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_reference_images_per_s(args.model, budget_s=4.0)
+    for _ in range(max(1, args.steps)):
+        v, cores, sample = cpu_reference_images_per_s(args.model, budget_s=args.ref_budget)
+        vals.append(v)
+    value = sorted(vals)[len(vals) // 2]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * GLOBAL_BATCH / value,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"SAM {args.model} encoder W8A8 SmoothQuant, 1024x1024, global batch {GLOBAL_BATCH}"},
+        "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------
+
+def run_ours(args):
+    import torch.distributed as dist
+    from sam_quantization_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the W8A8 engine has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert GLOBAL_BATCH % world == 0
+    local_n = GLOBAL_BATCH // world
+    chunk = min(args.chunk, local_n)
+
+    model = build_quantized_encoder(args.model, dev)
+    enc = model.image_encoder
+
+    # this rank's shard of the global batch: images [rank*local_n, (rank+1)*local_n), seeded per image
+    host = torch.empty((local_n, 3, 1024, 1024), dtype=torch.float16).pin_memory()
+    for i in range(local_n):
+        host[i] = synthetic_images(1, 4000 + rank * local_n + i)[0]
+    resident = host.to(dev)
+    out_host = torch.empty((local_n, 256, 64, 64), dtype=torch.float16).pin_memory()
+    out_dev = torch.empty((local_n, 256, 64, 64), dtype=torch.float16, device=dev)
+
+    def encode(src):
+        with torch.no_grad():
+            for i in range(0, local_n, chunk):
+                out_dev[i:i + chunk] = enc(src[i:i + chunk])
+
+    def step_resident():
+        encode(resident)
+
+    stage = torch.empty_like(resident)
+
+    def step_e2e():
+        for i in range(0, local_n, chunk):
+            stage[i:i + chunk].copy_(host[i:i + chunk], non_blocking=True)
+            with torch.no_grad():
+                out_dev[i:i + chunk] = enc(stage[i:i + chunk])
+        out_host.copy_(out_dev, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(3, args.warmup)):
+        step_resident()
+    ops.reset_counters()
+    with ClockSampler(local_rank) as clocks:
+        total_ms = timed(step_resident, args.steps)
+    launches = ops.launch_count()
+    ops.check_status(dev)
+    value = GLOBAL_BATCH * args.steps / (total_ms / 1000.0)
+
+    for _ in range(2):
+        step_e2e()
+    e2e_ms = timed(step_e2e, args.steps)
+    e2e_value = GLOBAL_BATCH * args.steps / (e2e_ms / 1000.0)
+
+    # per-kernel timing of the dominant kernel (the int8 GEMM): one more step with CUDA events
+    # around every GEMM launch on the launching stream
+    torch.cuda.synchronize()
+    ops.enable_kernel_timing(True)
+    step_resident()
+    torch.cuda.synchronize()
+    prof = ops.kernel_timing_summary()
+    ops.enable_kernel_timing(False)
+
+    # verification gather (outside every timed region): embeddings of all ranks to rank 0
+    checksum = None
+    if world > 1:
+        gathered = [torch.empty_like(out_dev) for _ in range(world)] if rank == 0 else None
+        dist.gather(out_dev, gathered, dst=0)
+        if rank == 0:
+            allv = torch.cat(gathered, 0)
+            checksum = float(allv.float().abs().mean().item())
+    else:
+        checksum = float(out_dev.float().abs().mean().item())
+    finite = bool(torch.isfinite(out_dev).all().item())
+
+    if rank == 0:
+        peaks, peak_kind = read_peaks()
+        gemm = prof.get("gemm_i8", {"ms": 0.0, "ops": 0.0, "launches": 0})
+        quant = prof.get("act_quant", {"ms": 0.0, "bytes": 0.0, "launches": 0})
+        # dense int8 tensor peak is twice the dense bf16 peak on this part; the measured bf16
+        # figure (sustained: the GEMMs run inside a long step) is doubled accordingly
+        int8_peak = 2.0 * float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
+        achieved = (gemm["ops"] / (gemm["ms"] / 1000.0) / 1e12) if gemm["ms"] > 0 else 0.0
+        line = {
+            "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": f"SAM {args.model} encoder W8A8 SmoothQuant, 1024x1024, global batch {GLOBAL_BATCH}"
+                                   f" sharded by image, {chunk} images per forward",
+                       "l2": "inputs and activations per forward exceed the 126 MB L2", "parallelism": f"dp{world}"},
+            "e2e": {"value": e2e_value, "unit": "images/s",
+                    "h2d_bytes_per_step": int(host.numel() * host.element_size()) * world,
+                    "d2h_bytes_per_step": int(out_host.numel() * out_host.element_size()) * world},
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
+                         "frac": achieved / int8_peak if int8_peak else None, "traffic": None,
+                         "kernel": "gemm_i8_kernel (tcgen05 kind::i8)", "peak_source": f"2 x bf16_tflops_sustained, {peak_kind}",
+                         "gemm_ms_per_step": gemm["ms"], "gemm_launches_per_step": gemm["launches"],
+                         "linear_tops_per_image": linear_ops_per_image(args.model) / 1e12},
+            "act_quant": {"achieved_gbs": (quant["bytes"] / (quant["ms"] / 1000.0) / 1e9) if quant["ms"] > 0 else 0.0,
+                          "peak_gbs": float(peaks["hbm_gbs"]), "ms_per_step": quant["ms"], "launches_per_step": quant["launches"]},
+            "verify": {"finite": finite, "mean_abs_embedding": checksum},
+        }
+        if not args.no_cpu_baseline and world == 1:
+            v, cores, sample = cpu_reference_images_per_s(args.model, budget_s=args.ref_budget)
+            line["cpu_baseline"] = {"value": v, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="vit_h", choices=list(ENC))
+    ap.add_argument("--chunk", type=int, default=8, help="images per encoder forward")
+    ap.add_argument("--ref-budget", dest="ref_budget", type=float, default=25.0, help="seconds of CPU work per reference sample")
+    ap.add_argument("--no-cpu-baseline", dest="no_cpu_baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -115,14 +115,16 @@ size_t samq_quant_workspace_bytes(int granularity);
  *   quantize_weight_per_tensor_absmax               :14-21
  *   quantize_weight_per_group_absmax_input_features :23-50
  * stopping before the final `mul_(scales)`:
- *     s = max(absmax, 1e-5) / 127          (in the tensor dtype)
+ *     s = max(absmax, 1e-5) / q_max        (in the tensor dtype; q_max = 2^(n_bits-1) - 1)
  *     q = round_half_even(x / s)           (quotient rounded to the tensor dtype first)
+ * n_bits is the reference's `n_bits` argument, 2..8; codes of fewer than 8 bits are still
+ * stored one per int8 and feed the same int8 GEMM.
  * Optional steps before the absmax, in this order:
  *     x <- x / divisor[col]   (SmoothQuant divisor, RTN_quantization/Smooth.py:39-40),
  *     x <- hadamard(x * signs) (see samq_hadamard_spec), each rounded once to the dtype.
  *
  * x        : [M, K] of `dtype`, row stride `ldx` elements
- * q_out    : [M, K] int8 codes, saturated to [-127, 127], or NULL
+ * q_out    : [M, K] int8 codes, saturated to [-q_max, q_max], or NULL
  * scale_out: fp32 copy of the dtype-rounded scale: [M] | [1] | [M, K/group], or NULL
  * fq_out   : [M, K] of `dtype`, the fake-quantized value q*s exactly as the
  *            reference function returns it (no saturation), or NULL
@@ -131,7 +133,7 @@ size_t samq_quant_workspace_bytes(int granularity);
  * Hadamard is only combined with SAMQ_GRAN_ROW. */
 int samq_act_quant_i8(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
                       const void* divisor, const samq_hadamard_spec* had,
-                      int granularity, int group_size,
+                      int granularity, int group_size, int n_bits,
                       int8_t* q_out, float* scale_out, void* fq_out, void* tx_out,
                       void* workspace, size_t workspace_bytes, void* stream);
 
@@ -139,7 +141,7 @@ int samq_act_quant_i8(const void* x, int dtype, int64_t M, int64_t K, int64_t ld
  * its own symbol because the reference names the weight quantizers separately
  * (per_tensor_channel_group.py:5-50). scale_out: [N] | [1] | [N, K/group]. */
 int samq_weight_quant_i8(const void* w, int dtype, int64_t N, int64_t K, int64_t ldw,
-                         int granularity, int group_size,
+                         int granularity, int group_size, int n_bits,
                          int8_t* q_out, float* scale_out, void* fq_out,
                          void* workspace, size_t workspace_bytes, void* stream);
 

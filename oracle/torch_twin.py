@@ -1,0 +1,144 @@
+"""Float / fake-quant twins of the quantized layers — TEST INFRASTRUCTURE, NOT PRODUCT.
+
+Torch restatements of the reference's modules, used to drive the float twin of the encoder
+through the reference's quantize -> dequantize arithmetic on the same weights:
+
+* ``RefW8A8Linear``      RTN_quantization/per_tensor_channel_group.py:95-199
+* ``RefActQuantWrapper`` quarot/utils.py:202-298 (Hadamard through the pure-torch ``matmul_hadU``,
+                         the designated stand-in for the absent fast_hadamard_transform kernel)
+
+They run wherever their tensors live (CPU in the no-GPU tests, cuda in the GPU tests) with plain
+torch ops, op for op in the tensor's dtype like the reference.  tests/test_oracle_golden.py pins
+``RefW8A8Linear`` to outputs of the reference's own class (tests/golden/w8a8_linear.npz).
+Only tests/, __graft_entry__.smoke() and bench.py's reference leg may import this file.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+
+
+@torch.no_grad()
+def fq_rows(t, n_bits=8):
+    """quantize_*_per_token/per_channel_absmax (:5-12,:53-61), in place."""
+    scales = t.abs().max(dim=-1, keepdim=True)[0]
+    scales.clamp_(min=1e-5).div_(2 ** (n_bits - 1) - 1)
+    t.div_(scales).round_().mul_(scales)
+    return t
+
+
+@torch.no_grad()
+def fq_tensor(t, n_bits=8):
+    """quantize_*_per_tensor_absmax (:14-21,:64-72), in place."""
+    scales = t.abs().max()
+    scales.clamp_(min=1e-5).div_(2 ** (n_bits - 1) - 1)
+    t.div_(scales).round_().mul_(scales)
+    return t
+
+
+@torch.no_grad()
+def fq_groups(t, group_size, n_bits=8):
+    """per-group variants (:23-50,:74-93): groups of the last dim are rows."""
+    shape = t.shape
+    assert shape[-1] % group_size == 0
+    fq_rows(t.view(-1, group_size), n_bits)
+    return t.view(shape)
+
+
+def fake_quant(t, granularity, group_size=None, n_bits=8):
+    if granularity in ("per_token", "per_channel"):
+        return fq_rows(t, n_bits)
+    if granularity == "per_tensor":
+        return fq_tensor(t, n_bits)
+    if granularity in ("per_group_token", "per_group"):
+        return fq_groups(t, group_size, n_bits)
+    raise ValueError(granularity)
+
+
+class RefW8A8Linear(nn.Module):
+    def __init__(self, weight, bias, act_quant="per_token", quantize_output=False, group_size=None, n_bits=8):
+        super().__init__()
+        self.weight, self.bias = weight, bias
+        self.act_quant_name, self.quantize_output = act_quant, quantize_output
+        self.group_size, self.n_bits = group_size, n_bits
+
+    @staticmethod
+    def from_float(module, n_bits, weight_quant="per_channel", act_quant="per_token", quantize_output=False, group_size=None):
+        assert isinstance(module, nn.Linear)
+        w = fake_quant(module.weight.data, weight_quant, group_size, n_bits)
+        return RefW8A8Linear(w, None if module.bias is None else module.bias.data, act_quant, quantize_output, group_size, n_bits)
+
+    @torch.no_grad()
+    def forward(self, x):
+        q_x = fake_quant(x.contiguous().clone(), self.act_quant_name, self.group_size, self.n_bits)
+        y = torch.nn.functional.linear(q_x, self.weight, self.bias)
+        if self.quantize_output:
+            y = fake_quant(y, self.act_quant_name, self.group_size, self.n_bits)
+        return y
+
+
+def is_pow2(n):
+    return n > 0 and (n & (n - 1)) == 0
+
+
+def matmul_hadU(X, hadK=None, K=1):
+    """quarot/hadamard_utils.py:59-80 with the table passed in."""
+    n = X.shape[-1]
+    y = X.reshape(-1, n).clone()
+    chunk, stride = n // K, 1
+    while stride < chunk:
+        v = y.view(-1, n // (2 * stride), 2, stride)
+        a, b = v[:, :, 0, :].clone(), v[:, :, 1, :].clone()
+        v[:, :, 0, :] = a + b
+        v[:, :, 1, :] = a - b
+        stride *= 2
+    if K > 1:
+        y = (hadK.view(1, K, K).to(y) @ y.view(-1, K, chunk)).reshape(-1, n)
+    return y.view(X.shape) / torch.tensor(n).sqrt()
+
+
+class RefActQuantWrapper(nn.Module):
+    """quarot/utils.py:202-298 with ``fp32_had`` semantics for the transforms."""
+
+    def __init__(self, module, act_quant="per_token", weight_quant="per_channel", n_bit=8, group_size=None):
+        super().__init__()
+        self.module = module
+        self.act_quant_name, self.group_size, self.n_bits = act_quant, group_size, n_bit
+        self.had_K, self.K, self.had_dim = None, 1, 0
+        self.online_full_had = self.online_partial_had = False
+        self.quantize_input = self.quantize_output = False
+        fake_quant(module.weight.data, weight_quant, group_size, n_bit)
+
+    @torch.no_grad()
+    def forward(self, x):
+        dt = x.dtype
+        if self.online_full_had:
+            x = matmul_hadU(x.float(), self.had_K, self.K).to(dt)
+        elif self.online_partial_had:
+            shape = x.shape
+            heads = shape[-1] // self.had_dim
+            v = x.float().reshape(-1, heads, self.had_dim).transpose(1, 2)
+            if self.K == 1:
+                v = matmul_hadU(v.contiguous())
+            else:
+                v = (self.had_K.to(v) @ v.transpose(1, 2)).transpose(1, 2) / math.sqrt(heads)
+            x = v.transpose(1, 2).reshape(shape).to(dt)
+        if self.quantize_input:
+            x = fake_quant(x.contiguous().clone(), self.act_quant_name, self.group_size, self.n_bits)
+        x = self.module(x).to(dt)
+        if self.quantize_output:
+            x = fake_quant(x, self.act_quant_name, self.group_size, self.n_bits)
+        return x
+
+
+def replace_linears(module, factory, exclude=()):
+    """Swap every nn.Linear below ``module`` for ``factory(linear)`` (walk of
+    RTN_quantization/utils.py:33-61)."""
+    for name, child in module.named_children():
+        if isinstance(child, nn.Linear) and name not in exclude:
+            setattr(module, name, factory(child))
+        else:
+            replace_linears(child, factory, exclude)
+    return module

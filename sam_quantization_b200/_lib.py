@@ -72,14 +72,14 @@ def load() -> ctypes.CDLL:
     lib.samq_act_quant_i8.argtypes = [
         c_void_p, c_int, c_int64, c_int64, c_int64,      # x, dtype, M, K, ldx
         c_void_p, POINTER(HadamardSpec),                 # divisor, had
-        c_int, c_int,                                    # granularity, group_size
+        c_int, c_int, c_int,                             # granularity, group_size, n_bits
         c_void_p, c_void_p, c_void_p, c_void_p,          # q, scale, fq, tx
         c_void_p, c_size_t, c_void_p,                    # workspace, bytes, stream
     ]
     lib.samq_weight_quant_i8.restype = c_int
     lib.samq_weight_quant_i8.argtypes = [
         c_void_p, c_int, c_int64, c_int64, c_int64,
-        c_int, c_int,
+        c_int, c_int, c_int,
         c_void_p, c_void_p, c_void_p,
         c_void_p, c_size_t, c_void_p,
     ]

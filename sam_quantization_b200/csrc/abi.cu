@@ -20,7 +20,7 @@ int fail(int code, const char* fmt, ...) {
 
 int act_quant_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
                        const void* divisor, const samq_hadamard_spec* had,
-                       int gran, int group_size, int8_t* q, float* scale, void* fq, void* tx,
+                       int gran, int group_size, int n_bits, int8_t* q, float* scale, void* fq, void* tx,
                        void* workspace, size_t workspace_bytes, void* stream);
 
 int gemm_i8_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
@@ -49,20 +49,20 @@ size_t samq_quant_workspace_bytes(int granularity) {
 
 int samq_act_quant_i8(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
                       const void* divisor, const samq_hadamard_spec* had,
-                      int granularity, int group_size,
+                      int granularity, int group_size, int n_bits,
                       int8_t* q_out, float* scale_out, void* fq_out, void* tx_out,
                       void* workspace, size_t workspace_bytes, void* stream)
 {
-    return samq::act_quant_dispatch(x, dtype, M, K, ldx, divisor, had, granularity, group_size,
+    return samq::act_quant_dispatch(x, dtype, M, K, ldx, divisor, had, granularity, group_size, n_bits,
                                     q_out, scale_out, fq_out, tx_out, workspace, workspace_bytes, stream);
 }
 
 int samq_weight_quant_i8(const void* w, int dtype, int64_t N, int64_t K, int64_t ldw,
-                         int granularity, int group_size,
+                         int granularity, int group_size, int n_bits,
                          int8_t* q_out, float* scale_out, void* fq_out,
                          void* workspace, size_t workspace_bytes, void* stream)
 {
-    return samq::act_quant_dispatch(w, dtype, N, K, ldw, nullptr, nullptr, granularity, group_size,
+    return samq::act_quant_dispatch(w, dtype, N, K, ldw, nullptr, nullptr, granularity, group_size, n_bits,
                                     q_out, scale_out, fq_out, nullptr, workspace, workspace_bytes, stream);
 }
 

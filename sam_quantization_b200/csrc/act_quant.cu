@@ -70,22 +70,22 @@ template <> struct PackedCodes<8> { typedef uint2 type; };
 template <> struct PackedCodes<4> { typedef uint32_t type; };
 
 template <int N>
-__device__ __forceinline__ typename PackedCodes<N>::type pack_codes(const float (&q)[N]);
-template <> __device__ __forceinline__ uint2 pack_codes<8>(const float (&q)[8]) {
+__device__ __forceinline__ typename PackedCodes<N>::type pack_codes(const float (&q)[N], float qmax);
+template <> __device__ __forceinline__ uint2 pack_codes<8>(const float (&q)[8], float qmax) {
     uint32_t w[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         uint32_t v = 0;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v |= (uint32_t)(uint8_t)saturate_i8(q[4 * h + i]) << (8 * i);
+        for (int i = 0; i < 4; ++i) v |= (uint32_t)(uint8_t)saturate_i8(q[4 * h + i], qmax) << (8 * i);
         w[h] = v;
     }
     return make_uint2(w[0], w[1]);
 }
-template <> __device__ __forceinline__ uint32_t pack_codes<4>(const float (&q)[4]) {
+template <> __device__ __forceinline__ uint32_t pack_codes<4>(const float (&q)[4], float qmax) {
     uint32_t v = 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) v |= (uint32_t)(uint8_t)saturate_i8(q[i]) << (8 * i);
+    for (int i = 0; i < 4; ++i) v |= (uint32_t)(uint8_t)saturate_i8(q[i], qmax) << (8 * i);
     return v;
 }
 
@@ -99,7 +99,7 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(256)
 quant_rows_vec_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
                       const T* __restrict__ divisor, int gran, int lanes_per_group,
-                      const float* __restrict__ tensor_absmax,
+                      const float* __restrict__ tensor_absmax, float qmax,
                       int8_t* __restrict__ q_out, float* __restrict__ scale_out,
                       T* __restrict__ fq_out, T* __restrict__ tx_out)
 {
@@ -143,10 +143,10 @@ quant_rows_vec_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
 #pragma unroll
         for (int i = 0; i < NV; ++i) m = fmaxf(m, vmax[i]);
         m = warp_max(m);
-        row_scale = scale_from_absmax<T>(m);
+        row_scale = scale_from_absmax<T>(m, qmax);
         if (lane == 0 && scale_out != nullptr) scale_out[row] = row_scale;
     } else if (gran == SAMQ_GRAN_TENSOR) {
-        row_scale = scale_from_absmax<T>(*tensor_absmax);
+        row_scale = scale_from_absmax<T>(*tensor_absmax, qmax);
         if (row == 0 && lane == 0 && scale_out != nullptr) scale_out[0] = row_scale;
     }
 
@@ -159,7 +159,7 @@ quant_rows_vec_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
             float m = vmax[i];
             for (int o = lanes_per_group >> 1; o > 0; o >>= 1)
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            s = scale_from_absmax<T>(m);
+            s = scale_from_absmax<T>(m, qmax);
             if (v < nvec && (lane & (lanes_per_group - 1)) == 0 && scale_out != nullptr)
                 scale_out[row * groups_per_row + v / lanes_per_group] = s;
         }
@@ -169,7 +169,7 @@ quant_rows_vec_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
 #pragma unroll
         for (int e = 0; e < E; ++e) q[e] = quant_value<T>(f[e], s);
         if (q_out != nullptr)
-            *reinterpret_cast<typename PackedCodes<E>::type*>(q_out + row * K + (int64_t)v * E) = pack_codes<E>(q);
+            *reinterpret_cast<typename PackedCodes<E>::type*>(q_out + row * K + (int64_t)v * E) = pack_codes<E>(q, qmax);
         if (tx_out != nullptr)
             *reinterpret_cast<uint4*>(tx_out + row * K + (int64_t)v * E) = raw[i];
         if (fq_out != nullptr) {
@@ -189,7 +189,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 quant_rows_generic_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
                           const T* __restrict__ divisor, int gran, int group_size,
-                          const float* __restrict__ tensor_absmax,
+                          const float* __restrict__ tensor_absmax, float qmax,
                           int8_t* __restrict__ q_out, float* __restrict__ scale_out,
                           T* __restrict__ fq_out, T* __restrict__ tx_out)
 {
@@ -204,7 +204,7 @@ quant_rows_generic_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx
 
     float s;
     if (gran == SAMQ_GRAN_TENSOR) {
-        s = scale_from_absmax<T>(*tensor_absmax);
+        s = scale_from_absmax<T>(*tensor_absmax, qmax);
         if (unit == 0 && lane == 0 && scale_out != nullptr) scale_out[0] = s;
     } else {
         float m = 0.f;
@@ -214,14 +214,14 @@ quant_rows_generic_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx
             m = fmaxf(m, fabsf(v));
         }
         m = warp_max(m);
-        s = scale_from_absmax<T>(m);
+        s = scale_from_absmax<T>(m, qmax);
         if (lane == 0 && scale_out != nullptr) scale_out[unit] = s;
     }
     for (int c = c0 + lane; c < c0 + span; c += 32) {
         float v = Elem<T>::up(xr[c]);
         if (divisor != nullptr) v = round_to<T>(__fdiv_rn(v, Elem<T>::up(divisor[c])));
         const float q = quant_value<T>(v, s);
-        if (q_out != nullptr) q_out[row * K + c] = saturate_i8(q);
+        if (q_out != nullptr) q_out[row * K + c] = saturate_i8(q, qmax);
         if (tx_out != nullptr) tx_out[row * K + c] = Elem<T>::down(v);
         if (fq_out != nullptr) fq_out[row * K + c] = Elem<T>::down(q * s);
     }
@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(1024)
 hadamard_quant_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
                       const T* __restrict__ divisor, const int8_t* __restrict__ signs,
                       int inner, int axis, int had_k, int log2_pow,
-                      const float* __restrict__ hadk,
+                      const float* __restrict__ hadk, float qmax,
                       int8_t* __restrict__ q_out, float* __restrict__ scale_out,
                       T* __restrict__ fq_out, T* __restrict__ tx_out)
 {
@@ -367,14 +367,14 @@ hadamard_quant_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
         if (tid == 0) red[0] = t;
     }
     __syncthreads();
-    const float s = scale_from_absmax<T>(red[0]);
+    const float s = scale_from_absmax<T>(red[0], qmax);
     if (tid == 0 && scale_out != nullptr) scale_out[row] = s;
 
     // (e) quantize and store
     for (int c = tid; c < K; c += nthr) {
         const float v = sm[padded(c)];
         const float q = quant_value<T>(v, s);
-        if (q_out != nullptr) q_out[row * K + c] = saturate_i8(q);
+        if (q_out != nullptr) q_out[row * K + c] = saturate_i8(q, qmax);
         if (tx_out != nullptr) tx_out[row * K + c] = Elem<T>::down(v);
         if (fq_out != nullptr) fq_out[row * K + c] = Elem<T>::down(q * s);
     }
@@ -387,7 +387,7 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 template <typename T>
 static int launch_rows(const T* x, int64_t M, int K, int64_t ldx, const T* divisor,
-                       int gran, int group_size, const float* tensor_absmax,
+                       int gran, int group_size, const float* tensor_absmax, float qmax,
                        int8_t* q, float* scale, T* fq, T* tx, cudaStream_t st)
 {
     constexpr int E = Elem<T>::kPerVec;
@@ -405,7 +405,7 @@ static int launch_rows(const T* x, int64_t M, int K, int64_t ldx, const T* divis
         dim3 grid((unsigned)((M + warps - 1) / warps)), block(warps * 32);
 #define SAMQ_LAUNCH_NV(NVAL)                                                               \
         quant_rows_vec_kernel<T, NVAL><<<grid, block, 0, st>>>(x, M, K, ldx, divisor, gran, \
-            lanes_per_group, tensor_absmax, q, scale, fq, tx)
+            lanes_per_group, tensor_absmax, qmax, q, scale, fq, tx)
         if (nv <= 1) SAMQ_LAUNCH_NV(1);
         else if (nv <= 2) SAMQ_LAUNCH_NV(2);
         else if (nv <= 3) SAMQ_LAUNCH_NV(3);
@@ -425,7 +425,7 @@ static int launch_rows(const T* x, int64_t M, int K, int64_t ldx, const T* divis
         const int warps = 8;
         dim3 grid((unsigned)((units + warps - 1) / warps)), block(warps * 32);
         quant_rows_generic_kernel<T><<<grid, block, 0, st>>>(x, M, K, ldx, divisor, gran, group_size,
-                                                             tensor_absmax, q, scale, fq, tx);
+                                                             tensor_absmax, qmax, q, scale, fq, tx);
     }
     SAMQ_CUDA_TRY(cudaGetLastError());
     return SAMQ_OK;
@@ -433,7 +433,7 @@ static int launch_rows(const T* x, int64_t M, int K, int64_t ldx, const T* divis
 
 template <typename T>
 static int quant_typed(const T* x, int64_t M, int K, int64_t ldx, const T* divisor,
-                       const samq_hadamard_spec* had, int gran, int group_size,
+                       const samq_hadamard_spec* had, int gran, int group_size, float qmax,
                        int8_t* q, float* scale, T* fq, T* tx,
                        void* workspace, size_t workspace_bytes, cudaStream_t st)
 {
@@ -465,7 +465,7 @@ static int quant_typed(const T* x, int64_t M, int K, int64_t ldx, const T* divis
         int threads = ((K / 16 + 31) / 32) * 32;
         threads = threads < 32 ? 32 : (threads > 1024 ? 1024 : threads);
         hadamard_quant_kernel<T><<<(unsigned)M, threads, smem, st>>>(x, M, K, ldx, divisor, had->signs,
-            inner, axis, hk, log2_pow, had->hadk, q, scale, fq, tx);
+            inner, axis, hk, log2_pow, had->hadk, qmax, q, scale, fq, tx);
         SAMQ_CUDA_TRY(cudaGetLastError());
         return SAMQ_OK;
     }
@@ -487,14 +487,16 @@ static int quant_typed(const T* x, int64_t M, int K, int64_t ldx, const T* divis
     } else if (gran != SAMQ_GRAN_ROW) {
         return fail(SAMQ_ERR_BAD_ARG, "unknown granularity %d", gran);
     }
-    return launch_rows<T>(x, M, K, ldx, divisor, gran, group_size, tensor_absmax, q, scale, fq, tx, st);
+    return launch_rows<T>(x, M, K, ldx, divisor, gran, group_size, tensor_absmax, qmax, q, scale, fq, tx, st);
 }
 
 int act_quant_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
                        const void* divisor, const samq_hadamard_spec* had,
-                       int gran, int group_size, int8_t* q, float* scale, void* fq, void* tx,
+                       int gran, int group_size, int n_bits, int8_t* q, float* scale, void* fq, void* tx,
                        void* workspace, size_t workspace_bytes, void* stream)
 {
+    if (n_bits < 2 || n_bits > 8) return fail(SAMQ_ERR_UNSUPPORTED, "n_bits=%d: int8 codes hold 2..8 bits", n_bits);
+    const float qmax = (float)((1 << (n_bits - 1)) - 1);
     if (M < 0 || K <= 0 || ldx < K) return fail(SAMQ_ERR_BAD_ARG, "bad shape M=%lld K=%lld ldx=%lld",
                                                 (long long)M, (long long)K, (long long)ldx);
     if (M > 0 && x == nullptr) return fail(SAMQ_ERR_BAD_ARG, "x is null");
@@ -503,14 +505,14 @@ int act_quant_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t l
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dtype) {
     case SAMQ_F16:
-        return quant_typed<__half>((const __half*)x, M, (int)K, ldx, (const __half*)divisor, had, gran, group_size,
+        return quant_typed<__half>((const __half*)x, M, (int)K, ldx, (const __half*)divisor, had, gran, group_size, qmax,
                                    q, scale, (__half*)fq, (__half*)tx, workspace, workspace_bytes, st);
     case SAMQ_BF16:
         return quant_typed<__nv_bfloat16>((const __nv_bfloat16*)x, M, (int)K, ldx, (const __nv_bfloat16*)divisor, had,
-                                          gran, group_size, q, scale, (__nv_bfloat16*)fq, (__nv_bfloat16*)tx,
+                                          gran, group_size, qmax, q, scale, (__nv_bfloat16*)fq, (__nv_bfloat16*)tx,
                                           workspace, workspace_bytes, st);
     case SAMQ_F32:
-        return quant_typed<float>((const float*)x, M, (int)K, ldx, (const float*)divisor, had, gran, group_size,
+        return quant_typed<float>((const float*)x, M, (int)K, ldx, (const float*)divisor, had, gran, group_size, qmax,
                                   q, scale, (float*)fq, (float*)tx, workspace, workspace_bytes, st);
     default:
         return fail(SAMQ_ERR_BAD_ARG, "unknown dtype %d", dtype);

@@ -47,13 +47,13 @@ template <typename T>
 __device__ __forceinline__ float round_to(float v) { return Elem<T>::up(Elem<T>::down(v)); }
 
 // The reference clamps the absolute maximum with `clamp_(min=1e-5)` in the
-// tensor dtype and divides by 127 in that dtype
+// tensor dtype and divides by q_max = 2^(n_bits-1)-1 in that dtype
 // (RTN_quantization/per_tensor_channel_group.py:57-59).
 template <typename T>
-__device__ __forceinline__ float scale_from_absmax(float absmax) {
+__device__ __forceinline__ float scale_from_absmax(float absmax, float qmax) {
     const float floor_t = round_to<T>(1e-5f);
     float a = fmaxf(absmax, floor_t);
-    return round_to<T>(__fdiv_rn(a, 127.0f));
+    return round_to<T>(__fdiv_rn(a, qmax));
 }
 
 // q = round_half_even( T(x / s) ) as a float holding an integer value
@@ -63,8 +63,8 @@ __device__ __forceinline__ float quant_value(float x, float s) {
     return rintf(round_to<T>(__fdiv_rn(x, s)));
 }
 
-__device__ __forceinline__ int8_t saturate_i8(float q) {
-    q = fminf(fmaxf(q, -127.0f), 127.0f);
+__device__ __forceinline__ int8_t saturate_i8(float q, float qmax) {
+    q = fminf(fmaxf(q, -qmax), qmax);
     return (int8_t)(int)q;
 }
 

@@ -56,6 +56,61 @@ def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
 
 _status_words = {}
 
+# ---- launch accounting and optional per-kernel timing (used by bench.py) -----------------------
+_launches = 0
+_timing_on = False
+_timing_records = []          # (kind, start_event, end_event, work)
+
+
+def reset_counters() -> None:
+    global _launches
+    _launches = 0
+
+
+def launch_count() -> int:
+    """CUDA kernels of this library launched since ``reset_counters()``."""
+    return _launches
+
+
+def enable_kernel_timing(on: bool) -> None:
+    """Bracket every C-ABI launch with CUDA events on the launching stream."""
+    global _timing_on
+    _timing_on = bool(on)
+    _timing_records.clear()
+
+
+def kernel_timing_summary() -> dict:
+    """{kind: {"ms", "launches", "ops" | "bytes"}} summed over the bracketed launches
+    (synchronises).  ``ops`` = 2*M*N*K per GEMM, ``bytes`` = the algorithmic M*(in+1)*K+4M of K1."""
+    torch.cuda.synchronize()
+    out = {}
+    for kind, e0, e1, work in _timing_records:
+        d = out.setdefault(kind, {"ms": 0.0, "launches": 0, "ops": 0.0, "bytes": 0.0})
+        d["ms"] += e0.elapsed_time(e1)
+        d["launches"] += 1
+        d["ops" if kind == "gemm_i8" else "bytes"] += work
+    return out
+
+
+class _Timed:
+    def __init__(self, kind, work, kernels=1):
+        self.kind, self.work, self.kernels = kind, work, kernels
+
+    def __enter__(self):
+        global _launches
+        _launches += self.kernels
+        if _timing_on:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e1 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if _timing_on:
+            self.e1.record()
+            _timing_records.append((self.kind, self.e0, self.e1, self.work))
+        return False
+
 
 def status_word(device: torch.device) -> torch.Tensor:
     """Per-device int32 that GEMM kernels raise when one of their bounded waits ran out."""
@@ -107,7 +162,7 @@ def _spec(had: Optional[Hadamard], keep: list) -> Optional[HadamardSpec]:
 
 def quantize(x: torch.Tensor, granularity: int = GRAN_ROW, group_size: Optional[int] = None,
              divisor: Optional[torch.Tensor] = None, hadamard: Optional[Hadamard] = None,
-             codes: bool = True, fake_quant: bool = False, transformed: bool = False):
+             codes: bool = True, fake_quant: bool = False, transformed: bool = False, n_bits: int = 8):
     """Run K1 on ``x`` ([..., K]; fp16 / bf16 / fp32).
 
     Returns a dict with the requested outputs: ``q`` int8 [..., K], ``scale`` fp32
@@ -145,11 +200,13 @@ def quantize(x: torch.Tensor, granularity: int = GRAN_ROW, group_size: Optional[
         if divisor.numel() != K:
             raise ValueError("divisor must have K elements")
     spec = _spec(hadamard, keep)
-    with torch.cuda.device(dev):
+    nbytes = M * (K * x.element_size() + (K if codes else 0) + (K * x.element_size() if fake_quant else 0)
+                  + (K * x.element_size() if transformed else 0)) + scale.numel() * 4
+    with torch.cuda.device(dev), _Timed("act_quant", nbytes, 3 if granularity == GRAN_TENSOR else 1):
         _lib.check(lib.samq_act_quant_i8(
             _ptr(x2), _DTYPE_CODE[x.dtype], M, K, ldx, _ptr(divisor),
             ctypes.byref(spec) if spec is not None else None,
-            granularity, g, _ptr(q), _ptr(scale), _ptr(fq), _ptr(tx),
+            granularity, g, int(n_bits), _ptr(q), _ptr(scale), _ptr(fq), _ptr(tx),
             _ptr(ws), ws_bytes, _stream()))
     if codes:
         out["q"] = q.view(*lead, K)
@@ -167,7 +224,7 @@ def quantize(x: torch.Tensor, granularity: int = GRAN_ROW, group_size: Optional[
 
 
 def quantize_weight(w: torch.Tensor, granularity: int = GRAN_ROW, group_size: Optional[int] = None,
-                    codes: bool = True, fake_quant: bool = False):
+                    codes: bool = True, fake_quant: bool = False, n_bits: int = 8):
     """Run K3 (weight quantization) on ``w`` [N, K] through ``samq_weight_quant_i8``."""
     _require_cuda(w, "w")
     if w.dim() != 2:
@@ -189,9 +246,9 @@ def quantize_weight(w: torch.Tensor, granularity: int = GRAN_ROW, group_size: Op
     fq = torch.empty((N, K), dtype=w.dtype, device=dev) if fake_quant else None
     ws_bytes = int(lib.samq_quant_workspace_bytes(granularity))
     ws = torch.empty((max(ws_bytes, 4) // 4,), dtype=torch.int32, device=dev) if ws_bytes else None
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _Timed("weight_quant", N * K * (w.element_size() + 1), 3 if granularity == GRAN_TENSOR else 1):
         _lib.check(lib.samq_weight_quant_i8(
-            _ptr(w2), _DTYPE_CODE[w.dtype], N, K, ldw, granularity, g,
+            _ptr(w2), _DTYPE_CODE[w.dtype], N, K, ldw, granularity, g, int(n_bits),
             _ptr(q), _ptr(scale), _ptr(fq), _ptr(ws), ws_bytes, _stream()))
     out = {"scale": scale}
     if codes:
@@ -244,7 +301,7 @@ def gemm_i8(a_q: torch.Tensor, w_q: torch.Tensor,
         a_scale = a_scale.to(device=dev, dtype=torch.float32).contiguous()
     if w_scale is not None:
         w_scale = w_scale.to(device=dev, dtype=torch.float32).contiguous()
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _Timed("gemm_i8", 2.0 * M * N * K):
         _lib.check(lib.samq_gemm_i8(
             _ptr(a2), lda, _ptr(w2), ldw, M, N, K,
             _ptr(a_scale), a_gran, _ptr(w_scale), w_gran, int(group_size or 0),

@@ -186,6 +186,41 @@ def config1_case(ptcg, Smooth):
     return out
 
 
+TINY = dict(model_type="vit_b", img_size=224, window_size=4, embed_dim=64, depth=3, num_heads=4,
+            global_attn_indexes=(2,), out_chans=32)
+
+
+def tiny_images(seed=7, n=2, size=224):
+    g = torch.Generator().manual_seed(seed)
+    img = torch.rand(n, 3, size, size, generator=g)
+    mean = torch.tensor([0.485, 0.456, 0.406]).view(1, 3, 1, 1)
+    std = torch.tensor([0.229, 0.224, 0.225]).view(1, 3, 1, 1)
+    return (img - mean) / std
+
+
+def encoder_case(ptcg):
+    """A small encoder of this repository's architecture (14x14 tokens, window 4 -> padded to 16,
+    one global block) whose Linears are replaced by the reference's own W8A8Linear, fp32 on CPU.
+    Stores the embeddings for two quantization settings."""
+    repo = os.path.dirname(os.path.dirname(HERE))
+    sys.path.insert(0, repo)
+    from sam_quantization_b200.sam_encoder import build_encoder
+    from oracle.torch_twin import replace_linears
+    out = {}
+    for tag, kw in (("w8a8", dict(weight_quant="per_channel", act_quant="per_token", quantize_output=False)),
+                    ("w8a8_qout", dict(weight_quant="per_channel", act_quant="per_token", quantize_output=True)),
+                    ("w8a8_tensor", dict(weight_quant="per_tensor", act_quant="per_tensor", quantize_output=False))):
+        model = build_encoder(seed=5, dtype=torch.float32, attn_dtype=None, **TINY)
+        replace_linears(model, lambda lin: ptcg.W8A8Linear.from_float(lin, 8, **kw))
+        with torch.no_grad():
+            emb = model(tiny_images())
+        out[f"{tag}/embedding"] = emb.numpy().astype(np.float32)
+    model = build_encoder(seed=5, dtype=torch.float32, attn_dtype=None, **TINY)
+    with torch.no_grad():
+        out["float/embedding"] = model(tiny_images()).numpy().astype(np.float32)
+    return out
+
+
 def main():
     root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     ptcg, Smooth, H = _import_reference(root)
@@ -195,6 +230,7 @@ def main():
     np.savez_compressed(os.path.join(HERE, "smooth.npz"), **smooth_cases(Smooth))
     np.savez_compressed(os.path.join(HERE, "hadamard.npz"), **hadamard_cases(H))
     np.savez_compressed(os.path.join(HERE, "config1.npz"), **config1_case(ptcg, Smooth))
+    np.savez_compressed(os.path.join(HERE, "encoder_tiny.npz"), **encoder_case(ptcg))
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -1,0 +1,242 @@
+"""The reference-facing Python surface on the GPU: W8A8Linear, the six quantizer functions,
+replace_linear_with_target_and_quantize, SmoothQuant folding, ActQuantWrapper / rotate_sam, and
+the encoder against its float twin driven through the reference's arithmetic."""
+import copy
+import types
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from oracle.torch_twin import RefActQuantWrapper, RefW8A8Linear, replace_linears
+from tests.golden.make_golden import TINY, tiny_images
+
+pytestmark = pytest.mark.gpu
+TDT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+
+
+def cosine(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float(a @ b / (a.norm() * b.norm()))
+
+
+def rel_err(a, b):
+    return float((a.double() - b.double()).abs().max() / b.double().abs().max())
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16", "f32"])
+def test_w8a8linear_against_reference_outputs(cuda_device, golden, dt):
+    from sam_quantization_b200.RTN_quantization import W8A8Linear
+    g = golden("w8a8_linear")
+    dev = cuda_device
+    x = torch.from_numpy(g[f"{dt}/x"]).to(TDT[dt]).to(dev)
+    for wq, aq, gs, qo in [("per_channel", "per_token", None, 0), ("per_tensor", "per_tensor", None, 0),
+                           ("per_channel", "per_token", None, 1)]:
+        lin = torch.nn.Linear(256, 72).to(dev)
+        lin.weight.data = torch.from_numpy(g[f"{dt}/w"]).to(TDT[dt]).to(dev)
+        lin.bias.data = torch.from_numpy(g[f"{dt}/b"]).to(TDT[dt]).to(dev)
+        m = W8A8Linear.from_float(lin, 8, weight_quant=wq, act_quant=aq, quantize_output=bool(qo), group_size=gs)
+        y = m(x.clone())
+        want = torch.from_numpy(g[f"{dt}/y/{wq}/{aq}/{gs}/{qo}"])
+        assert y.dtype == TDT[dt] and y.shape == want.shape
+        assert rel_err(y.float().cpu(), want) < 1e-2, (wq, aq, qo)
+        # the source Linear now holds the fake-quantized weight; m.weight (codes * scale) equals it
+        # bit for bit except where bf16's short mantissa let the reference's quotient reach 128,
+        # which an int8 code saturates to 127
+        if dt == "bf16":
+            assert (lin.weight.data != m.weight).float().mean() < 0.02
+        else:
+            assert torch.equal(lin.weight.data, m.weight)
+    assert repr(m) == str(g[f"{dt}/repr"]).replace("weight_quant=per_group", "weight_quant=per_channel").replace(
+        "act_quant=per_token, output_quant=None", "act_quant=per_token, output_quant=per_token")
+
+
+def test_w8a8linear_errors_and_shapes(cuda_device):
+    from sam_quantization_b200.RTN_quantization import W8A8Linear
+    lin = torch.nn.Linear(64, 32).half().to(cuda_device)
+    with pytest.raises(ValueError):
+        W8A8Linear.from_float(lin, 8, weight_quant="per_row")
+    with pytest.raises(ValueError):
+        W8A8Linear.from_float(lin, 8, act_quant="per_row")
+    m = W8A8Linear.from_float(lin, 8)
+    y = m(torch.randn(2, 5, 7, 64, device=cuda_device, dtype=torch.float16))
+    assert y.shape == (2, 5, 7, 32)
+    assert m(torch.zeros(0, 64, device=cuda_device, dtype=torch.float16)).shape == (0, 32)
+
+
+def test_six_quantizer_functions_in_place(cuda_device, golden):
+    from sam_quantization_b200.RTN_quantization import per_tensor_channel_group as P
+    g = golden("quantizers")
+    for dt in ("f16", "bf16", "f32"):
+        x = torch.from_numpy(g[f"{dt}/x"]).to(TDT[dt]).to(cuda_device)
+        w = torch.from_numpy(g[f"{dt}/w"]).to(TDT[dt]).to(cuda_device)
+        for fn, arg, key, extra in [
+                (P.quantize_activation_per_token_absmax, x, "act_per_token", ()),
+                (P.quantize_activation_per_tensor_absmax, x, "act_per_tensor", ()),
+                (P.quantize_activation_per_group_absmax_token_dim, x, "act_per_group32", (32,)),
+                (P.quantize_weight_per_channel_absmax, w, "w_per_channel", ()),
+                (P.quantize_weight_per_tensor_absmax, w, "w_per_tensor", ()),
+                (P.quantize_weight_per_group_absmax_input_features, w, "w_per_group32", (32,))]:
+            t = arg.clone()
+            r = fn(t, *extra)
+            assert r is t                                              # in place, like the reference
+            assert np.array_equal(t.float().cpu().numpy(), g[f"{dt}/{key}"]), (dt, key)
+
+
+def test_four_bit_codes_in_int8_container(cuda_device):
+    """n_bits=4 (what most of the reference's YAMLs set): q_max = 7, codes still feed the int8 GEMM."""
+    from sam_quantization_b200.RTN_quantization import per_tensor_channel_group as P
+    from oracle.torch_twin import fq_rows
+    x = torch.randn(33, 256, device=cuda_device, dtype=torch.float16)
+    want = fq_rows(x.clone(), 4)
+    q, s = P.quantize_activation_codes(x, "per_token", n_bits=4)
+    assert int(q.abs().max()) <= 7
+    got = P.quantize_activation_per_token_absmax(x.clone(), n_bits=4)
+    assert torch.equal(got, want)
+
+
+def test_replace_linear_walk(cuda_device):
+    from sam_quantization_b200.RTN_quantization import W8A8Linear, replace_linear_with_target_and_quantize
+
+    class Inner(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc = torch.nn.Linear(32, 32)
+            self.lm_head = torch.nn.Linear(32, 16)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = torch.nn.Embedding(10, 32)
+            self.a = torch.nn.Linear(32, 32)
+            self.lm_head = Inner()
+
+    net = Net().half().to(cuda_device)
+    replace_linear_with_target_and_quantize(net, W8A8Linear, 8, ["lm_head"])
+    assert isinstance(net.a, W8A8Linear)
+    assert isinstance(net.lm_head.fc, W8A8Linear)                  # excluded containers are still visited
+    assert isinstance(net.lm_head.lm_head, torch.nn.Linear)        # exact child-name match is skipped
+    assert isinstance(net.emb, torch.nn.Embedding)
+
+
+def test_smooth_ln_fcs_matches_reference(cuda_device, golden):
+    from sam_quantization_b200.RTN_quantization import smooth_ln_fcs
+    g = golden("smooth")
+    for dt in ("f16", "f32"):
+        C = 64
+        ln = torch.nn.LayerNorm(C).to(cuda_device)
+        ln.weight.data = torch.from_numpy(g[f"{dt}/ln_w"]).to(TDT[dt]).to(cuda_device)
+        ln.bias.data = torch.from_numpy(g[f"{dt}/ln_b"]).to(TDT[dt]).to(cuda_device)
+        fc1, fc2 = torch.nn.Linear(C, 96).to(cuda_device), torch.nn.Linear(C, 32).to(cuda_device)
+        fc1.weight.data = torch.from_numpy(g[f"{dt}/fc1_w"]).to(TDT[dt]).to(cuda_device)
+        fc2.weight.data = torch.from_numpy(g[f"{dt}/fc2_w"]).to(TDT[dt]).to(cuda_device)
+        smooth_ln_fcs(ln, [fc1, fc2], torch.from_numpy(g[f"{dt}/act_scales"]), alpha=0.5)
+        for got, key in ((ln.weight, "ln_w_s"), (ln.bias, "ln_b_s"), (fc1.weight, "fc1_w_s"), (fc2.weight, "fc2_w_s")):
+            want = torch.from_numpy(g[f"{dt}/{key}"])
+            # CUDA pow() may differ from the CPU's by an ulp of the dtype
+            tol = 2e-3 if dt == "f16" else 1e-6
+            assert rel_err(got.float().cpu(), want) <= tol, (dt, key)
+
+
+def test_hadamard_tables_and_offline_transform(cuda_device, golden):
+    from sam_quantization_b200.quarot import hadamard_utils as H
+    g = golden("hadamard")
+    assert np.array_equal(H.get_had12().numpy().astype(np.int8), g["had12"])
+    assert np.array_equal(H.get_had20().numpy().astype(np.int8), g["had20"])
+    assert np.array_equal(H.get_had40().numpy().astype(np.int8), g["had40"])
+    for n in (768, 1024, 1280, 3072, 4096, 5120, 12, 16, 64):
+        assert H.get_hadK(n)[1] == int(g[f"hadK_of/{n}"])
+    for n in (16, 64, 256, 1024, 4096):
+        x = torch.from_numpy(g[f"hadU/{n}/x"])
+        assert np.array_equal(H.matmul_hadU(x).numpy(), g[f"hadU/{n}/y"])
+        y = H.matmul_hadU_cuda(x.half().to(cuda_device), None, 1)
+        assert np.array_equal(y.float().cpu().numpy(), g[f"hadU/{n}/y_f16_via_f32"])
+    for n in (64, 1024):
+        Q = H.random_hadamard_matrix(n, "cpu", 123)
+        assert np.array_equal(Q[0].numpy(), g[f"randhad/{n}/row0"])
+        assert np.array_equal(H.random_hadamard_signs(n, 123).numpy(), g[f"randhad/{n}/signs"])
+
+
+def _tiny_pair(dev, dtype, attn_dtype, seed=5):
+    from sam_quantization_b200.sam_encoder import build_encoder
+    mine = build_encoder(seed=seed, dtype=dtype, attn_dtype=attn_dtype, device=dev, **TINY)
+    twin = copy.deepcopy(mine)
+    return mine, twin
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_tiny_encoder_rtn_vs_twin_and_reference(cuda_device, golden, dtype):
+    """W8A8 on all linears: the CUDA engine against the float twin running the reference's
+    fake-quant arithmetic on the same weights (cosine >= 0.999), and against the embeddings the
+    reference's own W8A8Linear produced on the CPU (fixture)."""
+    from sam_quantization_b200.RTN_quantization import W8A8Linear, replace_linear_with_target_and_quantize
+    dev = cuda_device
+    mine, twin = _tiny_pair(dev, dtype, None)
+    replace_linear_with_target_and_quantize(mine, W8A8Linear, 8, [])
+    replace_linears(twin, lambda lin: RefW8A8Linear.from_float(lin, 8))
+    img = tiny_images().to(dev, dtype)
+    with torch.no_grad():
+        a, b = mine(img), twin(img)
+    assert cosine(a, b) >= 0.999
+    want = torch.from_numpy(golden("encoder_tiny")["w8a8/embedding"])
+    assert cosine(a.float().cpu(), want) >= 0.999
+    assert rel_err(a.float().cpu(), want) < 5e-2
+
+
+def test_tiny_encoder_smoothquant(cuda_device):
+    from sam_quantization_b200.RTN_quantization import (W8A8Linear, get_act_scales_sam,
+                                                        replace_linear_with_target_and_quantize, smooth_sam)
+    dev = cuda_device
+    mine, twin = _tiny_pair(dev, torch.float16, torch.bfloat16)
+    calib = [tiny_images(seed=200 + i).to(dev, torch.float16) for i in range(3)]
+    scales = get_act_scales_sam(mine, calib)
+    assert set(k.split(".")[-1] for k in scales) == {"qkv", "proj", "lin1", "lin2"}
+    smooth_sam(mine, scales, alpha=0.5)
+    smooth_sam(twin, scales, alpha=0.5)
+    assert torch.equal(mine.image_encoder.blocks[0].norm1.weight, twin.image_encoder.blocks[0].norm1.weight)
+    replace_linear_with_target_and_quantize(mine, W8A8Linear, 8, [])
+    replace_linears(twin, lambda lin: RefW8A8Linear.from_float(lin, 8))
+    img = tiny_images().to(dev, torch.float16)
+    with torch.no_grad():
+        assert cosine(mine(img), twin(img)) >= 0.999
+
+
+def test_tiny_encoder_quarot(cuda_device):
+    """rotate_sam on a power-of-two encoder (hidden 64, 4 heads): the fused engine against a twin
+    that applies the same recipe with the reference's dense x @ Q, pure-torch Hadamards and
+    fake-quant wrappers."""
+    from sam_quantization_b200.quarot import rotate_sam, utils as qutils, hadamard_utils as H
+    from sam_quantization_b200.quarot import rotation_utils
+    dev = cuda_device
+    mine, twin = _tiny_pair(dev, torch.float16, torch.bfloat16)
+    args = types.SimpleNamespace(hidden_size_image_en=64, num_attention_head_image_en=4, hidden_size_mask_de=256,
+                                 num_attention_head_mask_de=8, rotate_mode="hadamard", device=str(dev), seed=123,
+                                 fp32_had=True)
+    cfg = types.SimpleNamespace(n_bits=8, weight_quant="per_channel", act_quant="per_token", group_size=None,
+                                quantize_output=False, quantize_input=True)
+    float_model = copy.deepcopy(mine)
+    img = tiny_images().to(dev, torch.float16)
+    with torch.no_grad():
+        y_float = float_model(img)
+    # twin: same weight rotation (offline, shared code path is the package's torch/K1 transform),
+    # then reference-style wrappers and a dense online Q
+    Q = rotation_utils.get_orthogonal_matrix(64, "hadamard", device=str(dev), seed=123)
+    rotation_utils.rotate_model(twin, Q, None, args)
+    replace_linears(twin, lambda lin: RefActQuantWrapper(lin))
+    for name, layer in qutils.find_qlayers(twin, layers=(RefActQuantWrapper,)).items():
+        layer.quantize_input = True
+        if "lin2" in name:
+            layer.online_full_had = True
+        if "proj" in name:
+            layer.online_partial_had, layer.had_dim = True, 16
+    qlayers = rotate_sam(mine, args, cfg)
+    assert all(isinstance(v, qutils.ActQuantWrapper) for v in qlayers.values())
+    assert qlayers["image_encoder.blocks.0.mlp.lin2"].online_full_had
+    assert qlayers["image_encoder.blocks.0.attn.proj"].online_partial_had
+    assert qlayers["image_encoder.blocks.0.attn.proj"].had_dim == 16
+    with torch.no_grad():
+        a, b = mine(img), twin(img)
+    assert cosine(a, b) >= 0.999
+    # rotation is an exact change of basis: the quantized rotated model still tracks the float model
+    assert cosine(a, y_float) >= 0.99
