@@ -40,7 +40,9 @@ def test_w8a8linear_against_reference_outputs(cuda_device, golden, dt):
         y = m(x.clone())
         want = torch.from_numpy(g[f"{dt}/y/{wq}/{aq}/{gs}/{qo}"])
         assert y.dtype == TDT[dt] and y.shape == want.shape
-        assert rel_err(y.float().cpu(), want) < 1e-2, (wq, aq, qo)
+        # 1e-2 relative max-abs on dequantized layer outputs; when the output is fake-quantized
+        # again, one flipped rounding is a whole quantization step (max/127), so allow two steps
+        assert rel_err(y.float().cpu(), want) < (2e-2 if qo else 1e-2), (wq, aq, qo)
         # the source Linear now holds the fake-quantized weight; m.weight (codes * scale) equals it
         # bit for bit except where bf16's short mantissa let the reference's quotient reach 128,
         # which an int8 code saturates to 127
