@@ -145,6 +145,29 @@ int samq_weight_quant_i8(const void* w, int dtype, int64_t N, int64_t K, int64_t
                          int8_t* q_out, float* scale_out, void* fq_out,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* Per-tensor activation quantization that allocates nothing and takes no workspace.
+ *
+ * This entry point has no counterpart in the reference.  It exists for callers that cannot
+ * obtain device memory on the path that runs a layer — a plugin living inside a host process
+ * that pre-sized its arena, or code executing while the allocator must stay untouched — and
+ * therefore cannot supply the 256-byte workspace samq_act_quant_i8 wants for SAMQ_GRAN_TENSOR.
+ * The scratch (one partial maximum per 64 rows plus the reduced maximum, 16.4 KB) is a fixed
+ * array inside the library image; each GPU that loads the library holds it until exit.
+ *
+ * Same arithmetic and outputs as samq_act_quant_i8(..., SAMQ_GRAN_TENSOR, ...) without a
+ * divisor or Hadamard: q_out [M,K] int8 (or NULL), scale_out [1] fp32 (or NULL), fq_out [M,K]
+ * of `dtype` (or NULL).
+ *
+ * Limits and rules:
+ *  - at most 262144 rows (64 rows x 4096 scratch slots); larger M returns SAMQ_ERR_TOO_LARGE;
+ *  - the first call on each device looks up the array's device address (no allocation); make
+ *    that first call outside any stream capture;
+ *  - all calls on a device share the one array, which keeps what the previous call left there.
+ *    Nothing in it has to be zeroed (each call overwrites every slot it later reads), but two
+ *    calls that overlap on the GPU (different streams, no ordering) race on it: serialise them. */
+int samq_act_quant_per_tensor_static(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, int n_bits,
+                                     int8_t* q_out, float* scale_out, void* fq_out, void* stream);
+
 /* ---- K2: int8 GEMM with fused dequant epilogue ---------------------------
  *
  * Replaces `qgemm.matmul` + `qgemm.sym_dequant`

@@ -24,6 +24,7 @@ EXPORTED_SYMBOLS = (
     "samq_quant_workspace_bytes",
     "samq_act_quant_i8",
     "samq_weight_quant_i8",
+    "samq_act_quant_per_tensor_static",
     "samq_gemm_i8",
 )
 
@@ -82,6 +83,11 @@ def load() -> ctypes.CDLL:
         c_int, c_int, c_int,
         c_void_p, c_void_p, c_void_p,
         c_void_p, c_size_t, c_void_p,
+    ]
+    lib.samq_act_quant_per_tensor_static.restype = c_int
+    lib.samq_act_quant_per_tensor_static.argtypes = [
+        c_void_p, c_int, c_int64, c_int64, c_int64, c_int,   # x, dtype, M, K, ldx, n_bits
+        c_void_p, c_void_p, c_void_p, c_void_p,              # q, scale, fq, stream
     ]
     lib.samq_gemm_i8.restype = c_int
     lib.samq_gemm_i8.argtypes = [

@@ -23,6 +23,9 @@ int act_quant_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t l
                        int gran, int group_size, int n_bits, int8_t* q, float* scale, void* fq, void* tx,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+int act_quant_per_tensor_static_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, int n_bits,
+                                         int8_t* q, float* scale, void* fq, void* stream);
+
 int gemm_i8_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
                      int64_t M, int64_t N, int64_t K,
                      const float* a_scale, int a_gran, const float* w_scale, int w_gran, int group_size,
@@ -64,6 +67,12 @@ int samq_weight_quant_i8(const void* w, int dtype, int64_t N, int64_t K, int64_t
 {
     return samq::act_quant_dispatch(w, dtype, N, K, ldw, nullptr, nullptr, granularity, group_size, n_bits,
                                     q_out, scale_out, fq_out, nullptr, workspace, workspace_bytes, stream);
+}
+
+int samq_act_quant_per_tensor_static(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, int n_bits,
+                                     int8_t* q_out, float* scale_out, void* fq_out, void* stream)
+{
+    return samq::act_quant_per_tensor_static_dispatch(x, dtype, M, K, ldx, n_bits, q_out, scale_out, fq_out, stream);
 }
 
 int samq_gemm_i8(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,

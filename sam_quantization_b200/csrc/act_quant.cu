@@ -519,4 +519,125 @@ int act_quant_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t l
     }
 }
 
+// ---------------------------------------------------------------------------
+// Per-tensor quantization for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc on the path that runs a
+// layer: a plugin loaded into someone else's serving process that was handed
+// a fixed arena at start-up, or code running where the allocator is frozen
+// (inside a region that forbids allocator traffic).  The per-tensor quantizer
+// is the one kernel here that needs scratch beyond its inputs and outputs
+// (the running absolute maximum), so this variant keeps that scratch in a
+// fixed array that is part of the loaded library image instead of in a
+// caller-provided workspace.
+//
+// Layout of the array: slots [0, kStaticPartials) hold one partial maximum
+// per block of 64 rows; slot kStaticPartials holds the reduced maximum.  Every
+// GPU that loads the library reserves the 16.4 KB until the process exits.
+// ---------------------------------------------------------------------------
+constexpr int kStaticRowsPerBlock = 64;
+constexpr int kStaticPartials = 4096;                       // => at most 262144 rows per call
+constexpr int64_t kStaticMaxRows = (int64_t)kStaticRowsPerBlock * kStaticPartials;
+
+static __device__ __align__(256) float g_static_scratch[kStaticPartials + 64];
+
+// one block reduces |x| over its 64 rows and overwrites its own slot
+template <typename T>
+__global__ void __launch_bounds__(256)
+static_partial_absmax_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx, float* __restrict__ partials)
+{
+    __shared__ float red[8];
+    const int64_t r0 = (int64_t)blockIdx.x * kStaticRowsPerBlock;
+    const int64_t r1 = (r0 + kStaticRowsPerBlock < M) ? r0 + kStaticRowsPerBlock : M;
+    float m = 0.f;
+    for (int64_t r = r0 + (threadIdx.x >> 5); r < r1; r += 8)
+        for (int c = threadIdx.x & 31; c < K; c += 32)
+            m = fmaxf(m, fabsf(Elem<T>::up(x[r * ldx + c])));
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < 8 ? red[threadIdx.x] : 0.f;
+        t = warp_max(t);
+        if (threadIdx.x == 0) partials[blockIdx.x] = t;
+    }
+}
+
+// a single block folds the partials of this call into the final slot
+__global__ void __launch_bounds__(256)
+static_reduce_partials_kernel(const float* __restrict__ partials, int n, float* __restrict__ result)
+{
+    __shared__ float red[8];
+    float m = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) m = fmaxf(m, partials[i]);
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < 8 ? red[threadIdx.x] : 0.f;
+        t = warp_max(t);
+        if (threadIdx.x == 0) *result = t;
+    }
+}
+
+// Device address of g_static_scratch for the current device.  In host code the array's
+// name is only a handle; the address a kernel can use comes from cudaGetSymbolAddress,
+// asked once per device with that device current.
+static int static_scratch_address(float** out)
+{
+    constexpr int kMaxDevices = 64;
+    static float* cached[kMaxDevices] = {nullptr};
+    int dev = 0;
+    SAMQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(SAMQ_ERR_UNSUPPORTED, "device index %d beyond %d", dev, kMaxDevices);
+    float* p = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+    if (p == nullptr) {
+        void* addr = nullptr;
+        SAMQ_CUDA_TRY(cudaGetSymbolAddress(&addr, g_static_scratch));
+        p = static_cast<float*>(addr);
+        __atomic_store_n(&cached[dev], p, __ATOMIC_RELEASE);
+    }
+    *out = p;
+    return SAMQ_OK;
+}
+
+template <typename T>
+static int per_tensor_static_typed(const T* x, int64_t M, int K, int64_t ldx, float qmax,
+                                   int8_t* q, float* scale, T* fq, cudaStream_t st)
+{
+    float* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc != SAMQ_OK) return rc;
+    const int blocks = (int)((M + kStaticRowsPerBlock - 1) / kStaticRowsPerBlock);
+    static_partial_absmax_kernel<T><<<blocks, 256, 0, st>>>(x, M, K, ldx, scratch);
+    SAMQ_CUDA_TRY(cudaGetLastError());
+    static_reduce_partials_kernel<<<1, 256, 0, st>>>(scratch, blocks, scratch + kStaticPartials);
+    SAMQ_CUDA_TRY(cudaGetLastError());
+    return launch_rows<T>(x, M, K, ldx, nullptr, SAMQ_GRAN_TENSOR, 0, scratch + kStaticPartials, qmax,
+                          q, scale, fq, nullptr, st);
+}
+
+int act_quant_per_tensor_static_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, int n_bits,
+                                         int8_t* q, float* scale, void* fq, void* stream)
+{
+    if (M < 0 || K <= 0 || ldx < K) return fail(SAMQ_ERR_BAD_ARG, "bad shape M=%lld K=%lld ldx=%lld",
+                                                (long long)M, (long long)K, (long long)ldx);
+    if (M > kStaticMaxRows)
+        return fail(SAMQ_ERR_TOO_LARGE, "M=%lld rows exceed the %lld rows the built-in scratch array covers; "
+                    "use samq_act_quant_i8 with a caller workspace", (long long)M, (long long)kStaticMaxRows);
+    if (K > (1 << 20)) return fail(SAMQ_ERR_TOO_LARGE, "K=%lld exceeds 2^20", (long long)K);
+    if (n_bits < 2 || n_bits > 8) return fail(SAMQ_ERR_UNSUPPORTED, "n_bits=%d: int8 codes hold 2..8 bits", n_bits);
+    if (M == 0) return SAMQ_OK;
+    if (x == nullptr) return fail(SAMQ_ERR_BAD_ARG, "x is null");
+    const float qmax = (float)((1 << (n_bits - 1)) - 1);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+    case SAMQ_F16:  return per_tensor_static_typed<__half>((const __half*)x, M, (int)K, ldx, qmax, q, scale, (__half*)fq, st);
+    case SAMQ_BF16: return per_tensor_static_typed<__nv_bfloat16>((const __nv_bfloat16*)x, M, (int)K, ldx, qmax, q, scale, (__nv_bfloat16*)fq, st);
+    case SAMQ_F32:  return per_tensor_static_typed<float>((const float*)x, M, (int)K, ldx, qmax, q, scale, (float*)fq, st);
+    default:        return fail(SAMQ_ERR_BAD_ARG, "unknown dtype %d", dtype);
+    }
+}
+
+
 }  // namespace samq
