@@ -90,6 +90,26 @@ typedef struct samq_hadamard_spec {
     const int8_t* signs;     /* device, [K] of +-1, or NULL                        */
 } samq_hadamard_spec;
 
+/* Steps that may run inside the quantization kernel before the absmax, replacing separate
+ * passes of the encoder block (quarot/model_utils.py:180-198):
+ *   row_map   : gather. Output row r is computed from source row row_map[r]; a negative entry
+ *               yields a row of zeros — `window_partition` with its zero padding
+ *               (quarot/model_utils.py:15-36) or `window_unpartition` (:39-59) as an index map.
+ *               M of the call is the number of OUTPUT rows.
+ *   ln_weight / ln_bias / ln_eps : LayerNorm over the K columns of the (gathered) source row,
+ *               fp32 statistics, result rounded once to `dtype` (norm1 / norm2 of the block).
+ *               Padding rows stay zero (the reference pads after the norm).
+ *   src_dtype : storage type of x when it differs from `dtype`, or -1. Supported pair:
+ *               SAMQ_BF16 storage with dtype SAMQ_F16 (bf16 attention output that the model
+ *               casts to fp16 before `proj`). */
+typedef struct samq_quant_prologue {
+    const int32_t* row_map;    /* device, [M] int32, or NULL                 */
+    const void*    ln_weight;  /* device, [K] of `dtype`, or NULL            */
+    const void*    ln_bias;    /* device, [K] of `dtype`, or NULL            */
+    float          ln_eps;
+    int32_t        src_dtype;  /* SAMQ_* or -1                               */
+} samq_quant_prologue;
+
 /* ---- library ------------------------------------------------------------ */
 
 /* Library version, major*10000 + minor*100 + patch.  No reference counterpart
@@ -136,6 +156,14 @@ int samq_act_quant_i8(const void* x, int dtype, int64_t M, int64_t K, int64_t ld
                       int granularity, int group_size, int n_bits,
                       int8_t* q_out, float* scale_out, void* fq_out, void* tx_out,
                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* samq_act_quant_i8 with a prologue (see samq_quant_prologue); `prologue` may be NULL. */
+int samq_act_quant_i8_ex(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                         const samq_quant_prologue* prologue,
+                         const void* divisor, const samq_hadamard_spec* had,
+                         int granularity, int group_size, int n_bits,
+                         int8_t* q_out, float* scale_out, void* fq_out, void* tx_out,
+                         void* workspace, size_t workspace_bytes, void* stream);
 
 /* Same arithmetic applied to a weight [N, K] (rows = output channels).  Kept as
  * its own symbol because the reference names the weight quantizers separately
@@ -201,6 +229,32 @@ int samq_gemm_i8(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
                  const void* bias, const void* residual, int64_t ldr,
                  int activation, void* out, int out_dtype, int64_t ldo,
                  int32_t* status, void* stream);
+
+/* ---- attention-side helpers (the step between qkv and proj) -------------------------------
+ *
+ * They implement the decomposed relative position bias that the reference applies through
+ * `add_decomposed_rel_pos` (quarot/model_utils.py:162-166):
+ *   bias[(qh,qw),(kh,kw)] = q . rel_pos_h[qh-kh+H-1] + q . rel_pos_w[qw-kw+W-1].
+ * The dot products come in precomputed (one small tensor-core GEMM by the caller) as
+ *   rel_all[head, token, j] = q[token, head, :] . table[j, :],  j < 2H-1 : rel_pos_h rows,
+ *                                                               then 2W-1 rel_pos_w rows,
+ * fp16 or bf16, row pitch rel_pitch >= (2H-1)+(2W-1) elements.  The kernels move data only.
+ *
+ * samq_attn_window_prep reads q and k in place from the qkv GEMM output `qkv` [tokens, 3*C]
+ * (C = heads*head_dim, head_dim and width multiples of 8) and writes, per token and head,
+ *   q_aug = [ q*scale | rel_h[kh], kh<H | rel_w[kw], kw<W | 0.. ]   (width columns)
+ *   k_aug = [ k       | onehot(kh)      | onehot(kw)      | 0.. ]
+ * as [tokens, heads, width], so that softmax(q_aug k_aug^T) v equals the biased attention with
+ * no bias tensor.  tokens = windows*H*W in window order; width >= head_dim + H + W.
+ *
+ * samq_attn_rel_bias writes the explicit bias [images, heads, H*W, H*W] for global attention,
+ * where H + W extra columns would not fit a fused attention kernel (H <= 64, W % 8 == 0). */
+int samq_attn_window_prep(const void* qkv, const void* rel_all, int dtype, int64_t tokens, int rel_pitch,
+                          int H, int W, int num_heads, int head_dim, float scale, int width,
+                          void* q_aug, void* k_aug, void* stream);
+
+int samq_attn_rel_bias(const void* rel_all, int dtype, int64_t images, int rel_pitch, int H, int W, int num_heads,
+                       void* bias, void* stream);
 
 #ifdef __cplusplus
 }

@@ -167,6 +167,31 @@ class W8A8Linear(nn.Module):
             y = self.output_quant(y)
         return y
 
+    def can_fuse_prologue(self) -> bool:
+        """True when LayerNorm / row gather may be folded into this layer's quantization kernel
+        (per-token and per-group activations; a per-tensor scale needs a separate reduction)."""
+        return self.act_quant_name in ("per_token", "per_group_token")
+
+    @torch.no_grad()
+    def forward_fused(self, x, row_map=None, layer_norm=None, as_dtype=None, residual=None,
+                      activation=None, out_dtype=None):
+        """The layer with its neighbours folded in: ``x`` is [rows, K]; ``row_map`` gathers rows
+        (window partition / unpartition), ``layer_norm=(w, b, eps)`` normalises them, ``as_dtype``
+        reads bf16 storage as fp16, all inside K1; ``activation`` / ``residual`` / ``out_dtype``
+        act in K2's epilogue.  Returns [rows_out, N]."""
+        a_gran = ops.ACT_GRANULARITY[self.act_quant_name]
+        w_gran = ops.WEIGHT_GRANULARITY[self.weight_quant_name]
+        tdtype = as_dtype or x.dtype
+        xa = ops.quantize(x, a_gran, self.group_size, divisor=self.smooth_divisor, hadamard=self.hadamard,
+                          n_bits=self.n_bits, row_map=row_map, layer_norm=layer_norm, as_dtype=as_dtype)
+        y = ops.gemm_i8(xa["q"], self.qweight, xa["scale"], self.w_scale, a_gran, w_gran,
+                        self.group_size or 0, bias=self.bias, residual=residual,
+                        activation=ACT_GELU if activation == "gelu" else ACT_NONE,
+                        out_dtype=out_dtype or tdtype)
+        if self.quantize_output:
+            y = self.output_quant(y)
+        return y
+
     @staticmethod
     def from_float(module, n_bits, weight_quant="per_channel", act_quant="per_token",
                    quantize_output=False, group_size=None):

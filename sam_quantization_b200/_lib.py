@@ -23,9 +23,12 @@ EXPORTED_SYMBOLS = (
     "samq_last_error_string",
     "samq_quant_workspace_bytes",
     "samq_act_quant_i8",
+    "samq_act_quant_i8_ex",
     "samq_weight_quant_i8",
     "samq_act_quant_per_tensor_static",
     "samq_gemm_i8",
+    "samq_attn_window_prep",
+    "samq_attn_rel_bias",
 )
 
 
@@ -38,6 +41,18 @@ class HadamardSpec(Structure):
         ("hadk", c_void_p),
         ("had_dim", c_int32),
         ("signs", c_void_p),
+    ]
+
+
+class QuantPrologue(Structure):
+    """Mirror of ``samq_quant_prologue``."""
+
+    _fields_ = [
+        ("row_map", c_void_p),
+        ("ln_weight", c_void_p),
+        ("ln_bias", c_void_p),
+        ("ln_eps", c_float),
+        ("src_dtype", c_int32),
     ]
 
 
@@ -77,6 +92,15 @@ def load() -> ctypes.CDLL:
         c_void_p, c_void_p, c_void_p, c_void_p,          # q, scale, fq, tx
         c_void_p, c_size_t, c_void_p,                    # workspace, bytes, stream
     ]
+    lib.samq_act_quant_i8_ex.restype = c_int
+    lib.samq_act_quant_i8_ex.argtypes = [
+        c_void_p, c_int, c_int64, c_int64, c_int64,      # x, dtype, M (output rows), K, ldx
+        POINTER(QuantPrologue),                          # prologue
+        c_void_p, POINTER(HadamardSpec),                 # divisor, had
+        c_int, c_int, c_int,                             # granularity, group_size, n_bits
+        c_void_p, c_void_p, c_void_p, c_void_p,          # q, scale, fq, tx
+        c_void_p, c_size_t, c_void_p,                    # workspace, bytes, stream
+    ]
     lib.samq_weight_quant_i8.restype = c_int
     lib.samq_weight_quant_i8.argtypes = [
         c_void_p, c_int, c_int64, c_int64, c_int64,
@@ -97,6 +121,17 @@ def load() -> ctypes.CDLL:
         c_void_p, c_void_p, c_int64,                     # bias, residual, ldr
         c_int, c_void_p, c_int, c_int64,                 # activation, out, out_dtype, ldo
         c_void_p, c_void_p,                              # status, stream
+    ]
+    lib.samq_attn_window_prep.restype = c_int
+    lib.samq_attn_window_prep.argtypes = [
+        c_void_p, c_void_p, c_int, c_int64, c_int,              # qkv, rel_all, dtype, tokens, rel_pitch
+        c_int, c_int, c_int, c_int, c_float, c_int,             # H, W, heads, head_dim, scale, width
+        c_void_p, c_void_p, c_void_p,                           # q_aug, k_aug, stream
+    ]
+    lib.samq_attn_rel_bias.restype = c_int
+    lib.samq_attn_rel_bias.argtypes = [
+        c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int,   # rel_all, dtype, images, rel_pitch, H, W, heads
+        c_void_p, c_void_p,                                     # bias, stream
     ]
     _lib = lib
     return lib

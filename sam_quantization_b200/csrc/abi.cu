@@ -19,6 +19,7 @@ int fail(int code, const char* fmt, ...) {
 }
 
 int act_quant_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                       const samq_quant_prologue* prologue,
                        const void* divisor, const samq_hadamard_spec* had,
                        int gran, int group_size, int n_bits, int8_t* q, float* scale, void* fq, void* tx,
                        void* workspace, size_t workspace_bytes, void* stream);
@@ -38,6 +39,11 @@ int gemm_i8_grouped_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int6
                              const void* bias, const void* residual, int64_t ldr, int activation,
                              void* out, int out_dtype, int64_t ldo, int32_t* status, void* stream);
 
+int attn_window_prep_dispatch(const void* qkv, const void* rel_all, int dtype, int64_t tokens, int J,
+                              int H, int W, int nh, int d, float scale, int width, void* qa, void* ka, void* stream);
+
+int attn_rel_bias_dispatch(const void* rel_all, int dtype, int64_t images, int J, int H, int W, int nh, void* bias, void* stream);
+
 }  // namespace samq
 
 extern "C" {
@@ -56,7 +62,18 @@ int samq_act_quant_i8(const void* x, int dtype, int64_t M, int64_t K, int64_t ld
                       int8_t* q_out, float* scale_out, void* fq_out, void* tx_out,
                       void* workspace, size_t workspace_bytes, void* stream)
 {
-    return samq::act_quant_dispatch(x, dtype, M, K, ldx, divisor, had, granularity, group_size, n_bits,
+    return samq::act_quant_dispatch(x, dtype, M, K, ldx, nullptr, divisor, had, granularity, group_size, n_bits,
+                                    q_out, scale_out, fq_out, tx_out, workspace, workspace_bytes, stream);
+}
+
+int samq_act_quant_i8_ex(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                         const samq_quant_prologue* prologue,
+                         const void* divisor, const samq_hadamard_spec* had,
+                         int granularity, int group_size, int n_bits,
+                         int8_t* q_out, float* scale_out, void* fq_out, void* tx_out,
+                         void* workspace, size_t workspace_bytes, void* stream)
+{
+    return samq::act_quant_dispatch(x, dtype, M, K, ldx, prologue, divisor, had, granularity, group_size, n_bits,
                                     q_out, scale_out, fq_out, tx_out, workspace, workspace_bytes, stream);
 }
 
@@ -65,7 +82,7 @@ int samq_weight_quant_i8(const void* w, int dtype, int64_t N, int64_t K, int64_t
                          int8_t* q_out, float* scale_out, void* fq_out,
                          void* workspace, size_t workspace_bytes, void* stream)
 {
-    return samq::act_quant_dispatch(w, dtype, N, K, ldw, nullptr, nullptr, granularity, group_size, n_bits,
+    return samq::act_quant_dispatch(w, dtype, N, K, ldw, nullptr, nullptr, nullptr, granularity, group_size, n_bits,
                                     q_out, scale_out, fq_out, nullptr, workspace, workspace_bytes, stream);
 }
 
@@ -73,6 +90,20 @@ int samq_act_quant_per_tensor_static(const void* x, int dtype, int64_t M, int64_
                                      int8_t* q_out, float* scale_out, void* fq_out, void* stream)
 {
     return samq::act_quant_per_tensor_static_dispatch(x, dtype, M, K, ldx, n_bits, q_out, scale_out, fq_out, stream);
+}
+
+int samq_attn_window_prep(const void* qkv, const void* rel_all, int dtype, int64_t tokens, int rel_pitch,
+                          int H, int W, int num_heads, int head_dim, float scale, int width,
+                          void* q_aug, void* k_aug, void* stream)
+{
+    return samq::attn_window_prep_dispatch(qkv, rel_all, dtype, tokens, rel_pitch, H, W, num_heads, head_dim, scale,
+                                           width, q_aug, k_aug, stream);
+}
+
+int samq_attn_rel_bias(const void* rel_all, int dtype, int64_t images, int rel_pitch, int H, int W, int num_heads,
+                       void* bias, void* stream)
+{
+    return samq::attn_rel_bias_dispatch(rel_all, dtype, images, rel_pitch, H, W, num_heads, bias, stream);
 }
 
 int samq_gemm_i8(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,

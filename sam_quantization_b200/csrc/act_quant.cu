@@ -12,6 +12,7 @@
 // memory), and written once as K int8 codes plus one fp32 scale:
 // 3K + 4 algorithmic bytes per row.
 #include "common.cuh"
+#include <type_traits>
 
 namespace samq {
 
@@ -77,7 +78,7 @@ template <> __device__ __forceinline__ uint2 pack_codes<8>(const float (&q)[8], 
     for (int h = 0; h < 2; ++h) {
         uint32_t v = 0;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v |= (uint32_t)(uint8_t)saturate_i8(q[4 * h + i], qmax) << (8 * i);
+        for (int i = 0; i < 4; ++i) v |= code_byte(q[4 * h + i], qmax) << (8 * i);
         w[h] = v;
     }
     return make_uint2(w[0], w[1]);
@@ -85,52 +86,124 @@ template <> __device__ __forceinline__ uint2 pack_codes<8>(const float (&q)[8], 
 template <> __device__ __forceinline__ uint32_t pack_codes<4>(const float (&q)[4], float qmax) {
     uint32_t v = 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) v |= (uint32_t)(uint8_t)saturate_i8(q[i], qmax) << (8 * i);
+    for (int i = 0; i < 4; ++i) v |= code_byte(q[i], qmax) << (8 * i);
     return v;
 }
 
 // ---------------------------------------------------------------------------
-// Row kernel: one warp owns one row and keeps it in registers.
+// What may precede the absmax in the row kernels (all optional):
+//   row_map   gather: output row r reads source row row_map[r]; a negative entry is a row of
+//             zeros (the zero padding of window_partition, quarot/model_utils.py:28-31)
+//   SrcT      storage type of x when it differs from the tensor type T the arithmetic
+//             emulates (bf16 attention output that the model casts to fp16 before proj)
+//   LayerNorm y = T(gamma * (rstd * (x - mean)) + beta), fp32 statistics, the expression order
+//             of torch's CUDA LayerNorm
+//   divisor   SmoothQuant: y = T(y / d)
+// ---------------------------------------------------------------------------
+struct Prologue {
+    const int32_t* row_map;
+    const void* ln_gamma;
+    const void* ln_beta;
+    float ln_eps;
+};
+
+// ---------------------------------------------------------------------------
+// Row kernel: a row lives in the registers of one warp (MULTI = false, up to 8 vectors of 16
+// bytes per lane) or of `tpr` threads of a CTA (MULTI = true, 4 vectors per thread), so large
+// rows keep occupancy.  Vector v of a row belongs to thread v % tpr: loads stay coalesced.
 //   GRAN ROW    : scale from the row's absolute maximum
 //   GRAN GROUP  : `lanes_per_group` adjacent lanes (a power of two <= 32) share a scale
-//   GRAN TENSOR : the absolute maximum was reduced by absmax_kernel into *tensor_absmax
+//   GRAN TENSOR : the absolute maximum was reduced beforehand into *tensor_absmax
 // ---------------------------------------------------------------------------
-template <typename T, int NV>
+template <typename T, typename SrcT, int NV, bool MULTI, bool LN>
 __global__ void __launch_bounds__(256)
-quant_rows_vec_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
-                      const T* __restrict__ divisor, int gran, int lanes_per_group,
-                      const float* __restrict__ tensor_absmax, float qmax,
-                      int8_t* __restrict__ q_out, float* __restrict__ scale_out,
-                      T* __restrict__ fq_out, T* __restrict__ tx_out)
+quant_rows_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx, int tpr, Prologue pro,
+                  const T* __restrict__ divisor, int gran, int lanes_per_group,
+                  const float* __restrict__ tensor_absmax, float qmax,
+                  int8_t* __restrict__ q_out, float* __restrict__ scale_out,
+                  T* __restrict__ fq_out, T* __restrict__ tx_out)
 {
     constexpr int E = Elem<T>::kPerVec;
-    const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= M) return;
+    static_assert(sizeof(SrcT) == sizeof(T), "source and tensor types must have the same width");
+    __shared__ float red[8];
+    const int rows_per_cta = blockDim.x / tpr;
+    const int rin = threadIdx.x / tpr;                 // row inside the CTA
+    const int t = threadIdx.x - rin * tpr;             // thread inside the row
+    const int64_t row = (int64_t)blockIdx.x * rows_per_cta + rin;
+    const bool active = row < M;
+    if (!MULTI && !active) return;
     const int nvec = K / E;
-    const T* xr = x + row * ldx;
+
+    int64_t src = row;
+    if (pro.row_map != nullptr && active) src = pro.row_map[row];
+    const bool live = active && src >= 0;
+    const SrcT* xr = x + (live ? src : 0) * ldx;
 
     uint4 raw[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-        const int v = i * 32 + lane;
-        raw[i] = (v < nvec) ? ld_stream(xr + (int64_t)v * E) : make_uint4(0, 0, 0, 0);
+        const int v = i * tpr + t;
+        raw[i] = (live && v < nvec) ? ld_stream(xr + (int64_t)v * E) : make_uint4(0, 0, 0, 0);
+    }
+
+    // ---- optional LayerNorm (single-warp rows only) -------------------------------------
+    float mean = 0.f, rstd = 0.f;
+    if constexpr (LN) {
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            float f[E];
+            unpack<SrcT>(raw[i], f);
+#pragma unroll
+            for (int e = 0; e < E; ++e) sum += f[e];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        mean = sum / (float)K;
+        float var = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int v = i * tpr + t;
+            float f[E];
+            unpack<SrcT>(raw[i], f);
+            if (v < nvec) {
+#pragma unroll
+                for (int e = 0; e < E; ++e) { const float d = f[e] - mean; var += d * d; }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+        rstd = rsqrtf(var / (float)K + pro.ln_eps);
     }
 
     float vmax[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-        const int v = i * 32 + lane;
+        const int v = i * tpr + t;
         float f[E];
-        unpack<T>(raw[i], f);
+        unpack<SrcT>(raw[i], f);
+        bool repack = !std::is_same<SrcT, T>::value;
+        if (!std::is_same<SrcT, T>::value) RoundVec<T, E>::run(f);
+        if constexpr (LN) {
+            if (live && v < nvec) {
+                float g[E], b[E];
+                unpack<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(pro.ln_gamma) + (int64_t)v * E), g);
+                unpack<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(pro.ln_beta) + (int64_t)v * E), b);
+#pragma unroll
+                for (int e = 0; e < E; ++e) f[e] = g[e] * (rstd * (f[e] - mean)) + b[e];
+                RoundVec<T, E>::run(f);
+                repack = true;
+            }
+        }
         if (divisor != nullptr && v < nvec) {
             float d[E];
-            uint4 draw = *reinterpret_cast<const uint4*>(divisor + (int64_t)v * E);
-            unpack<T>(draw, d);
+            unpack<T>(*reinterpret_cast<const uint4*>(divisor + (int64_t)v * E), d);
 #pragma unroll
-            for (int e = 0; e < E; ++e) f[e] = round_to<T>(__fdiv_rn(f[e], d[e]));
-            raw[i] = pack<T>(f);
+            for (int e = 0; e < E; ++e) f[e] = __fdiv_rn(f[e], d[e]);
+            RoundVec<T, E>::run(f);
+            repack = true;
         }
+        if (repack) raw[i] = pack<T>(f);
         float m = 0.f;
 #pragma unroll
         for (int e = 0; e < E; ++e) m = fmaxf(m, fabsf(f[e]));
@@ -143,31 +216,43 @@ quant_rows_vec_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
 #pragma unroll
         for (int i = 0; i < NV; ++i) m = fmaxf(m, vmax[i]);
         m = warp_max(m);
+        if constexpr (MULTI) {
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+            __syncthreads();
+            const int w0 = (rin * tpr) >> 5, nw = tpr >> 5;
+            m = 0.f;
+            for (int w = 0; w < nw; ++w) m = fmaxf(m, red[w0 + w]);
+        }
         row_scale = scale_from_absmax<T>(m, qmax);
-        if (lane == 0 && scale_out != nullptr) scale_out[row] = row_scale;
+        if (active && t == 0 && scale_out != nullptr) scale_out[row] = row_scale;
     } else if (gran == SAMQ_GRAN_TENSOR) {
         row_scale = scale_from_absmax<T>(*tensor_absmax, qmax);
-        if (row == 0 && lane == 0 && scale_out != nullptr) scale_out[0] = row_scale;
+        if (row == 0 && t == 0 && scale_out != nullptr) scale_out[0] = row_scale;
     }
+    if (MULTI && !active) return;
 
     const int groups_per_row = (gran == SAMQ_GRAN_GROUP) ? nvec / lanes_per_group : 0;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-        const int v = i * 32 + lane;
+        const int v = i * tpr + t;
         float s = row_scale;
         if (gran == SAMQ_GRAN_GROUP) {
             float m = vmax[i];
             for (int o = lanes_per_group >> 1; o > 0; o >>= 1)
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
             s = scale_from_absmax<T>(m, qmax);
-            if (v < nvec && (lane & (lanes_per_group - 1)) == 0 && scale_out != nullptr)
+            if (v < nvec && (t & (lanes_per_group - 1)) == 0 && scale_out != nullptr)
                 scale_out[row * groups_per_row + v / lanes_per_group] = s;
         }
         if (v >= nvec) continue;
         float f[E], q[E];
         unpack<T>(raw[i], f);
+        const Divider dv = make_divider(s);
 #pragma unroll
-        for (int e = 0; e < E; ++e) q[e] = quant_value<T>(f[e], s);
+        for (int e = 0; e < E; ++e) q[e] = div_exact(f[e], dv);
+        RoundVec<T, E>::run(q);
+#pragma unroll
+        for (int e = 0; e < E; ++e) q[e] = rint_small(q[e]);
         if (q_out != nullptr)
             *reinterpret_cast<typename PackedCodes<E>::type*>(q_out + row * K + (int64_t)v * E) = pack_codes<E>(q, qmax);
         if (tx_out != nullptr)
@@ -185,9 +270,9 @@ quant_rows_vec_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
 // Covers every shape the vector kernel does not (odd K, unaligned rows,
 // very long rows, group sizes that are not 8 * 2^j).
 // ---------------------------------------------------------------------------
-template <typename T>
+template <typename T, typename SrcT>
 __global__ void __launch_bounds__(256)
-quant_rows_generic_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
+quant_rows_generic_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx, const int32_t* __restrict__ row_map,
                           const T* __restrict__ divisor, int gran, int group_size,
                           const float* __restrict__ tensor_absmax, float qmax,
                           int8_t* __restrict__ q_out, float* __restrict__ scale_out,
@@ -200,7 +285,14 @@ quant_rows_generic_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx
     if (unit >= M * units_per_row) return;
     const int64_t row = unit / units_per_row;
     const int c0 = (int)(unit % units_per_row) * span;
-    const T* xr = x + row * ldx;
+    const int64_t src = row_map != nullptr ? (int64_t)row_map[row] : row;
+    const SrcT* xr = x + (src >= 0 ? src : 0) * ldx;
+    auto value = [&](int c) -> float {
+        if (src < 0) return 0.f;
+        float v = round_to<T>(Elem<SrcT>::up(xr[c]));
+        if (divisor != nullptr) v = round_to<T>(__fdiv_rn(v, Elem<T>::up(divisor[c])));
+        return v;
+    };
 
     float s;
     if (gran == SAMQ_GRAN_TENSOR) {
@@ -208,19 +300,15 @@ quant_rows_generic_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx
         if (unit == 0 && lane == 0 && scale_out != nullptr) scale_out[0] = s;
     } else {
         float m = 0.f;
-        for (int c = c0 + lane; c < c0 + span; c += 32) {
-            float v = Elem<T>::up(xr[c]);
-            if (divisor != nullptr) v = round_to<T>(__fdiv_rn(v, Elem<T>::up(divisor[c])));
-            m = fmaxf(m, fabsf(v));
-        }
+        for (int c = c0 + lane; c < c0 + span; c += 32) m = fmaxf(m, fabsf(value(c)));
         m = warp_max(m);
         s = scale_from_absmax<T>(m, qmax);
         if (lane == 0 && scale_out != nullptr) scale_out[unit] = s;
     }
+    const Divider dv = make_divider(s);
     for (int c = c0 + lane; c < c0 + span; c += 32) {
-        float v = Elem<T>::up(xr[c]);
-        if (divisor != nullptr) v = round_to<T>(__fdiv_rn(v, Elem<T>::up(divisor[c])));
-        const float q = quant_value<T>(v, s);
+        const float v = value(c);
+        const float q = quant_value<T>(v, dv);
         if (q_out != nullptr) q_out[row * K + c] = saturate_i8(q, qmax);
         if (tx_out != nullptr) tx_out[row * K + c] = Elem<T>::down(v);
         if (fq_out != nullptr) fq_out[row * K + c] = Elem<T>::down(q * s);
@@ -267,9 +355,9 @@ absmax_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ int padded(int i) { return i + (i >> 4); }
 
-template <typename T>
+template <typename T, typename SrcT>
 __global__ void __launch_bounds__(1024)
-hadamard_quant_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
+hadamard_quant_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx, const int32_t* __restrict__ row_map,
                       const T* __restrict__ divisor, const int8_t* __restrict__ signs,
                       int inner, int axis, int had_k, int log2_pow,
                       const float* __restrict__ hadk, float qmax,
@@ -281,11 +369,12 @@ hadamard_quant_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
     float* red = hk + had_k * had_k;
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int64_t row = blockIdx.x;
-    const T* xr = x + row * ldx;
+    const int64_t src = row_map != nullptr ? (int64_t)row_map[row] : row;
+    const SrcT* xr = x + (src >= 0 ? src : 0) * ldx;
 
-    // (a) load, SmoothQuant divisor, sign flip
+    // (a) load (gathered row, or zeros for a padding row), SmoothQuant divisor, sign flip
     for (int c = tid; c < K; c += nthr) {
-        float v = Elem<T>::up(xr[c]);
+        float v = src >= 0 ? round_to<T>(Elem<SrcT>::up(xr[c])) : 0.f;
         if (divisor != nullptr) v = round_to<T>(__fdiv_rn(v, Elem<T>::up(divisor[c])));
         if (signs != nullptr && signs[c] < 0) v = -v;
         sm[padded(c)] = v;
@@ -351,10 +440,10 @@ hadamard_quant_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
     }
 
     // (d) scale by 1/sqrt(axis) with a true division, round once to T, absmax
-    const float root = sqrtf((float)axis);
+    const Divider root = make_divider(sqrtf((float)axis));
     float m = 0.f;
     for (int c = tid; c < K; c += nthr) {
-        const float v = round_to<T>(__fdiv_rn(sm[padded(c)], root));
+        const float v = round_to<T>(div_exact(sm[padded(c)], root));
         sm[padded(c)] = v;
         m = fmaxf(m, fabsf(v));
     }
@@ -371,9 +460,10 @@ hadamard_quant_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
     if (tid == 0 && scale_out != nullptr) scale_out[row] = s;
 
     // (e) quantize and store
+    const Divider dv = make_divider(s);
     for (int c = tid; c < K; c += nthr) {
         const float v = sm[padded(c)];
-        const float q = quant_value<T>(v, s);
+        const float q = quant_value<T>(v, dv);
         if (q_out != nullptr) q_out[row * K + c] = saturate_i8(q, qmax);
         if (tx_out != nullptr) tx_out[row * K + c] = Elem<T>::down(v);
         if (fq_out != nullptr) fq_out[row * K + c] = Elem<T>::down(q * s);
@@ -385,54 +475,76 @@ hadamard_quant_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
 // ---------------------------------------------------------------------------
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-template <typename T>
-static int launch_rows(const T* x, int64_t M, int K, int64_t ldx, const T* divisor,
+template <typename T, typename SrcT>
+static int launch_rows(const SrcT* x, int64_t M, int K, int64_t ldx, const Prologue& pro, const T* divisor,
                        int gran, int group_size, const float* tensor_absmax, float qmax,
                        int8_t* q, float* scale, T* fq, T* tx, cudaStream_t st)
 {
     constexpr int E = Elem<T>::kPerVec;
+    const bool ln = pro.ln_gamma != nullptr;
     bool vec_ok = (K % E == 0) && (ldx % E == 0) && aligned16(x) && aligned16(fq) && aligned16(tx) &&
-                  aligned16(divisor) && ((reinterpret_cast<uintptr_t>(q) & 7) == 0) && K <= 40 * 32 * E;
+                  aligned16(divisor) && aligned16(pro.ln_gamma) && aligned16(pro.ln_beta) &&
+                  ((reinterpret_cast<uintptr_t>(q) & 7) == 0) && K <= 256 * 4 * E;
     int lanes_per_group = 32;
     if (gran == SAMQ_GRAN_GROUP) {
         lanes_per_group = group_size / E;
         const bool pow2 = lanes_per_group > 0 && (lanes_per_group & (lanes_per_group - 1)) == 0;
         vec_ok = vec_ok && (group_size % E == 0) && pow2 && lanes_per_group <= 32;
     }
+    const int nvec = K / E;
+    if (ln && !(vec_ok && nvec <= 320))
+        return fail(SAMQ_ERR_UNSUPPORTED, "fused LayerNorm needs 16-byte aligned rows of at most %d elements (K=%d)", 320 * E, K);
     if (vec_ok) {
-        const int nv = (K / E + 31) / 32;
-        const int warps = 8;
-        dim3 grid((unsigned)((M + warps - 1) / warps)), block(warps * 32);
-#define SAMQ_LAUNCH_NV(NVAL)                                                               \
-        quant_rows_vec_kernel<T, NVAL><<<grid, block, 0, st>>>(x, M, K, ldx, divisor, gran, \
-            lanes_per_group, tensor_absmax, qmax, q, scale, fq, tx)
-        if (nv <= 1) SAMQ_LAUNCH_NV(1);
-        else if (nv <= 2) SAMQ_LAUNCH_NV(2);
-        else if (nv <= 3) SAMQ_LAUNCH_NV(3);
-        else if (nv <= 4) SAMQ_LAUNCH_NV(4);
-        else if (nv <= 5) SAMQ_LAUNCH_NV(5);
-        else if (nv <= 8) SAMQ_LAUNCH_NV(8);
-        else if (nv <= 12) SAMQ_LAUNCH_NV(12);
-        else if (nv <= 16) SAMQ_LAUNCH_NV(16);
-        else if (nv <= 20) SAMQ_LAUNCH_NV(20);
-        else if (nv <= 24) SAMQ_LAUNCH_NV(24);
-        else if (nv <= 32) SAMQ_LAUNCH_NV(32);
-        else SAMQ_LAUNCH_NV(40);
-#undef SAMQ_LAUNCH_NV
+#define SAMQ_LAUNCH(NVAL, MULTI_, LN_, TPR, GRID, BLOCK)                                               \
+        quant_rows_kernel<T, SrcT, NVAL, MULTI_, LN_><<<GRID, BLOCK, 0, st>>>(x, M, K, ldx, TPR, pro,    \
+            divisor, gran, lanes_per_group, tensor_absmax, qmax, q, scale, fq, tx)
+        if (nvec <= 320) {
+            const int nv = (nvec + 31) / 32;
+            const unsigned grid = (unsigned)((M + 7) / 8);
+            if (ln) {
+                switch (nv) {
+                case 1: SAMQ_LAUNCH(1, false, true, 32, grid, 256); break;
+                case 2: SAMQ_LAUNCH(2, false, true, 32, grid, 256); break;
+                case 3: SAMQ_LAUNCH(3, false, true, 32, grid, 256); break;
+                case 4: SAMQ_LAUNCH(4, false, true, 32, grid, 256); break;
+                case 5: SAMQ_LAUNCH(5, false, true, 32, grid, 256); break;
+                case 6: SAMQ_LAUNCH(6, false, true, 32, grid, 256); break;
+                case 7: case 8: SAMQ_LAUNCH(8, false, true, 32, grid, 256); break;
+                default: SAMQ_LAUNCH(10, false, true, 32, grid, 256); break;
+                }
+            } else {
+                switch (nv) {
+                case 1: SAMQ_LAUNCH(1, false, false, 32, grid, 256); break;
+                case 2: SAMQ_LAUNCH(2, false, false, 32, grid, 256); break;
+                case 3: SAMQ_LAUNCH(3, false, false, 32, grid, 256); break;
+                case 4: SAMQ_LAUNCH(4, false, false, 32, grid, 256); break;
+                case 5: SAMQ_LAUNCH(5, false, false, 32, grid, 256); break;
+                case 6: SAMQ_LAUNCH(6, false, false, 32, grid, 256); break;
+                case 7: case 8: SAMQ_LAUNCH(8, false, false, 32, grid, 256); break;
+                default: SAMQ_LAUNCH(10, false, false, 32, grid, 256); break;
+                }
+            }
+        } else {
+            int tpr = (((nvec + 3) / 4) + 31) / 32 * 32;             // threads per row at 4 vectors each
+            const int rows_per_cta = 256 / tpr > 0 ? 256 / tpr : 1;
+            const unsigned grid = (unsigned)((M + rows_per_cta - 1) / rows_per_cta);
+            SAMQ_LAUNCH(4, true, false, tpr, grid, rows_per_cta * tpr);
+        }
+#undef SAMQ_LAUNCH
     } else {
         const int span = (gran == SAMQ_GRAN_GROUP) ? group_size : K;
         const int64_t units = M * (K / span);
         const int warps = 8;
         dim3 grid((unsigned)((units + warps - 1) / warps)), block(warps * 32);
-        quant_rows_generic_kernel<T><<<grid, block, 0, st>>>(x, M, K, ldx, divisor, gran, group_size,
-                                                             tensor_absmax, qmax, q, scale, fq, tx);
+        quant_rows_generic_kernel<T, SrcT><<<grid, block, 0, st>>>(x, M, K, ldx, pro.row_map, divisor, gran, group_size,
+                                                                   tensor_absmax, qmax, q, scale, fq, tx);
     }
     SAMQ_CUDA_TRY(cudaGetLastError());
     return SAMQ_OK;
 }
 
-template <typename T>
-static int quant_typed(const T* x, int64_t M, int K, int64_t ldx, const T* divisor,
+template <typename T, typename SrcT>
+static int quant_typed(const SrcT* x, int64_t M, int K, int64_t ldx, const Prologue& pro, const T* divisor,
                        const samq_hadamard_spec* had, int gran, int group_size, float qmax,
                        int8_t* q, float* scale, T* fq, T* tx,
                        void* workspace, size_t workspace_bytes, cudaStream_t st)
@@ -441,6 +553,8 @@ static int quant_typed(const T* x, int64_t M, int K, int64_t ldx, const T* divis
     if (had != nullptr && had->mode != SAMQ_HAD_NONE) {
         if (gran != SAMQ_GRAN_ROW)
             return fail(SAMQ_ERR_UNSUPPORTED, "an online Hadamard is only combined with per-token quantization");
+        if (pro.ln_gamma != nullptr)
+            return fail(SAMQ_ERR_UNSUPPORTED, "LayerNorm and an online Hadamard are not combined in one call");
         int inner, axis;
         if (had->mode == SAMQ_HAD_FULL) { inner = 1; axis = K; }
         else if (had->mode == SAMQ_HAD_PARTIAL) {
@@ -460,17 +574,19 @@ static int quant_typed(const T* x, int64_t M, int K, int64_t ldx, const T* divis
         const size_t smem = (size_t)(K + (K >> 4) + 2 + hk * hk + 32) * sizeof(float);
         if (smem > 200 * 1024) return fail(SAMQ_ERR_TOO_LARGE, "row of K=%d does not fit in shared memory", K);
         if (smem > 48 * 1024)
-            SAMQ_CUDA_TRY(cudaFuncSetAttribute(hadamard_quant_kernel<T>,
+            SAMQ_CUDA_TRY(cudaFuncSetAttribute(hadamard_quant_kernel<T, SrcT>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         int threads = ((K / 16 + 31) / 32) * 32;
         threads = threads < 32 ? 32 : (threads > 1024 ? 1024 : threads);
-        hadamard_quant_kernel<T><<<(unsigned)M, threads, smem, st>>>(x, M, K, ldx, divisor, had->signs,
+        hadamard_quant_kernel<T, SrcT><<<(unsigned)M, threads, smem, st>>>(x, M, K, ldx, pro.row_map, divisor, had->signs,
             inner, axis, hk, log2_pow, had->hadk, qmax, q, scale, fq, tx);
         SAMQ_CUDA_TRY(cudaGetLastError());
         return SAMQ_OK;
     }
     const float* tensor_absmax = nullptr;
     if (gran == SAMQ_GRAN_TENSOR) {
+        if (pro.row_map != nullptr || pro.ln_gamma != nullptr || !std::is_same<T, SrcT>::value)
+            return fail(SAMQ_ERR_UNSUPPORTED, "per_tensor quantization takes no gather, LayerNorm or source-type prologue");
         if (workspace == nullptr || workspace_bytes < samq_quant_workspace_bytes(gran))
             return fail(SAMQ_ERR_WORKSPACE, "per_tensor quantization needs %zu bytes of workspace",
                         samq_quant_workspace_bytes(gran));
@@ -478,7 +594,7 @@ static int quant_typed(const T* x, int64_t M, int K, int64_t ldx, const T* divis
         const int64_t total = M * (int64_t)K;
         int blocks = (int)((total + 256 * 8 - 1) / (256 * 8));
         blocks = blocks < 1 ? 1 : (blocks > 148 * 8 ? 148 * 8 : blocks);
-        absmax_kernel<T><<<blocks, 256, 0, st>>>(x, M, K, ldx, divisor, static_cast<float*>(workspace));
+        absmax_kernel<T><<<blocks, 256, 0, st>>>(reinterpret_cast<const T*>(x), M, K, ldx, divisor, static_cast<float*>(workspace));
         SAMQ_CUDA_TRY(cudaGetLastError());
         tensor_absmax = static_cast<const float*>(workspace);
     } else if (gran == SAMQ_GRAN_GROUP) {
@@ -487,10 +603,11 @@ static int quant_typed(const T* x, int64_t M, int K, int64_t ldx, const T* divis
     } else if (gran != SAMQ_GRAN_ROW) {
         return fail(SAMQ_ERR_BAD_ARG, "unknown granularity %d", gran);
     }
-    return launch_rows<T>(x, M, K, ldx, divisor, gran, group_size, tensor_absmax, qmax, q, scale, fq, tx, st);
+    return launch_rows<T, SrcT>(x, M, K, ldx, pro, divisor, gran, group_size, tensor_absmax, qmax, q, scale, fq, tx, st);
 }
 
 int act_quant_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx,
+                       const samq_quant_prologue* prologue,
                        const void* divisor, const samq_hadamard_spec* had,
                        int gran, int group_size, int n_bits, int8_t* q, float* scale, void* fq, void* tx,
                        void* workspace, size_t workspace_bytes, void* stream)
@@ -502,18 +619,36 @@ int act_quant_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t l
     if (M > 0 && x == nullptr) return fail(SAMQ_ERR_BAD_ARG, "x is null");
     if (K > (1 << 20)) return fail(SAMQ_ERR_TOO_LARGE, "K=%lld exceeds 2^20", (long long)K);
     if (M > 2147483647LL) return fail(SAMQ_ERR_TOO_LARGE, "M=%lld exceeds 2^31-1", (long long)M);
+    Prologue pro = {nullptr, nullptr, nullptr, 0.f};
+    int src_dtype = dtype;
+    if (prologue != nullptr) {
+        pro.row_map = prologue->row_map;
+        pro.ln_gamma = prologue->ln_weight;
+        pro.ln_beta = prologue->ln_bias;
+        pro.ln_eps = prologue->ln_eps;
+        if ((pro.ln_gamma == nullptr) != (pro.ln_beta == nullptr))
+            return fail(SAMQ_ERR_BAD_ARG, "LayerNorm needs both weight and bias");
+        if (prologue->src_dtype >= 0) src_dtype = prologue->src_dtype;
+    }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (src_dtype != dtype) {
+        if (!(dtype == SAMQ_F16 && src_dtype == SAMQ_BF16))
+            return fail(SAMQ_ERR_UNSUPPORTED, "the only mixed pair is bf16 storage read as an fp16 tensor");
+        return quant_typed<__half, __nv_bfloat16>((const __nv_bfloat16*)x, M, (int)K, ldx, pro, (const __half*)divisor, had,
+                                                  gran, group_size, qmax, q, scale, (__half*)fq, (__half*)tx,
+                                                  workspace, workspace_bytes, st);
+    }
     switch (dtype) {
     case SAMQ_F16:
-        return quant_typed<__half>((const __half*)x, M, (int)K, ldx, (const __half*)divisor, had, gran, group_size, qmax,
-                                   q, scale, (__half*)fq, (__half*)tx, workspace, workspace_bytes, st);
+        return quant_typed<__half, __half>((const __half*)x, M, (int)K, ldx, pro, (const __half*)divisor, had, gran, group_size,
+                                           qmax, q, scale, (__half*)fq, (__half*)tx, workspace, workspace_bytes, st);
     case SAMQ_BF16:
-        return quant_typed<__nv_bfloat16>((const __nv_bfloat16*)x, M, (int)K, ldx, (const __nv_bfloat16*)divisor, had,
-                                          gran, group_size, qmax, q, scale, (__nv_bfloat16*)fq, (__nv_bfloat16*)tx,
-                                          workspace, workspace_bytes, st);
+        return quant_typed<__nv_bfloat16, __nv_bfloat16>((const __nv_bfloat16*)x, M, (int)K, ldx, pro, (const __nv_bfloat16*)divisor,
+                                                         had, gran, group_size, qmax, q, scale, (__nv_bfloat16*)fq,
+                                                         (__nv_bfloat16*)tx, workspace, workspace_bytes, st);
     case SAMQ_F32:
-        return quant_typed<float>((const float*)x, M, (int)K, ldx, (const float*)divisor, had, gran, group_size, qmax,
-                                  q, scale, (float*)fq, (float*)tx, workspace, workspace_bytes, st);
+        return quant_typed<float, float>((const float*)x, M, (int)K, ldx, pro, (const float*)divisor, had, gran, group_size,
+                                         qmax, q, scale, (float*)fq, (float*)tx, workspace, workspace_bytes, st);
     default:
         return fail(SAMQ_ERR_BAD_ARG, "unknown dtype %d", dtype);
     }
@@ -613,8 +748,9 @@ static int per_tensor_static_typed(const T* x, int64_t M, int K, int64_t ldx, fl
     SAMQ_CUDA_TRY(cudaGetLastError());
     static_reduce_partials_kernel<<<1, 256, 0, st>>>(scratch, blocks, scratch + kStaticPartials);
     SAMQ_CUDA_TRY(cudaGetLastError());
-    return launch_rows<T>(x, M, K, ldx, nullptr, SAMQ_GRAN_TENSOR, 0, scratch + kStaticPartials, qmax,
-                          q, scale, fq, nullptr, st);
+    const Prologue none = {nullptr, nullptr, nullptr, 0.f};
+    return launch_rows<T, T>(x, M, K, ldx, none, nullptr, SAMQ_GRAN_TENSOR, 0, scratch + kStaticPartials, qmax,
+                             q, scale, fq, nullptr, st);
 }
 
 int act_quant_per_tensor_static_dispatch(const void* x, int dtype, int64_t M, int64_t K, int64_t ldx, int n_bits,

@@ -56,17 +56,58 @@ __device__ __forceinline__ float scale_from_absmax(float absmax, float qmax) {
     return round_to<T>(__fdiv_rn(a, qmax));
 }
 
+// Division by a scale that is shared by many elements.  x / s is formed as a multiply by the
+// correctly rounded reciprocal followed by one residual correction,
+//     y0 = x * inv;  e = fma(-y0, s, x);  y = fma(e, inv, y0),
+// which yields the correctly rounded IEEE quotient (the classic two-FMA correction of a
+// faithful estimate) while keeping the special-function unit out of the per-element path.
+struct Divider { float s, inv; };
+__device__ __forceinline__ Divider make_divider(float s) { Divider d; d.s = s; d.inv = __frcp_rn(s); return d; }
+__device__ __forceinline__ float div_exact(float x, const Divider& d) {
+    const float y0 = x * d.inv;
+    const float e = fmaf(-y0, d.s, x);
+    return fmaf(e, d.inv, y0);
+}
+
+// round-half-even to an integer for |v| < 2^22 by adding and subtracting 1.5 * 2^23
+constexpr float kRoundMagic = 12582912.0f;
+// (the sign of the input is kept, so that -0.4 rounds to -0.0 as rintf does)
+__device__ __forceinline__ float rint_small(float v) {
+    const float r = (v + kRoundMagic) - kRoundMagic;
+    return __int_as_float(__float_as_int(r) | (__float_as_int(v) & 0x80000000));
+}
+
 // q = round_half_even( T(x / s) ) as a float holding an integer value
 // (`t.div_(scales).round_()`, per_tensor_channel_group.py:60).
 template <typename T>
-__device__ __forceinline__ float quant_value(float x, float s) {
-    return rintf(round_to<T>(__fdiv_rn(x, s)));
+__device__ __forceinline__ float quant_value(float x, const Divider& d) {
+    return rint_small(round_to<T>(div_exact(x, d)));
 }
 
-__device__ __forceinline__ int8_t saturate_i8(float q, float qmax) {
+// two's-complement byte of an integer-valued float clamped to [-qmax, qmax]
+__device__ __forceinline__ uint32_t code_byte(float q, float qmax) {
     q = fminf(fmaxf(q, -qmax), qmax);
-    return (int8_t)(int)q;
+    return (uint32_t)__float_as_int(q + kRoundMagic) & 0xFFu;
 }
+__device__ __forceinline__ int8_t saturate_i8(float q, float qmax) { return (int8_t)code_byte(q, qmax); }
+
+// round every element of a vector to T (RNE) and widen again, two elements per conversion
+template <typename T, int E> struct RoundVec;
+template <int E> struct RoundVec<__half, E> {
+    static __device__ __forceinline__ void run(float (&f)[E]) {
+#pragma unroll
+        for (int i = 0; i < E; i += 2) { float2 t = __half22float2(__floats2half2_rn(f[i], f[i + 1])); f[i] = t.x; f[i + 1] = t.y; }
+    }
+};
+template <int E> struct RoundVec<__nv_bfloat16, E> {
+    static __device__ __forceinline__ void run(float (&f)[E]) {
+#pragma unroll
+        for (int i = 0; i < E; i += 2) { float2 t = __bfloat1622float2(__floats2bfloat162_rn(f[i], f[i + 1])); f[i] = t.x; f[i + 1] = t.y; }
+    }
+};
+template <int E> struct RoundVec<float, E> {
+    static __device__ __forceinline__ void run(float (&)[E]) {}
+};
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

@@ -19,7 +19,8 @@
 // overlaps the MMAs of tile i+1.  Every mbarrier wait is bounded: when a wait runs out the
 // kernel raises a status word and winds down instead of hanging.
 #include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
+#include <string.h>
 #include <type_traits>
 
 namespace samq {
@@ -38,7 +39,6 @@ constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + EPI_WARPS * 32;
 constexpr int ACC_BUFS = 2;
 constexpr int TMEM_COLS = ACC_BUFS * BN;       // 512: all of tensor memory
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;   // about 2 s
 
 struct __align__(8) Control {
     uint64_t full[STAGES];
@@ -50,84 +50,13 @@ struct __align__(8) Control {
 };
 
 constexpr int EPI_PARAM_FLOATS = ACC_BUFS * 2 * BN;      // w_scale and bias per accumulator buffer
+constexpr int STAGING_BYTES = 32 * 64;                   // per epilogue warp: 32 rows x 64 bytes (64-byte swizzle)
 constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES +
+                              (size_t)EPI_WARPS * STAGING_BYTES +
                               EPI_PARAM_FLOATS * sizeof(float) + sizeof(Control);
 
-// ---- PTX wrappers ------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait. Returns false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 255u) == 0) {
-            if (*abort_flag != 0) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; return false; }
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-                 " [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+using namespace sm100;
 
-// Shared-memory matrix descriptor for a K-major operand tile whose rows are 128 bytes wide and
-// stored with the 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B):
-// start address >> 4 in bits [0,14); leading byte offset (unused for this layout) = 1 in [16,30);
-// stride byte offset = 1024 B (8 rows) >> 4 in [32,46); descriptor version 1 in [46,48);
-// layout type 2 (128-byte swizzle) in [61,64).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-    uint64_t d = (uint64_t)((smem_addr >> 4) & 0x3FFFu);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
 // Instruction descriptor for kind::i8: D = S32 (2) in bits [4,6); A, B = signed 8-bit (1) in
 // [7,10) and [10,13); both operands K-major (bits 15, 16 = 0); N >> 3 in [17,23); M >> 4 in [24,29).
 constexpr uint32_t kInstrDesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -157,6 +86,7 @@ struct GemmParams {
     void* out; int64_t ldo;
     int activation;
     int vec_ok;                                // rows of out/residual are 16-byte aligned
+    int tma_store;                             // out is described by map_out: store through shared memory + TMA
     int32_t* status;
 };
 
@@ -164,13 +94,14 @@ struct GemmParams {
 template <typename OutT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const GemmParams p)
+               const __grid_constant__ CUtensorMap map_out, const GemmParams p)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
     uint8_t* tiles = smem_raw + pad;                                   // 1024-byte aligned
-    float* epi_params = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES);
+    uint8_t* staging = tiles + (size_t)STAGES * STAGE_BYTES;            // 1024-byte aligned too
+    float* epi_params = reinterpret_cast<float*>(staging + (size_t)EPI_WARPS * STAGING_BYTES);
     Control* ctl = reinterpret_cast<Control*>(epi_params + EPI_PARAM_FLOATS);
     volatile uint32_t* abort_flag = &ctl->abort_flag;
 
@@ -188,6 +119,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_out) : "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -286,6 +218,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if constexpr (!std::is_same<OutT, int32_t>::value) {
                 if (p.a_scale != nullptr && row_ok) a_s = p.a_scale[(int64_t)row * p.a_stride];
             }
+            const uint32_t stage_addr = smem_u32(staging + (size_t)ew * STAGING_BYTES);
+            uint8_t* stage_ptr = staging + (size_t)ew * STAGING_BYTES;
+            const int rr = quad * 32 + lane;                       // row inside the tile
+            const uint32_t swz = (uint32_t)((lane >> 1) & 3);     // 64-byte swizzle: 16-byte slot ^= bits [7:8] of the offset
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 const int col0 = half_n * 128 + c * 32;
@@ -293,18 +229,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + col0), r);
                 tmem_ld_wait();
                 const int n_first = n0 + col0;
-                if (!row_ok || n_first >= p.N) continue;
+                if (n_first >= p.N) continue;                       // warp-uniform
                 const int n_valid = min(32, p.N - n_first);
+                constexpr int PER16 = 16 / (int)sizeof(OutT);       // elements per 16-byte vector
+                constexpr int NVEC = 32 / PER16;                    // 16-byte vectors per 32 columns: 4 or 8
+                uint4 packed[NVEC];
                 if constexpr (std::is_same<OutT, int32_t>::value) {
-                    int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)row * p.ldo + n_first;
-                    if (p.vec_ok && n_valid == 32) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            reinterpret_cast<uint4*>(o)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) if (j < n_valid) o[j] = (int32_t)r[j];
-                    }
+                    for (int j = 0; j < 8; ++j) packed[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
                 } else {
                     float y[32];
 #pragma unroll
@@ -320,35 +252,58 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 32; ++j) y[j] = gelu_erf(y[j]);
                     }
+                    if (p.residual != nullptr && row_ok) {
+                        const OutT* res = reinterpret_cast<const OutT*>(p.residual) + (int64_t)row * p.ldr + n_first;
+                        if (p.vec_ok && n_valid == 32) {
+#pragma unroll
+                            for (int j = 0; j < NVEC; ++j) {
+                                OutT tmp[PER16];
+                                *reinterpret_cast<uint4*>(tmp) = *reinterpret_cast<const uint4*>(res + j * PER16);
+#pragma unroll
+                                for (int e = 0; e < PER16; ++e) y[j * PER16 + e] += OutOps<OutT>::up(tmp[e]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) if (j < n_valid) y[j] += OutOps<OutT>::up(res[j]);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < NVEC; ++j) {
+                        OutT tmp[PER16];
+#pragma unroll
+                        for (int e = 0; e < PER16; ++e) tmp[e] = OutOps<OutT>::down(y[j * PER16 + e]);
+                        packed[j] = *reinterpret_cast<const uint4*>(tmp);
+                    }
+                }
+                if (p.tma_store) {
+                    // rows of 64 bytes per box: 32 columns of a 2-byte type, 16 columns of a 4-byte type
+#pragma unroll
+                    for (int part = 0; part < NVEC / 4; ++part) {
+                        if (lane == 0) bulk_wait_read0();            // the previous box has left shared memory
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            *reinterpret_cast<uint4*>(stage_ptr + lane * 64 + (((uint32_t)j ^ swz) << 4)) = packed[part * 4 + j];
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&map_out, stage_addr, n_first + part * (64 / (int)sizeof(OutT)), m0 + quad * 32);
+                            bulk_commit();
+                        }
+                    }
+                } else if (row_ok) {
                     OutT* o = reinterpret_cast<OutT*>(p.out) + (int64_t)row * p.ldo + n_first;
-                    const OutT* res = p.residual != nullptr
-                        ? reinterpret_cast<const OutT*>(p.residual) + (int64_t)row * p.ldr + n_first : nullptr;
-                    constexpr int PER16 = 16 / (int)sizeof(OutT);
                     if (p.vec_ok && n_valid == 32) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += PER16) {
-                            OutT tmp[PER16];
-                            if (res != nullptr) {
-                                *reinterpret_cast<uint4*>(tmp) = *reinterpret_cast<const uint4*>(res + j);
-#pragma unroll
-                                for (int e = 0; e < PER16; ++e) y[j + e] += OutOps<OutT>::up(tmp[e]);
-                            }
-#pragma unroll
-                            for (int e = 0; e < PER16; ++e) tmp[e] = OutOps<OutT>::down(y[j + e]);
-                            *reinterpret_cast<uint4*>(o + j) = *reinterpret_cast<const uint4*>(tmp);
-                        }
+                        for (int j = 0; j < NVEC; ++j) reinterpret_cast<uint4*>(o)[j] = packed[j];
                     } else {
+                        const OutT* src = reinterpret_cast<const OutT*>(packed);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (j < n_valid) {
-                                float v = y[j];
-                                if (res != nullptr) v += OutOps<OutT>::up(res[j]);
-                                o[j] = OutOps<OutT>::down(v);
-                            }
-                        }
+                        for (int j = 0; j < 32; ++j) if (j < n_valid) o[j] = src[j];
                     }
                 }
             }
+            (void)rr;
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
@@ -356,6 +311,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     }
 
+    if (warp >= 2 && lane == 0 && p.tma_store) bulk_wait0();          // this thread's TMA stores have completed
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
@@ -411,12 +367,27 @@ int sm_count() {
     return cached;
 }
 
+// [M, N] output with row stride ldo elements of esize bytes; box = 32 rows x 64 bytes, 64-byte swizzle.
+int make_out_map(CUtensorMap* map, void* base, int64_t M, int64_t N, int64_t ldo, int esize) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    cuuint64_t strides[1] = {(cuuint64_t)(ldo * esize)};
+    cuuint32_t box[2] = {(cuuint32_t)(64 / esize), 32u};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, base, dims,
+                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
+    return SAMQ_OK;
+}
+
 template <typename OutT>
-int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, const GemmParams& p, cudaStream_t st) {
     SAMQ_CUDA_TRY(cudaFuncSetAttribute(gemm_i8_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    gemm_i8_kernel<OutT><<<grid, THREADS, SMEM_BYTES, st>>>(ma, mw, p);
+    gemm_i8_kernel<OutT><<<grid, THREADS, SMEM_BYTES, st>>>(ma, mw, mo, p);
     SAMQ_CUDA_TRY(cudaGetLastError());
     return SAMQ_OK;
 }
@@ -463,12 +434,22 @@ int gemm_i8_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
     const size_t esz = (out_dtype == SAMQ_F16 || out_dtype == SAMQ_BF16) ? 2 : 4;
     p.vec_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((ldo * esz) % 16 == 0) &&
                (residual == nullptr || (((reinterpret_cast<uintptr_t>(residual) & 15) == 0) && ((ldr * esz) % 16 == 0)));
+    // the coalesced path: tiles leave through shared memory and TMA stores, which need a 16-byte
+    // aligned base and row pitch; anything else takes direct per-thread stores
+    CUtensorMap mo;
+    memset(&mo, 0, sizeof(mo));
+    p.tma_store = 0;
+    if (((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((ldo * esz) % 16 == 0)) {
+        rc = make_out_map(&mo, out, M, N, ldo, (int)esz);
+        if (rc != SAMQ_OK) return rc;
+        p.tma_store = 1;
+    }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (out_dtype) {
-    case SAMQ_F16:  return launch_gemm<__half>(ma, mw, p, st);
-    case SAMQ_BF16: return launch_gemm<__nv_bfloat16>(ma, mw, p, st);
-    case SAMQ_F32:  return launch_gemm<float>(ma, mw, p, st);
-    case SAMQ_I32:  return launch_gemm<int32_t>(ma, mw, p, st);
+    case SAMQ_F16:  return launch_gemm<__half>(ma, mw, mo, p, st);
+    case SAMQ_BF16: return launch_gemm<__nv_bfloat16>(ma, mw, mo, p, st);
+    case SAMQ_F32:  return launch_gemm<float>(ma, mw, mo, p, st);
+    case SAMQ_I32:  return launch_gemm<int32_t>(ma, mw, mo, p, st);
     default: return fail(SAMQ_ERR_BAD_ARG, "unknown out_dtype %d", out_dtype);
     }
 }

@@ -14,7 +14,7 @@ import torch
 
 from . import _lib
 from ._lib import (ACT_GELU, ACT_NONE, BF16, F16, F32, GRAN_GROUP, GRAN_ROW, GRAN_TENSOR, HAD_FULL,
-                   HAD_NONE, HAD_PARTIAL, I32, HadamardSpec)
+                   HAD_NONE, HAD_PARTIAL, I32, HadamardSpec, QuantPrologue)
 
 _DTYPE_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
 _OUT_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32, torch.int32: I32}
@@ -162,12 +162,18 @@ def _spec(had: Optional[Hadamard], keep: list) -> Optional[HadamardSpec]:
 
 def quantize(x: torch.Tensor, granularity: int = GRAN_ROW, group_size: Optional[int] = None,
              divisor: Optional[torch.Tensor] = None, hadamard: Optional[Hadamard] = None,
-             codes: bool = True, fake_quant: bool = False, transformed: bool = False, n_bits: int = 8):
+             codes: bool = True, fake_quant: bool = False, transformed: bool = False, n_bits: int = 8,
+             row_map: Optional[torch.Tensor] = None, layer_norm=None, as_dtype: Optional[torch.dtype] = None):
     """Run K1 on ``x`` ([..., K]; fp16 / bf16 / fp32).
 
     Returns a dict with the requested outputs: ``q`` int8 [..., K], ``scale`` fp32
-    ([...] | [1] | [..., K/group]), ``fq`` (fake-quantized, x.dtype) and ``tx`` (input after
-    divisor / Hadamard, x.dtype).
+    ([...] | [1] | [..., K/group]), ``fq`` (fake-quantized) and ``tx`` (input after the
+    prologue / divisor / Hadamard), both in the tensor dtype.
+
+    Prologue fused into the same kernel (see ``samq_quant_prologue``): ``row_map`` int32 [M_out]
+    gathers source rows (negative = a zero row) and makes the outputs ``[M_out, ...]``;
+    ``layer_norm=(weight, bias, eps)`` normalises each source row first; ``as_dtype=torch.float16``
+    reads a bf16 ``x`` as the fp16 tensor the model would cast it to.
     """
     _require_cuda(x, "x")
     if x.dtype not in _DTYPE_CODE:
@@ -175,6 +181,29 @@ def quantize(x: torch.Tensor, granularity: int = GRAN_ROW, group_size: Optional[
     lib = _lib.load()
     lead = x.shape[:-1]
     x2, M, K, ldx = _as_rows(x)
+    tdtype = x.dtype
+    pro = None
+    keep_pro = []
+    if row_map is not None or layer_norm is not None or (as_dtype is not None and as_dtype != x.dtype):
+        pro = QuantPrologue(0, 0, 0, 0.0, -1)
+        if row_map is not None:
+            _require_cuda(row_map, "row_map")
+            if row_map.dtype != torch.int32 or not row_map.is_contiguous():
+                raise TypeError("row_map must be a contiguous int32 tensor")
+            pro.row_map = row_map.data_ptr()
+            M = row_map.numel()
+            lead = (M,)
+        if as_dtype is not None and as_dtype != x.dtype:
+            if not (x.dtype == torch.bfloat16 and as_dtype == torch.float16):
+                raise TypeError("as_dtype only reads bf16 storage as an fp16 tensor")
+            pro.src_dtype = _DTYPE_CODE[x.dtype]
+            tdtype = as_dtype
+        if layer_norm is not None:
+            ln_w, ln_b, ln_eps = layer_norm
+            ln_w = ln_w.detach().to(device=x.device, dtype=tdtype).contiguous()
+            ln_b = ln_b.detach().to(device=x.device, dtype=tdtype).contiguous()
+            keep_pro += [ln_w, ln_b]
+            pro.ln_weight, pro.ln_bias, pro.ln_eps = ln_w.data_ptr(), ln_b.data_ptr(), float(ln_eps)
     g = int(group_size) if granularity == GRAN_GROUP else 0
     if granularity == GRAN_GROUP:
         if not isinstance(group_size, int):
@@ -190,21 +219,22 @@ def quantize(x: torch.Tensor, granularity: int = GRAN_ROW, group_size: Optional[
         scale = torch.empty((1,), dtype=torch.float32, device=dev)
     else:
         scale = torch.empty((M, K // g), dtype=torch.float32, device=dev)
-    fq = torch.empty((M, K), dtype=x.dtype, device=dev) if fake_quant else None
-    tx = torch.empty((M, K), dtype=x.dtype, device=dev) if transformed else None
+    fq = torch.empty((M, K), dtype=tdtype, device=dev) if fake_quant else None
+    tx = torch.empty((M, K), dtype=tdtype, device=dev) if transformed else None
     ws_bytes = int(lib.samq_quant_workspace_bytes(granularity))
     ws = torch.empty((max(ws_bytes, 4) // 4,), dtype=torch.int32, device=dev) if ws_bytes else None
     keep = []
     if divisor is not None:
-        divisor = divisor.to(device=dev, dtype=x.dtype).contiguous()
+        divisor = divisor.to(device=dev, dtype=tdtype).contiguous()
         if divisor.numel() != K:
             raise ValueError("divisor must have K elements")
     spec = _spec(hadamard, keep)
     nbytes = M * (K * x.element_size() + (K if codes else 0) + (K * x.element_size() if fake_quant else 0)
                   + (K * x.element_size() if transformed else 0)) + scale.numel() * 4
     with torch.cuda.device(dev), _Timed("act_quant", nbytes, 3 if granularity == GRAN_TENSOR else 1):
-        _lib.check(lib.samq_act_quant_i8(
-            _ptr(x2), _DTYPE_CODE[x.dtype], M, K, ldx, _ptr(divisor),
+        _lib.check(lib.samq_act_quant_i8_ex(
+            _ptr(x2), _DTYPE_CODE[tdtype], M, K, ldx,
+            ctypes.byref(pro) if pro is not None else None, _ptr(divisor),
             ctypes.byref(spec) if spec is not None else None,
             granularity, g, int(n_bits), _ptr(q), _ptr(scale), _ptr(fq), _ptr(tx),
             _ptr(ws), ws_bytes, _stream()))
@@ -308,3 +338,61 @@ def gemm_i8(a_q: torch.Tensor, w_q: torch.Tensor,
             _ptr(bias), _ptr(residual), ldr, activation,
             _ptr(out), _OUT_CODE[out_dtype], N, _ptr(status_word(dev)), _stream()))
     return out.view(*lead, N)
+
+
+def rel_pos_products(qkv: torch.Tensor, num_heads: int, rel_pos_h: torch.Tensor, rel_pos_w: torch.Tensor) -> torch.Tensor:
+    """rel_all[head, token, j] = q[token, head, :] . table[j, :] for the rows of ``rel_pos_h``
+    followed by those of ``rel_pos_w`` (pitch rounded up to 8): one batched tensor-core GEMM on
+    strided views of ``qkv`` [tokens, 3C], no copy of q."""
+    tokens, three_c = qkv.shape
+    d = three_c // 3 // num_heads
+    rows = rel_pos_h.shape[0] + rel_pos_w.shape[0]
+    J = (rows + 7) // 8 * 8
+    tab = torch.zeros((J, d), dtype=qkv.dtype, device=qkv.device)
+    tab[:rel_pos_h.shape[0]] = rel_pos_h.detach().to(qkv.dtype)
+    tab[rel_pos_h.shape[0]:rows] = rel_pos_w.detach().to(qkv.dtype)
+    q_heads = qkv.view(tokens, 3, num_heads, d)[:, 0].permute(1, 0, 2)          # [heads, tokens, d], strides (d, 3C, 1)
+    return torch.matmul(q_heads, tab.t())                                        # [heads, tokens, J]
+
+
+def attn_window_prep(qkv: torch.Tensor, H: int, W: int, num_heads: int, rel_pos_h: torch.Tensor,
+                     rel_pos_w: torch.Tensor, scale: float, width: int):
+    """Augmented attention inputs for windows (``samq_attn_window_prep``): from ``qkv``
+    [tokens, 3C] returns ``(q_aug, k_aug)``, each [tokens, heads, width]."""
+    _require_cuda(qkv, "qkv")
+    lib = _lib.load()
+    tokens, three_c = qkv.shape
+    d = three_c // 3 // num_heads
+    if not qkv.is_contiguous():
+        raise ValueError("qkv must be contiguous")
+    if rel_pos_h.shape != (2 * H - 1, d) or rel_pos_w.shape != (2 * W - 1, d):
+        raise ValueError("relative position tables must be [2H-1, d] and [2W-1, d]")
+    rel_all = rel_pos_products(qkv, num_heads, rel_pos_h, rel_pos_w)
+    if not rel_all.is_contiguous():
+        rel_all = rel_all.contiguous()
+    qa = torch.empty((tokens, num_heads, width), dtype=qkv.dtype, device=qkv.device)
+    ka = torch.empty((tokens, num_heads, width), dtype=qkv.dtype, device=qkv.device)
+    with torch.cuda.device(qkv.device), _Timed("attn_prep", tokens * num_heads * (2 * d + 2 * width) * qkv.element_size()):
+        _lib.check(lib.samq_attn_window_prep(_ptr(qkv), _ptr(rel_all), _DTYPE_CODE[qkv.dtype], tokens, rel_all.shape[-1],
+                                             H, W, num_heads, d, float(scale), width, _ptr(qa), _ptr(ka), _stream()))
+    return qa, ka
+
+
+def attn_rel_bias(qkv: torch.Tensor, images: int, H: int, W: int, num_heads: int, rel_pos_h: torch.Tensor,
+                  rel_pos_w: torch.Tensor) -> torch.Tensor:
+    """Explicit relative-position bias [images, heads, H*W, H*W] for global attention
+    (``samq_attn_rel_bias``) from ``qkv`` [images*H*W, 3C]."""
+    _require_cuda(qkv, "qkv")
+    lib = _lib.load()
+    tokens, three_c = qkv.shape
+    L = H * W
+    if tokens != images * L or not qkv.is_contiguous():
+        raise ValueError("qkv must be a contiguous [images*H*W, 3C] tensor")
+    rel_all = rel_pos_products(qkv, num_heads, rel_pos_h, rel_pos_w)
+    if not rel_all.is_contiguous():
+        rel_all = rel_all.contiguous()
+    bias = torch.empty((images, num_heads, L, L), dtype=qkv.dtype, device=qkv.device)
+    with torch.cuda.device(qkv.device), _Timed("attn_bias", bias.numel() * bias.element_size()):
+        _lib.check(lib.samq_attn_rel_bias(_ptr(rel_all), _DTYPE_CODE[qkv.dtype], images, rel_all.shape[-1], H, W, num_heads,
+                                          _ptr(bias), _stream()))
+    return bias

@@ -149,6 +149,32 @@ class ActQuantWrapper(torch.nn.Module):
         self._pre_k = int(K)
         self._pre_hadk = hadK
 
+    def can_fuse_prologue(self) -> bool:
+        return bool(self.quantize_input) and self.qweight is not None and \
+            self.act_quant_name in ("per_token", "per_group_token")
+
+    @torch.no_grad()
+    def forward_fused(self, x, row_map=None, layer_norm=None, as_dtype=None, residual=None,
+                      activation=None, out_dtype=None):
+        """Same contract as ``W8A8Linear.forward_fused``.  An online Hadamard and a LayerNorm are
+        two passes of K1 (normalise + gather, then transform + quantize); otherwise one."""
+        spec = self._hadamard_spec(x)
+        tdtype = as_dtype or x.dtype
+        if spec is not None and (layer_norm is not None):
+            x = ops.quantize(x, ops.GRAN_ROW, codes=False, transformed=True, row_map=row_map,
+                             layer_norm=layer_norm, as_dtype=as_dtype)["tx"]
+            row_map, layer_norm, as_dtype = None, None, None
+        a_gran = ops.ACT_GRANULARITY[self.act_quant_name]
+        xa = ops.quantize(x, a_gran, self.group_size, hadamard=spec, n_bits=self.n_bits, row_map=row_map,
+                          layer_norm=layer_norm, as_dtype=as_dtype)
+        y = ops.gemm_i8(xa["q"], self.qweight, xa["scale"], self.w_scale, a_gran,
+                        ops.WEIGHT_GRANULARITY[self.weight_quant_name], self.group_size or 0,
+                        bias=self.bias, residual=residual,
+                        activation=ACT_GELU if activation == "gelu" else ACT_NONE, out_dtype=out_dtype or tdtype)
+        if self.quantize_output:
+            y = self.act_quant(y)
+        return y
+
     @torch.no_grad()
     def forward(self, x, residual=None, activation=None, out_dtype=None):
         x_dtype = x.dtype

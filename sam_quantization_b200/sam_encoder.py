@@ -91,25 +91,36 @@ def get_rel_pos(q_size: int, k_size: int, rel_pos: torch.Tensor) -> torch.Tensor
     return rel_pos[rel.long()]
 
 
-def decomposed_rel_pos_bias(q: torch.Tensor, rel_pos_h: torch.Tensor, rel_pos_w: torch.Tensor,
-                            q_size: Tuple[int, int], k_size: Tuple[int, int]) -> torch.Tensor:
-    """Additive attention bias [B*heads, q_h*q_w, k_h*k_w] from the decomposed relative position
-    embeddings: bias[(qh,qw),(kh,kw)] = q . Rh[qh-kh] + q . Rw[qw-kw]."""
-    q_h, q_w = q_size
-    k_h, k_w = k_size
-    Rh = get_rel_pos(q_h, k_h, rel_pos_h).to(q.dtype)
-    Rw = get_rel_pos(q_w, k_w, rel_pos_w).to(q.dtype)
-    B, _, dim = q.shape
-    r_q = q.reshape(B, q_h, q_w, dim)
-    rel_h = torch.einsum("bhwc,hkc->bhwk", r_q, Rh)
-    rel_w = torch.einsum("bhwc,wkc->bhwk", r_q, Rw)
-    bias = rel_h[:, :, :, :, None] + rel_w[:, :, :, None, :]
-    return bias.reshape(B, q_h * q_w, k_h * k_w)
+_WINDOW_MAPS = {}
+
+
+def window_row_maps(B: int, H: int, W: int, window_size: int, device) -> Tuple[torch.Tensor, torch.Tensor, Tuple[int, int]]:
+    """Index form of ``window_partition`` / ``window_unpartition`` for token rows.
+
+    ``part[r]``  : for row r of the window-ordered, zero-padded layout [B*nW*ws*ws], the row of the
+                   [B*H*W] token layout it copies, or -1 for a padding row.
+    ``unpart[t]``: for token row t, its row in the window-ordered layout.
+    Both int32 on ``device``; cached per shape."""
+    key = (B, H, W, window_size, str(device))
+    if key not in _WINDOW_MAPS:
+        tok = torch.arange(B * H * W, dtype=torch.float32).view(B, H, W, 1) + 1.0     # 0 marks padding
+        win, (Hp, Wp) = window_partition(tok, window_size)
+        part = (win.reshape(-1).to(torch.int64) - 1).to(torch.int32)
+        pos = torch.arange(part.numel(), dtype=torch.float32).view(-1, window_size, window_size, 1)
+        unpart = window_unpartition(pos, window_size, (Hp, Wp), (H, W)).reshape(-1).to(torch.int32)
+        _WINDOW_MAPS[key] = (part.to(device), unpart.to(device), (Hp, Wp))
+    return _WINDOW_MAPS[key]
 
 
 class Attention(nn.Module):
     """Multi-head attention with a fused qkv projection and decomposed relative position bias.
-    ``attn_dtype`` is the type the softmax(QK^T)V math runs in (bf16 in the W8A8 configs)."""
+    ``attn_dtype`` is the type the softmax(QK^T)V math runs in (bf16 in the W8A8 configs).
+
+    The bias ``rel_h[q, kh] + rel_w[q, kw]`` is never materialised for windows: the query gets
+    ``rel_h[q, :]`` and ``rel_w[q, :]`` appended to its features and the key gets one-hot codes of
+    its row and column, so that ``q' . k' = scale * q . k + rel_h[q, kh] + rel_w[q, kw]`` and a
+    stock fused attention kernel applies (head width d + H + W <= 128).  Global attention
+    (64 x 64 keys) would need 128 extra features; it adds an explicit bias instead."""
 
     def __init__(self, dim: int, num_heads: int = 8, qkv_bias: bool = True, use_rel_pos: bool = False,
                  rel_pos_zero_init: bool = True, input_size: Optional[Tuple[int, int]] = None):
@@ -121,41 +132,103 @@ class Attention(nn.Module):
         self.proj = nn.Linear(dim, dim)
         self.use_rel_pos = use_rel_pos
         self.attn_dtype: Optional[torch.dtype] = None
-        self.global_chunk = 4            # images per SDPA call when the bias is [heads, 4096, 4096]
+        self.global_chunk = 4            # images per attention call when the bias is [heads, 4096, 4096]
+        self.native_prep = True          # build the attention inputs with the library's CUDA kernels when possible
+        self._onehot = {}
         if use_rel_pos:
             assert input_size is not None
             self.rel_pos_h = nn.Parameter(torch.zeros(2 * input_size[0] - 1, head_dim))
             self.rel_pos_w = nn.Parameter(torch.zeros(2 * input_size[1] - 1, head_dim))
 
-    def _sdpa(self, q, k, v, H, W):
-        # q, k, v: [B, heads, HW, d]
-        B, nh, L, d = q.shape
-        bias = None
-        if self.use_rel_pos:
-            bias = decomposed_rel_pos_bias(q.reshape(B * nh, L, d), self.rel_pos_h, self.rel_pos_w, (H, W), (H, W))
-            bias = bias.view(B, nh, L, L)
-        return F.scaled_dot_product_attention(q, k, v, attn_mask=bias, scale=self.scale)
+    # -- relative position terms -------------------------------------------------------------
+    def _rel_terms(self, q: torch.Tensor, H: int, W: int):
+        """q [B, H*W, nh, d] (any strides) -> rel_h [B, H, W, nh, H], rel_w [B, H, W, nh, W]."""
+        B, L, nh, d = q.shape
+        Rh = get_rel_pos(H, H, self.rel_pos_h).to(q.dtype)
+        Rw = get_rel_pos(W, W, self.rel_pos_w).to(q.dtype)
+        r_q = q.reshape(B, H, W, nh, d)
+        rel_h = torch.einsum("bhwnc,hkc->bhwnk", r_q, Rh)
+        rel_w = torch.einsum("bhwnc,wkc->bhwnk", r_q, Rw)
+        return rel_h, rel_w
 
-    def attend(self, qkv: torch.Tensor, B: int, H: int, W: int) -> torch.Tensor:
-        """qkv [B, H*W, 3*C] -> attention output [B, H, W, C]."""
-        L = H * W
-        qkv = qkv.reshape(B, L, 3, self.num_heads, -1).permute(2, 0, 3, 1, 4)
-        q, k, v = qkv.unbind(0)
-        step = B if L <= 1024 else max(1, self.global_chunk)
-        outs = [self._sdpa(q[i:i + step], k[i:i + step], v[i:i + step], H, W) for i in range(0, B, step)]
-        x = outs[0] if len(outs) == 1 else torch.cat(outs, 0)
-        return x.permute(0, 2, 1, 3).reshape(B, H, W, -1)
+    def _key_codes(self, H: int, W: int, width: int, dtype, device) -> torch.Tensor:
+        key = (H, W, width, dtype, str(device))
+        if key not in self._onehot:
+            kh = torch.arange(H).view(H, 1).expand(H, W).reshape(-1)
+            kw = torch.arange(W).view(1, W).expand(H, W).reshape(-1)
+            codes = torch.zeros(H * W, width)
+            codes[torch.arange(H * W), kh] = 1.0
+            codes[torch.arange(H * W), H + kw] = 1.0
+            self._onehot[key] = codes.to(device=device, dtype=dtype)
+        return self._onehot[key]
+
+    def _native(self, qkv: torch.Tensor, d: int, H: int, W: int) -> bool:
+        if not (self.native_prep and qkv.is_cuda and qkv.dtype in (torch.float16, torch.bfloat16) and qkv.is_contiguous()):
+            return False
+        if d % 8 != 0:
+            return False
+        return d + H + W <= 128 or (H <= 64 and W % 8 == 0)
+
+    def attend_flat(self, qkv: torch.Tensor, B: int, H: int, W: int) -> torch.Tensor:
+        """qkv [B*H*W, 3C] -> attention output [B*H*W, C] (same dtype), heads side by side."""
+        L, nh = H * W, self.num_heads
+        qkv5 = qkv.view(B, L, 3, nh, -1)
+        q, k, v = qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2]          # [B, L, nh, d] strided views
+        d = q.shape[-1]
+        if not self.use_rel_pos:
+            out = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), scale=self.scale)
+            return out.transpose(1, 2).reshape(B * L, nh * d)
+        extra = H + W
+        if self._native(qkv, d, H, W):
+            from . import ops
+            if d + extra <= 128:
+                width = (d + extra + 7) // 8 * 8
+                qa, ka = ops.attn_window_prep(qkv, H, W, nh, self.rel_pos_h, self.rel_pos_w, self.scale, width)
+                out = F.scaled_dot_product_attention(qa.view(B, L, nh, width).transpose(1, 2), ka.view(B, L, nh, width).transpose(1, 2),
+                                                     v.transpose(1, 2), scale=1.0)
+                return out.transpose(1, 2).reshape(B * L, nh * d)
+            outs = []
+            step = max(1, self.global_chunk)
+            for i in range(0, B, step):
+                b = min(step, B - i)
+                bias = ops.attn_rel_bias(qkv[i * L:(i + b) * L], b, H, W, nh, self.rel_pos_h, self.rel_pos_w)
+                o = F.scaled_dot_product_attention(q[i:i + b].transpose(1, 2), k[i:i + b].transpose(1, 2),
+                                                   v[i:i + b].transpose(1, 2), attn_mask=bias, scale=self.scale)
+                outs.append(o.transpose(1, 2).reshape(b * L, nh * d))
+            return outs[0] if len(outs) == 1 else torch.cat(outs, 0)
+        rel_h, rel_w = self._rel_terms(q, H, W)
+        if d + extra <= 128:
+            width = (d + extra + 7) // 8 * 8
+            qa = q.new_zeros((B, L, nh, width)) if width > d + extra else q.new_empty((B, L, nh, width))
+            qa[..., :d] = q * self.scale
+            qa[..., d:d + H] = rel_h.reshape(B, L, nh, H)
+            qa[..., d + H:d + extra] = rel_w.reshape(B, L, nh, W)
+            ka = q.new_empty((B, L, nh, width))
+            ka[..., :d] = k
+            ka[..., d:] = self._key_codes(H, W, width - d, q.dtype, q.device).view(1, L, 1, width - d)
+            out = F.scaled_dot_product_attention(qa.transpose(1, 2), ka.transpose(1, 2), v.transpose(1, 2), scale=1.0)
+            return out.transpose(1, 2).reshape(B * L, nh * d)
+        outs = []
+        step = max(1, self.global_chunk)
+        for i in range(0, B, step):
+            rh, rw = rel_h[i:i + step], rel_w[i:i + step]                  # [b, H, W, nh, H|W]
+            b = rh.shape[0]
+            bias = rh.permute(0, 3, 1, 2, 4).reshape(b, nh, L, H, 1) + rw.permute(0, 3, 1, 2, 4).reshape(b, nh, L, 1, W)
+            o = F.scaled_dot_product_attention(q[i:i + step].transpose(1, 2), k[i:i + step].transpose(1, 2),
+                                               v[i:i + step].transpose(1, 2), attn_mask=bias.view(b, nh, L, L), scale=self.scale)
+            outs.append(o.transpose(1, 2).reshape(b * L, nh * d))
+        return outs[0] if len(outs) == 1 else torch.cat(outs, 0)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        B, H, W, _ = x.shape
+        B, H, W, C = x.shape
         dt = x.dtype
         adt = self.attn_dtype or dt
         if _fusable(self.qkv):
             qkv = self.qkv(x, out_dtype=adt)                 # the GEMM epilogue stores bf16 directly
         else:
             qkv = self.qkv(x).to(adt)
-        x = self.attend(qkv, B, H, W).to(dt)
-        return self.proj(x)
+        o = self.attend_flat(qkv.reshape(B * H * W, 3 * C), B, H, W).to(dt)
+        return self.proj(o.view(B, H, W, C))
 
 
 class Block(nn.Module):
@@ -171,8 +244,52 @@ class Block(nn.Module):
         self.norm2 = norm_layer(dim)
         self.mlp = MLPBlock(embedding_dim=dim, mlp_dim=int(dim * mlp_ratio), act=act_layer)
         self.window_size = window_size
+        self.fuse = True                 # allow the fused quantized path when the linears support it
+
+    # -- fused quantized path --------------------------------------------------------------------
+    def _can_fuse(self, x: torch.Tensor) -> bool:
+        if not (self.fuse and x.is_cuda and x.dim() == 4):
+            return False
+        lins = (self.attn.qkv, self.attn.proj, self.mlp.lin1, self.mlp.lin2)
+        if not all(hasattr(m, "forward_fused") and m.can_fuse_prologue() for m in lins):
+            return False
+        if not (isinstance(self.norm1, nn.LayerNorm) and isinstance(self.norm2, nn.LayerNorm)):
+            return False
+        if not (isinstance(self.mlp.act, nn.GELU) and self.mlp.act.approximate == "none"):
+            return False
+        # an online dense rotation in front of qkv / lin1 must have been folded into the kernels
+        for holder, lin in ((self.attn, self.attn.qkv), (self.mlp, self.mlp.lin1)):
+            if getattr(holder, "Q", None) is not None and getattr(lin, "pre_signs", None) is None:
+                return False
+        return True
+
+    def _forward_fused(self, x: torch.Tensor) -> torch.Tensor:
+        """The block with LayerNorm, window partition / unpartition, GELU, both residual adds and
+        the dtype casts around attention folded into the quantization and GEMM kernels:
+        K1(norm1 + window gather) -> K2(qkv) -> attention -> K1(window scatter as a gather) ->
+        K2(proj + residual) -> K1(norm2) -> K2(lin1 + GELU) -> K1 -> K2(lin2 + residual)."""
+        B, H, W, C = x.shape
+        x2 = x.reshape(B * H * W, C)
+        adt = self.attn.attn_dtype or x.dtype
+        ln1 = (self.norm1.weight, self.norm1.bias, self.norm1.eps)
+        ln2 = (self.norm2.weight, self.norm2.bias, self.norm2.eps)
+        if self.window_size > 0:
+            part, unpart, (Hp, Wp) = window_row_maps(B, H, W, self.window_size, x.device)
+            ws = self.window_size
+            qkv = self.attn.qkv.forward_fused(x2, row_map=part, layer_norm=ln1, out_dtype=adt)
+            o = self.attn.attend_flat(qkv, qkv.shape[0] // (ws * ws), ws, ws)
+            y = self.attn.proj.forward_fused(o, row_map=unpart, as_dtype=x.dtype, residual=x2)
+        else:
+            qkv = self.attn.qkv.forward_fused(x2, layer_norm=ln1, out_dtype=adt)
+            o = self.attn.attend_flat(qkv, B, H, W)
+            y = self.attn.proj.forward_fused(o, as_dtype=x.dtype, residual=x2)
+        h = self.mlp.lin1.forward_fused(y, layer_norm=ln2, activation="gelu")
+        out = self.mlp.lin2.forward_fused(h, residual=y)
+        return out.view(B, H, W, C)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self._can_fuse(x):
+            return self._forward_fused(x)
         shortcut = x
         x = self.norm1(x)
         if self.window_size > 0:

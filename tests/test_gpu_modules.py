@@ -242,3 +242,26 @@ def test_tiny_encoder_quarot(cuda_device):
     assert cosine(a, b) >= 0.999
     # rotation is an exact change of basis: the quantized rotated model still tracks the float model
     assert cosine(a, y_float) >= 0.99
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("H,W,dim,nh", [(14, 14, 160, 2), (4, 4, 64, 4), (14, 14, 128, 2), (16, 16, 64, 2), (64, 64, 80, 1)])
+def test_attention_prep_kernels_against_torch_path(cuda_device, dtype, H, W, dim, nh):
+    """The CUDA kernels that build the attention inputs (augmented q / k rows for windows, the
+    explicit bias for global attention) against the same attention written with torch ops."""
+    from sam_quantization_b200.sam_encoder import Attention
+    torch.manual_seed(H * 100 + dim)
+    attn = Attention(dim, nh, use_rel_pos=True, input_size=(H, W)).to(cuda_device, dtype)
+    with torch.no_grad():
+        attn.rel_pos_h.normal_(0, 0.3)
+        attn.rel_pos_w.normal_(0, 0.3)
+        B = 3
+        qkv = torch.randn(B * H * W, 3 * dim, device=cuda_device, dtype=dtype)
+        attn.native_prep = True
+        a = attn.attend_flat(qkv, B, H, W)
+        attn.native_prep = False
+        b = attn.attend_flat(qkv, B, H, W)
+    assert a.shape == b.shape == (B * H * W, dim)
+    tol = 3e-2 if dtype == torch.bfloat16 else 4e-3
+    assert rel_err(a.float(), b.float()) < tol
+    assert cosine(a, b) > 0.9999

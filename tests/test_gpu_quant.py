@@ -187,3 +187,78 @@ def test_full_hadamard_with_explicit_factor(cuda_device, golden, n):
     got = f32(out["tx"])
     assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max()
     assert (got != want).mean() < 0.01
+
+
+# ---- prologue fused into K1: row gather, LayerNorm, bf16 storage read as fp16 ------------------
+
+def test_row_gather_with_padding_rows(cuda_device):
+    from sam_quantization_b200 import ops
+    rng = np.random.default_rng(31)
+    x = O.rnd(rng.standard_normal((50, 768)).astype(np.float32), "f16")
+    row_map = np.array([3, -1, 49, 0, 0, -1, 17, 25, 8], np.int32)
+    out = ops.quantize(to_dev(x, "f16", cuda_device), 0, row_map=torch.from_numpy(row_map).to(cuda_device),
+                       fake_quant=True, transformed=True)
+    gathered = np.where(row_map[:, None] >= 0, x[np.maximum(row_map, 0)], 0.0).astype(np.float32)
+    q, s, fq = O.quantize(gathered, "per_token", "f16")
+    assert out["q"].shape == (9, 768)
+    assert np.array_equal(out["q"].cpu().numpy(), O.saturate_codes(q))
+    assert np.array_equal(f32(out["scale"]), s)
+    assert np.array_equal(f32(out["fq"]), fq)
+    assert np.array_equal(f32(out["tx"]), gathered)
+    # long rows take the multi-warp layout, odd widths the scalar kernel: same gather
+    for K in (5120, 100):
+        xk = O.rnd(rng.standard_normal((20, K)).astype(np.float32), "f16")
+        rm = np.array([19, -1, 0, 7], np.int32)
+        o = ops.quantize(to_dev(xk, "f16", cuda_device), 0, row_map=torch.from_numpy(rm).to(cuda_device))
+        qk, sk, _ = O.quantize(np.where(rm[:, None] >= 0, xk[np.maximum(rm, 0)], 0.0).astype(np.float32), "per_token", "f16")
+        assert np.array_equal(o["q"].cpu().numpy(), O.saturate_codes(qk)) and np.array_equal(f32(o["scale"]), sk)
+
+
+def test_bf16_storage_read_as_fp16(cuda_device):
+    from sam_quantization_b200 import ops
+    xb = (torch.randn(77, 1280, device=cuda_device) * 3).to(torch.bfloat16)
+    out = ops.quantize(xb, 0, as_dtype=torch.float16, fake_quant=True)
+    ref = ops.quantize(xb.to(torch.float16), 0, fake_quant=True)
+    assert out["fq"].dtype == torch.float16
+    assert torch.equal(out["q"], ref["q"]) and torch.equal(out["scale"], ref["scale"]) and torch.equal(out["fq"], ref["fq"])
+
+
+@pytest.mark.parametrize("dt,K", [("f16", 768), ("f16", 1280), ("f16", 1024), ("bf16", 768), ("f32", 1280)])
+def test_fused_layernorm_then_quant(cuda_device, dt, K):
+    """LayerNorm inside K1 against torch's LayerNorm followed by the plain kernel.  The two
+    LayerNorms sum in different orders, so the normalised value may differ in its last bit and a
+    code by one step on a handful of elements; everything else must be identical."""
+    from sam_quantization_b200 import ops
+    g = torch.Generator().manual_seed(K)
+    x = (torch.randn(300, K, generator=g) * 2 + 0.3).to(TDT[dt]).to(cuda_device)
+    w = (1 + 0.2 * torch.randn(K, generator=g)).to(TDT[dt]).to(cuda_device)
+    b = (0.1 * torch.randn(K, generator=g)).to(TDT[dt]).to(cuda_device)
+    row_map = torch.arange(299, -1, -1, dtype=torch.int32, device=cuda_device)
+    row_map[5] = -1
+    out = ops.quantize(x, 0, layer_norm=(w, b, 1e-6), row_map=row_map, transformed=True)
+    ln = torch.nn.functional.layer_norm(x, (K,), w, b, 1e-6)
+    ln = torch.where(row_map[:, None] >= 0, ln[row_map.clamp(min=0).long()], torch.zeros((), dtype=ln.dtype, device=ln.device))
+    ref = ops.quantize(ln, 0)
+    tx, lnf = out["tx"].float(), ln.float()
+    # fp32 keeps every bit of the statistics' summation-order difference: a few fp32 ulps
+    ulp = {"f16": 2.0 ** -10, "bf16": 2.0 ** -7, "f32": 2.0 ** -17}[dt]
+    assert float(((tx - lnf).abs() / lnf.abs().clamp(min=2.0 ** -6)).max()) <= 1.01 * ulp
+    if dt != "f32":
+        assert (tx != lnf).float().mean() < 0.01
+    dq = (out["q"].int() - ref["q"].int()).abs()
+    assert int(dq.max()) <= 1 and float((dq > 0).float().mean()) < 2e-3
+    assert torch.equal(out["q"][5], torch.zeros(K, dtype=torch.int8, device=cuda_device))
+    rel = ((out["scale"] - ref["scale"]).abs() / ref["scale"]).max()
+    assert float(rel) <= 2 * ulp
+
+
+def test_hadamard_with_gather_and_bf16_source(cuda_device):
+    from sam_quantization_b200 import ops
+    xb = (torch.randn(40, 1024, device=cuda_device)).to(torch.bfloat16)
+    row_map = torch.tensor([39, -1, 0, 12], dtype=torch.int32, device=cuda_device)
+    had = ops.Hadamard("partial", had_dim=64)
+    out = ops.quantize(xb, 0, hadamard=had, row_map=row_map, as_dtype=torch.float16, transformed=True)
+    src = xb.to(torch.float16)
+    g = torch.where(row_map[:, None] >= 0, src[row_map.clamp(min=0).long()], torch.zeros((), dtype=src.dtype, device=src.device))
+    ref = ops.quantize(g, 0, hadamard=had, transformed=True)
+    assert torch.equal(out["tx"], ref["tx"]) and torch.equal(out["q"], ref["q"]) and torch.equal(out["scale"], ref["scale"])
