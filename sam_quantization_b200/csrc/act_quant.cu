@@ -252,7 +252,7 @@ quant_rows_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx, int
         for (int e = 0; e < E; ++e) q[e] = div_exact(f[e], dv);
         RoundVec<T, E>::run(q);
 #pragma unroll
-        for (int e = 0; e < E; ++e) q[e] = rint_small(q[e]);
+        for (int e = 0; e < E; ++e) q[e] = rint_small(q[e], f[e]);
         if (q_out != nullptr)
             *reinterpret_cast<typename PackedCodes<E>::type*>(q_out + row * K + (int64_t)v * E) = pack_codes<E>(q, qmax);
         if (tx_out != nullptr)

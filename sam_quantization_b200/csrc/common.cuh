@@ -71,17 +71,18 @@ __device__ __forceinline__ float div_exact(float x, const Divider& d) {
 
 // round-half-even to an integer for |v| < 2^22 by adding and subtracting 1.5 * 2^23
 constexpr float kRoundMagic = 12582912.0f;
-// (the sign of the input is kept, so that -0.4 rounds to -0.0 as rintf does)
-__device__ __forceinline__ float rint_small(float v) {
+// The sign is taken from `sign_src` (the dividend: the scale is positive), so that -0.4 and
+// -0.0 round to -0.0 as the reference's div_().round_() does.
+__device__ __forceinline__ float rint_small(float v, float sign_src) {
     const float r = (v + kRoundMagic) - kRoundMagic;
-    return __int_as_float(__float_as_int(r) | (__float_as_int(v) & 0x80000000));
+    return __int_as_float(__float_as_int(r) | (__float_as_int(sign_src) & 0x80000000));
 }
 
 // q = round_half_even( T(x / s) ) as a float holding an integer value
 // (`t.div_(scales).round_()`, per_tensor_channel_group.py:60).
 template <typename T>
 __device__ __forceinline__ float quant_value(float x, const Divider& d) {
-    return rint_small(round_to<T>(div_exact(x, d)));
+    return rint_small(round_to<T>(div_exact(x, d)), x);
 }
 
 // two's-complement byte of an integer-valued float clamped to [-qmax, qmax]

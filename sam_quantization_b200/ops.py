@@ -340,17 +340,26 @@ def gemm_i8(a_q: torch.Tensor, w_q: torch.Tensor,
     return out.view(*lead, N)
 
 
+_table_cache = {}
+
+
 def rel_pos_products(qkv: torch.Tensor, num_heads: int, rel_pos_h: torch.Tensor, rel_pos_w: torch.Tensor) -> torch.Tensor:
     """rel_all[head, token, j] = q[token, head, :] . table[j, :] for the rows of ``rel_pos_h``
     followed by those of ``rel_pos_w`` (pitch rounded up to 8): one batched tensor-core GEMM on
     strided views of ``qkv`` [tokens, 3C], no copy of q."""
     tokens, three_c = qkv.shape
     d = three_c // 3 // num_heads
-    rows = rel_pos_h.shape[0] + rel_pos_w.shape[0]
-    J = (rows + 7) // 8 * 8
-    tab = torch.zeros((J, d), dtype=qkv.dtype, device=qkv.device)
-    tab[:rel_pos_h.shape[0]] = rel_pos_h.detach().to(qkv.dtype)
-    tab[rel_pos_h.shape[0]:rows] = rel_pos_w.detach().to(qkv.dtype)
+    key = (rel_pos_h.data_ptr(), rel_pos_w.data_ptr(), rel_pos_h._version, rel_pos_w._version, qkv.dtype, str(qkv.device))
+    tab = _table_cache.get(key)
+    if tab is None:
+        rows = rel_pos_h.shape[0] + rel_pos_w.shape[0]
+        J = (rows + 7) // 8 * 8
+        tab = torch.zeros((J, d), dtype=qkv.dtype, device=qkv.device)
+        tab[:rel_pos_h.shape[0]] = rel_pos_h.detach().to(qkv.dtype)
+        tab[rel_pos_h.shape[0]:rows] = rel_pos_w.detach().to(qkv.dtype)
+        if len(_table_cache) > 256:
+            _table_cache.clear()
+        _table_cache[key] = tab
     q_heads = qkv.view(tokens, 3, num_heads, d)[:, 0].permute(1, 0, 2)          # [heads, tokens, d], strides (d, 3C, 1)
     return torch.matmul(q_heads, tab.t())                                        # [heads, tokens, J]
 

@@ -262,3 +262,15 @@ def test_hadamard_with_gather_and_bf16_source(cuda_device):
     g = torch.where(row_map[:, None] >= 0, src[row_map.clamp(min=0).long()], torch.zeros((), dtype=src.dtype, device=src.device))
     ref = ops.quantize(g, 0, hadamard=had, transformed=True)
     assert torch.equal(out["tx"], ref["tx"]) and torch.equal(out["q"], ref["q"]) and torch.equal(out["scale"], ref["scale"])
+
+
+def test_sign_of_zero_survives(cuda_device):
+    """-0.0 and negative values that round to zero come out as -0.0, as the reference's
+    div_().round_().mul_() leaves them (the fixtures' digests compare raw bytes)."""
+    from sam_quantization_b200 import ops
+    x = np.array([[-0.0, 0.0, -1e-4, 1e-4, 5.0, -5.0, -0.0, 0.01] * 16], np.float32)
+    for dt in ("f16", "bf16", "f32"):
+        out = ops.quantize(to_dev(x, dt, cuda_device), 0, fake_quant=True)
+        _, _, fq = O.quantize(O.rnd(x, dt), "per_token", dt)
+        got = f32(out["fq"])
+        assert np.array_equal(got, fq) and np.array_equal(np.signbit(got), np.signbit(fq))
