@@ -1,0 +1,139 @@
+"""Per-kernel timing of the library's CUDA kernels on synthetic inputs.
+
+    python -m sam_quantization_b200.kernel_bench gemm  --M 32768 --N 5120 --K 1280 --gelu
+    python -m sam_quantization_b200.kernel_bench quant --M 65536 --K 1280 [--ln] [--gather] [--hadamard full]
+    python -m sam_quantization_b200.kernel_bench sweep            # the W8A8 GEMM sweep: M x (K, N) x granularity
+
+Each line of output is JSON: the shape, the mean CUDA-event time over ``--iters`` launches after
+``--warmup`` launches, and the achieved rate against the roofline that bounds the kernel
+(int8 TOP/s for the GEMM: 2*M*N*K per launch; GB/s for the quantization kernels: the
+algorithmic M*(in_bytes*K + K + 4) per launch).  Buffers are rotated between launches so that
+inputs do not stay in L2 when the working set is small.  The same commands, with small
+``--iters``, are what the ncu summaries under profiles/ were captured from.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import ops
+
+SWEEP_M = (196, 4096, 32768, 262144)
+SWEEP_KN = ((768, 2304), (768, 3072), (3072, 768), (1024, 4096), (4096, 1024), (1280, 3840), (1280, 5120), (5120, 1280))
+
+
+def _time(fn, iters, warmup):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def synthetic_activation(M, K, dtype, device, seed=5):
+    """~N(0,1) with 1 % of the channels scaled x20 (the outlier channels of the W8A8 configs)."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    idx = torch.randperm(K, generator=g)[:max(1, K // 100)].to(device)
+    x = torch.randn((M, K), device=device, dtype=torch.float32)
+    x[:, idx] *= 20
+    return x.to(dtype)
+
+
+def bench_gemm(M, N, K, gelu=False, residual=False, w_gran="per_channel", out_dtype=torch.float16, iters=50, warmup=10,
+               group_size=128, nbuf=None):
+    dev = torch.device("cuda")
+    w = (torch.randn((N, K), device=dev) * 0.02).half()
+    wq = ops.quantize_weight(w, ops.WEIGHT_GRANULARITY[w_gran], group_size if w_gran == "per_group" else None)
+    # enough distinct A / C buffers that consecutive launches do not find their operands in the 126 MB L2
+    per = M * K + M * N * 2
+    nbuf = nbuf or max(1, min(8, (256 << 20) // max(per, 1) + 1))
+    acts = [ops.quantize(synthetic_activation(M, K, torch.float16, dev, seed=5 + i), ops.GRAN_ROW) for i in range(nbuf)]
+    outs = [torch.empty((M, N), dtype=out_dtype, device=dev) for _ in range(nbuf)]
+    bias = (torch.randn(N, device=dev) * 0.01).half()
+    res = torch.randn((M, N), device=dev, dtype=out_dtype) if residual else None
+
+    def run(i):
+        a = acts[i % nbuf]
+        ops.gemm_i8(a["q"], wq["q"], a["scale"], wq["scale"], ops.GRAN_ROW, ops.WEIGHT_GRANULARITY[w_gran],
+                    group_size if w_gran == "per_group" else 0, bias=bias, residual=res,
+                    activation=ops.ACT_GELU if gelu else ops.ACT_NONE, out_dtype=out_dtype, out=outs[i % nbuf])
+
+    ms = _time(run, iters, warmup)
+    ops.check_status()
+    return {"kernel": "gemm_i8", "M": M, "N": N, "K": K, "w_gran": w_gran, "gelu": gelu, "residual": residual,
+            "ms": round(ms, 5), "int8_tops": round(2.0 * M * N * K / ms / 1e9, 1), "buffers": nbuf}
+
+
+def bench_quant(M, K, dtype=torch.float16, ln=False, gather=False, hadamard=None, granularity="per_token", group_size=128,
+                iters=50, warmup=10):
+    dev = torch.device("cuda")
+    esz = torch.empty((), dtype=dtype).element_size()
+    nbuf = max(1, min(8, (256 << 20) // (M * K * esz) + 1))
+    xs = [synthetic_activation(M, K, dtype, dev, seed=9 + i) for i in range(nbuf)]
+    kw = {}
+    if ln:
+        kw["layer_norm"] = (torch.ones(K, device=dev, dtype=dtype), torch.zeros(K, device=dev, dtype=dtype), 1e-6)
+    if gather:
+        kw["row_map"] = torch.randperm(M, device=dev).to(torch.int32)
+    if hadamard:
+        kw["hadamard"] = ops.Hadamard(hadamard, had_dim=K // 16 if hadamard == "partial" else 0)
+    gran = ops.ACT_GRANULARITY[granularity]
+
+    def run(i):
+        ops.quantize(xs[i % nbuf], gran, group_size if granularity == "per_group_token" else None, **kw)
+
+    ms = _time(run, iters, warmup)
+    nbytes = M * (esz * K + K + 4)
+    return {"kernel": "act_quant", "M": M, "K": K, "dtype": str(dtype).split(".")[-1], "ln": ln, "gather": gather,
+            "hadamard": hadamard, "granularity": granularity, "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--M", type=int, default=32768)
+    g.add_argument("--N", type=int, default=5120)
+    g.add_argument("--K", type=int, default=1280)
+    g.add_argument("--gelu", action="store_true")
+    g.add_argument("--residual", action="store_true")
+    g.add_argument("--w-gran", dest="w_gran", default="per_channel", choices=list(ops.WEIGHT_GRANULARITY))
+    g.add_argument("--iters", type=int, default=50)
+    g.add_argument("--warmup", type=int, default=10)
+    q = sub.add_parser("quant")
+    q.add_argument("--M", type=int, default=65536)
+    q.add_argument("--K", type=int, default=1280)
+    q.add_argument("--dtype", default="float16", choices=["float16", "bfloat16", "float32"])
+    q.add_argument("--ln", action="store_true")
+    q.add_argument("--gather", action="store_true")
+    q.add_argument("--hadamard", default=None, choices=["full", "partial"])
+    q.add_argument("--granularity", default="per_token", choices=list(ops.ACT_GRANULARITY))
+    q.add_argument("--iters", type=int, default=50)
+    q.add_argument("--warmup", type=int, default=10)
+    s = sub.add_parser("sweep")
+    s.add_argument("--iters", type=int, default=100)
+    s.add_argument("--warmup", type=int, default=20)
+    s.add_argument("--granularities", default="per_tensor,per_channel")
+    args = ap.parse_args()
+    if args.cmd == "gemm":
+        print(json.dumps(bench_gemm(args.M, args.N, args.K, args.gelu, args.residual, args.w_gran, iters=args.iters, warmup=args.warmup)))
+    elif args.cmd == "quant":
+        print(json.dumps(bench_quant(args.M, args.K, getattr(torch, args.dtype), args.ln, args.gather, args.hadamard,
+                                     args.granularity, iters=args.iters, warmup=args.warmup)))
+    else:
+        for gran in args.granularities.split(","):
+            for K, N in SWEEP_KN:
+                for M in SWEEP_M:
+                    it = args.iters if M <= 32768 else max(10, args.iters // 5)
+                    print(json.dumps(bench_gemm(M, N, K, w_gran=gran, iters=it, warmup=args.warmup)), flush=True)
+
+
+if __name__ == "__main__":
+    main()
