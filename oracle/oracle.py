@@ -197,7 +197,12 @@ def w8a8_linear_int8(x, w, bias, dtype="f16", weight_quant="per_channel", act_qu
     else:
         acc = int32_group_accumulators(qa8, qw8, group_size)            # [M, N, G]
         M, N, G = acc.shape
-        sa_g = sa.reshape(M, 1, -1) if act_quant == "per_group_token" else np.broadcast_to(np.asarray(sa, np.float32).reshape(-1, 1, 1), (M, 1, 1))
+        if act_quant == "per_group_token":
+            sa_g = sa.reshape(M, 1, -1)
+        elif np.size(sa) == 1:
+            sa_g = np.asarray(sa, np.float32).reshape(1, 1, 1)
+        else:
+            sa_g = np.asarray(sa, np.float32).reshape(-1, 1, 1)
         sw_g = sw.reshape(1, N, -1) if weight_quant == "per_group" else np.broadcast_to(np.asarray(sw, np.float32).reshape(1, -1, 1), (1, N if np.size(sw) > 1 else 1, 1))
         y = (acc.astype(np.float32) * sa_g.astype(np.float32) * sw_g.astype(np.float32)).sum(axis=2, dtype=np.float32)
         if bias is not None:

@@ -116,7 +116,7 @@ struct Prologue {
 //   GRAN TENSOR : the absolute maximum was reduced beforehand into *tensor_absmax
 // ---------------------------------------------------------------------------
 template <typename T, typename SrcT, int NV, bool MULTI, bool LN>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, (LN && NV <= 5) ? 3 : 1)
 quant_rows_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx, int tpr, Prologue pro,
                   const T* __restrict__ divisor, int gran, int lanes_per_group,
                   const float* __restrict__ tensor_absmax, float qmax,
@@ -177,9 +177,18 @@ quant_rows_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx, int
     }
 
     float vmax[NV];
+    constexpr bool kPlainHalf = std::is_same<T, __half>::value && std::is_same<SrcT, __half>::value && !LN;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int v = i * tpr + t;
+        if constexpr (kPlainHalf) {
+            if (divisor == nullptr) {                  // |x| maximum on packed halves, no conversion
+                const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+                const __half2 m2 = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+                vmax[i] = fmaxf(__low2float(m2), __high2float(m2));
+                continue;
+            }
+        }
         float f[E];
         unpack<SrcT>(raw[i], f);
         bool repack = !std::is_same<SrcT, T>::value;
@@ -250,6 +259,27 @@ quant_rows_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx, int
         const Divider dv = make_divider(s);
 #pragma unroll
         for (int e = 0; e < E; ++e) q[e] = div_exact(f[e], dv);
+        if constexpr (std::is_same<T, __half>::value) {
+            if (fq_out == nullptr) {
+                // codes only: round the quotient to fp16, clamp, and let an fp16 addition of 1536
+                // (ulp 1 in [1024, 2048)) do the round-half-even; the code is then the low byte of
+                // the sum's bit pattern (0x6600 + q).  Two elements per instruction throughout.
+                const __half2 hi = __float2half2_rn(qmax), lo = __float2half2_rn(-qmax), magic = __float2half2_rn(1536.0f);
+                uint32_t hb[E / 2];
+#pragma unroll
+                for (int e = 0; e < E; e += 2) {
+                    __half2 h = __floats2half2_rn(q[e], q[e + 1]);
+                    h = __hadd2(__hmin2(__hmax2(h, lo), hi), magic);
+                    hb[e / 2] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                if (q_out != nullptr)
+                    *reinterpret_cast<uint2*>(q_out + row * K + (int64_t)v * E) =
+                        make_uint2(__byte_perm(hb[0], hb[1], 0x6420), __byte_perm(hb[2], hb[3], 0x6420));
+                if (tx_out != nullptr)
+                    *reinterpret_cast<uint4*>(tx_out + row * K + (int64_t)v * E) = raw[i];
+                continue;
+            }
+        }
         RoundVec<T, E>::run(q);
 #pragma unroll
         for (int e = 0; e < E; ++e) q[e] = rint_small(q[e], f[e]);

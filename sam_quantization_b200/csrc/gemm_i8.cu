@@ -18,18 +18,17 @@
 // The accumulator is double buffered (2 x 256 TMEM columns) so the epilogue of tile i
 // overlaps the MMAs of tile i+1.  Every mbarrier wait is bounded: when a wait runs out the
 // kernel raises a status word and winds down instead of hanging.
-#include "common.cuh"
-#include "tcgen05.cuh"
-#include <string.h>
-#include <type_traits>
+#include "gemm_common.cuh"
 
 namespace samq {
+
+using namespace sm100;
+using namespace gemm;
 
 namespace {
 
 constexpr int BM = 128;            // rows of A per tile   (UMMA M)
 constexpr int BN = 256;            // rows of W per tile   (UMMA N)
-constexpr int BK = 128;            // bytes (= int8 elements) of K per stage: one 128B swizzle row
 constexpr int UK = 32;             // K of one tcgen05.mma for 8-bit operands
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK;   // 16 KiB
@@ -55,45 +54,10 @@ constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_
                               (size_t)EPI_WARPS * STAGING_BYTES +
                               EPI_PARAM_FLOATS * sizeof(float) + sizeof(Control);
 
-using namespace sm100;
 
 // Instruction descriptor for kind::i8: D = S32 (2) in bits [4,6); A, B = signed 8-bit (1) in
 // [7,10) and [10,13); both operands K-major (bits 15, 16 = 0); N >> 3 in [17,23); M >> 4 in [24,29).
 constexpr uint32_t kInstrDesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-
-// Exact (erf) GELU, x * Phi(x), with one exp2 and no division:  for z = |x| / sqrt(2),
-// 0.5 * erfc(z) = 2^Q(z) with Q a degree-6 polynomial fitted on [0, 4.3] (beyond that the tail is
-// below 1e-9); Phi(x) = 1 - 2^Q for x >= 0 and 2^Q otherwise.  Absolute error of the result
-// < 4e-7, relative < 2e-5 — two orders below fp16 resolution — at a third of erff's cost, which
-// matters because the epilogue of a K = 1280 tile has only ~20 issue slots per output.
-__device__ __forceinline__ float gelu_erf(float x) {
-    const float z = fminf(fabsf(x) * 0.70710678118654752440f, 4.3f);
-    float q = 2.868852462e-04f;
-    q = fmaf(q, z, -4.492766690e-03f);
-    q = fmaf(q, z, 3.266510367e-02f);
-    q = fmaf(q, z, -1.514675319e-01f);
-    q = fmaf(q, z, -9.173173308e-01f);
-    q = fmaf(q, z, -1.628102660e+00f);
-    q = fmaf(q, z, -9.999881387e-01f);
-    float h;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(h) : "f"(q));
-    const float phi = (x >= 0.f) ? 1.0f - h : h;
-    return x * phi;
-}
-
-template <typename OutT> struct OutOps;
-template <> struct OutOps<__half> {
-    static __device__ __forceinline__ float up(__half v) { return __half2float(v); }
-    static __device__ __forceinline__ __half down(float v) { return __float2half_rn(v); }
-};
-template <> struct OutOps<__nv_bfloat16> {
-    static __device__ __forceinline__ float up(__nv_bfloat16 v) { return __bfloat162float(v); }
-    static __device__ __forceinline__ __nv_bfloat16 down(float v) { return __float2bfloat16_rn(v); }
-};
-template <> struct OutOps<float> {
-    static __device__ __forceinline__ float up(float v) { return v; }
-    static __device__ __forceinline__ float down(float v) { return v; }
-};
 
 struct GemmParams {
     int M, N, K;
@@ -108,8 +72,9 @@ struct GemmParams {
     int32_t* status;
 };
 
-// OutT = __half | __nv_bfloat16 | float | int32_t (raw accumulators)
-template <typename OutT>
+// OutT = __half | __nv_bfloat16 | float | int32_t (raw accumulators); GELU / RES compile the
+// activation and the residual add in or out of the epilogue
+template <typename OutT, bool GELU, bool RES>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_out, const GemmParams p)
@@ -240,12 +205,24 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint8_t* stage_ptr = staging + (size_t)ew * STAGING_BYTES;
             const int rr = quad * 32 + lane;                       // row inside the tile
             const uint32_t swz = (uint32_t)((lane >> 1) & 3);     // 64-byte swizzle: 16-byte slot ^= bits [7:8] of the offset
-#pragma unroll 1
+            // The accumulator is read 32 columns at a time; the load of chunk c+1 is in flight while
+            // chunk c is dequantised and stored, and the buffer is handed back to the MMA warp as soon
+            // as the last chunk sits in registers.
+            const uint32_t tmem_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + half_n * 128);
+            uint32_t rbuf[2][32];
+            tmem_ld32(tmem_row, rbuf[0]);
+#pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int col0 = half_n * 128 + c * 32;
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + col0), r);
+                uint32_t (&r)[32] = rbuf[c & 1];
                 tmem_ld_wait();
+                if (c + 1 < 4) {
+                    tmem_ld32(tmem_row + (uint32_t)((c + 1) * 32), rbuf[(c + 1) & 1]);
+                } else {
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
+                }
                 const int n_first = n0 + col0;
                 if (n_first >= p.N) continue;                       // warp-uniform
                 const int n_valid = min(32, p.N - n_first);
@@ -266,23 +243,65 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         y[j + 2] = fmaf(__int2float_rn((int)r[j + 2]) * a_s, w4.z, b4.z);
                         y[j + 3] = fmaf(__int2float_rn((int)r[j + 3]) * a_s, w4.w, b4.w);
                     }
-                    if (p.activation == SAMQ_ACT_GELU) {
+                    if constexpr (GELU) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) y[j] = gelu_erf(y[j]);
                     }
-                    if (p.residual != nullptr && row_ok) {
-                        const OutT* res = reinterpret_cast<const OutT*>(p.residual) + (int64_t)row * p.ldr + n_first;
-                        if (p.vec_ok && n_valid == 32) {
+                    if constexpr (RES) {
+                        const OutT* res_base = reinterpret_cast<const OutT*>(p.residual);
+                        if (p.tma_store && p.vec_ok && n_valid == 32) {
+                            // coalesced: the warp reads its 32 x 32 residual block row-segment by
+                            // row-segment (16 bytes per lane, whole rows per instruction group), parks
+                            // it in the staging buffer in the swizzled layout, and every lane then
+                            // picks up its own row from there
+                            constexpr int SEG = 32 / PER16;                      // 16-byte segments per row: 4 or 8
+                            constexpr int ROWS_PER_LD = 32 / SEG;                // rows covered by one warp-wide load
+                            uint4 seg[SEG];
 #pragma unroll
-                            for (int j = 0; j < NVEC; ++j) {
-                                OutT tmp[PER16];
-                                *reinterpret_cast<uint4*>(tmp) = *reinterpret_cast<const uint4*>(res + j * PER16);
-#pragma unroll
-                                for (int e = 0; e < PER16; ++e) y[j * PER16 + e] += OutOps<OutT>::up(tmp[e]);
+                            for (int k = 0; k < SEG; ++k) {
+                                const int rrow = k * ROWS_PER_LD + lane / SEG;
+                                const int grow = m0 + quad * 32 + rrow;
+                                seg[k] = grow < p.M
+                                    ? *reinterpret_cast<const uint4*>(res_base + (int64_t)grow * p.ldr + n_first + (lane % SEG) * PER16)
+                                    : make_uint4(0, 0, 0, 0);
                             }
-                        } else {
+                            if (lane == 0) bulk_wait_read0();                    // staging is free again
+                            __syncwarp();
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) if (j < n_valid) y[j] += OutOps<OutT>::up(res[j]);
+                            for (int part = 0; part < SEG / 4; ++part) {
+                                // a staging pass holds 64 bytes per row: all of a 2-byte row, half of a 4-byte row
+#pragma unroll
+                                for (int k = 0; k < SEG; ++k) {
+                                    const int rrow = k * ROWS_PER_LD + lane / SEG;
+                                    const int sg = lane % SEG;
+                                    if (sg / 4 == part)
+                                        *reinterpret_cast<uint4*>(stage_ptr + rrow * 64 +
+                                            ((((uint32_t)(sg & 3)) ^ (uint32_t)((rrow >> 1) & 3)) << 4)) = seg[k];
+                                }
+                                __syncwarp();
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    OutT tmp[PER16];
+                                    *reinterpret_cast<uint4*>(tmp) = *reinterpret_cast<const uint4*>(stage_ptr + lane * 64 + (((uint32_t)j ^ swz) << 4));
+#pragma unroll
+                                    for (int e = 0; e < PER16; ++e) y[(part * 4 + j) * PER16 + e] += OutOps<OutT>::up(tmp[e]);
+                                }
+                                __syncwarp();
+                            }
+                        } else if (row_ok) {
+                            const OutT* res = res_base + (int64_t)row * p.ldr + n_first;
+                            if (p.vec_ok && n_valid == 32) {
+#pragma unroll
+                                for (int j = 0; j < NVEC; ++j) {
+                                    OutT tmp[PER16];
+                                    *reinterpret_cast<uint4*>(tmp) = *reinterpret_cast<const uint4*>(res + j * PER16);
+#pragma unroll
+                                    for (int e = 0; e < PER16; ++e) y[j * PER16 + e] += OutOps<OutT>::up(tmp[e]);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) if (j < n_valid) y[j] += OutOps<OutT>::up(res[j]);
+                            }
                         }
                     }
 #pragma unroll
@@ -322,9 +341,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
             (void)rr;
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
             if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
         }
     }
@@ -340,74 +356,27 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0 && ctl->abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
 }
 
-// ---- host side -----------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = []() -> EncodeTiledFn {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-            qres != cudaDriverEntryPointSuccess)
-            return nullptr;
-        return reinterpret_cast<EncodeTiledFn>(ptr);
-    }();
-    return fn;
-}
-
-// [rows, K] int8 row-major with row stride ld bytes; box = box_rows x 128 bytes, 128-byte swizzle, zero fill.
-int make_operand_map(CUtensorMap* map, const int8_t* base, int64_t rows, int64_t K, int64_t ld, int box_rows) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (fn == nullptr) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-    return SAMQ_OK;
-}
-
-int sm_count() {
-    static thread_local int cached_dev = -1;
-    static thread_local int cached = 0;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (dev != cached_dev) {
-        int n = 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached = n; cached_dev = dev;
-    }
-    return cached;
-}
-
-// [M, N] output with row stride ldo elements of esize bytes; box = 32 rows x 64 bytes, 64-byte swizzle.
-int make_out_map(CUtensorMap* map, void* base, int64_t M, int64_t N, int64_t ldo, int esize) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (fn == nullptr) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
-    cuuint64_t strides[1] = {(cuuint64_t)(ldo * esize)};
-    cuuint32_t box[2] = {(cuuint32_t)(64 / esize), 32u};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, base, dims,
-                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
-                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
+template <typename OutT, bool GELU, bool RES>
+int launch_gemm_variant(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, const GemmParams& p, cudaStream_t st) {
+    SAMQ_CUDA_TRY(cudaFuncSetAttribute(gemm_i8_kernel<OutT, GELU, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    gemm_i8_kernel<OutT, GELU, RES><<<grid, THREADS, SMEM_BYTES, st>>>(ma, mw, mo, p);
+    SAMQ_CUDA_TRY(cudaGetLastError());
     return SAMQ_OK;
 }
 
 template <typename OutT>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, const GemmParams& p, cudaStream_t st) {
-    SAMQ_CUDA_TRY(cudaFuncSetAttribute(gemm_i8_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-    const int grid = tiles < sm_count() ? tiles : sm_count();
-    gemm_i8_kernel<OutT><<<grid, THREADS, SMEM_BYTES, st>>>(ma, mw, mo, p);
-    SAMQ_CUDA_TRY(cudaGetLastError());
-    return SAMQ_OK;
+    if constexpr (std::is_same<OutT, int32_t>::value) {
+        return launch_gemm_variant<OutT, false, false>(ma, mw, mo, p, st);
+    } else {
+        const bool gelu = p.activation == SAMQ_ACT_GELU, res = p.residual != nullptr;
+        if (gelu && res) return launch_gemm_variant<OutT, true, true>(ma, mw, mo, p, st);
+        if (gelu) return launch_gemm_variant<OutT, true, false>(ma, mw, mo, p, st);
+        if (res) return launch_gemm_variant<OutT, false, true>(ma, mw, mo, p, st);
+        return launch_gemm_variant<OutT, false, false>(ma, mw, mo, p, st);
+    }
 }
 
 }  // namespace

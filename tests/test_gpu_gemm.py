@@ -140,3 +140,40 @@ def test_config1_against_reference_digests(cuda_device, golden):
     want = g["y_sample"]
     got = f32(y)[::97, ::53]
     assert np.abs(got - want).max() / np.abs(want).max() < 1e-2
+
+
+@pytest.mark.parametrize("wq,aq,g", [("per_group", "per_token", 128), ("per_group", "per_group_token", 128),
+                                     ("per_channel", "per_group_token", 256), ("per_group", "per_tensor", 384)])
+def test_grouped_scales_against_oracle(cuda_device, wq, aq, g):
+    """Grouped weights and / or activations: per-group int32 partial sums scaled in fp32."""
+    from sam_quantization_b200 import ops
+    rng = np.random.default_rng(11)
+    M, N, K = 203, 392, 768
+    x = O.rnd(rng.standard_normal((M, K)).astype(np.float32), "f16")
+    x[:, 5] *= 20
+    w = O.rnd((rng.standard_normal((N, K)) * 0.02).astype(np.float32), "f16")
+    b = O.rnd(rng.standard_normal(N) * 0.01, "f16")
+    res = O.rnd(rng.standard_normal((M, N)), "f16")
+    dev = cuda_device
+    xa = ops.quantize(torch.from_numpy(x).half().to(dev), ops.ACT_GRANULARITY[aq], g if aq == "per_group_token" else None)
+    wa = ops.quantize_weight(torch.from_numpy(w).half().to(dev), ops.WEIGHT_GRANULARITY[wq], g if wq == "per_group" else None)
+    for act, use_res in ((None, False), ("gelu", True)):
+        y = ops.gemm_i8(xa["q"], wa["q"], xa["scale"], wa["scale"], ops.ACT_GRANULARITY[aq], ops.WEIGHT_GRANULARITY[wq], g,
+                        bias=torch.from_numpy(b).half().to(dev),
+                        residual=torch.from_numpy(res).half().to(dev) if use_res else None,
+                        activation=1 if act else 0, out_dtype=torch.float16)
+        torch.cuda.synchronize()
+        ops.check_status()
+        want = O.w8a8_linear_int8(x, w, b, "f16", wq, aq, g, activation=act, residual=res if use_res else None)[0]
+        got = f32(y)
+        assert np.all(np.abs(got - want) <= 2.0 ** -9 * np.maximum(np.abs(want), 1e-2) + 1e-5), (wq, aq, g, act)
+
+
+def test_grouped_gemm_rejects_small_groups(cuda_device):
+    from sam_quantization_b200 import ops
+    from sam_quantization_b200._lib import SamqError
+    dev = cuda_device
+    a = torch.zeros((8, 256), dtype=torch.int8, device=dev)
+    w = torch.zeros((8, 256), dtype=torch.int8, device=dev)
+    with pytest.raises(SamqError):
+        ops.gemm_i8(a, w, torch.ones(8, device=dev), torch.ones((8, 8), device=dev), 0, 2, 32, out_dtype=torch.float16)
