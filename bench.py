@@ -196,11 +196,13 @@ def run_ours(args):
         raise RuntimeError("bench.py needs a CUDA device: the W8A8 engine has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    assert GLOBAL_BATCH % world == 0
-    local_n = GLOBAL_BATCH // world
+    from sam_quantization_b200.dist import gather_shards, init_process_group, shard_range
+    init_process_group("nccl", device=dev)
+    first, last = shard_range(rank, world, GLOBAL_BATCH)          # this rank's images [first, last)
+    local_n = last - first
     chunk = min(args.chunk, local_n)
+    while local_n % chunk:                                        # graph replay needs a fixed batch
+        chunk -= 1
 
     from sam_quantization_b200.engine import EncoderRunner
     model = build_quantized_encoder(args.model, dev)
@@ -209,7 +211,7 @@ def run_ours(args):
     # this rank's shard of the global batch: images [rank*local_n, (rank+1)*local_n), seeded per image
     host = torch.empty((local_n, 3, 1024, 1024), dtype=torch.float16).pin_memory()
     for i in range(local_n):
-        host[i] = synthetic_images(1, 4000 + rank * local_n + i)[0]
+        host[i] = synthetic_images(1, 4000 + first + i)[0]
     resident = host.to(dev)
     out_host = torch.empty((local_n, 256, 64, 64), dtype=torch.float16).pin_memory()
     out_dev = torch.empty((local_n, 256, 64, 64), dtype=torch.float16, device=dev)
@@ -270,16 +272,14 @@ def run_ours(args):
     ops.enable_kernel_timing(False)
 
     # verification gather (outside every timed region): embeddings of all ranks to rank 0
-    checksum = None
-    if world > 1:
-        gathered = [torch.empty_like(out_dev) for _ in range(world)] if rank == 0 else None
-        dist.gather(out_dev, gathered, dst=0)
-        if rank == 0:
-            allv = torch.cat(gathered, 0)
-            checksum = float(allv.float().abs().mean().item())
-    else:
-        checksum = float(out_dev.float().abs().mean().item())
-    finite = bool(torch.isfinite(out_dev).all().item())
+    allv = gather_shards(out_dev, GLOBAL_BATCH, dst=0)
+    checksum, finite = None, None
+    if rank == 0:
+        # per-image fingerprints: identical for every world size because images are seeded by
+        # their global index and every rank runs the same kernels
+        checksum = float(allv.float().abs().mean().item())
+        finite = bool(torch.isfinite(allv).all().item())
+        fingerprint = [round(float(v), 6) for v in allv.float().abs().flatten(1).mean(1)[:: max(1, GLOBAL_BATCH // 8)].tolist()]
 
     if rank == 0:
         peaks, peak_kind = read_peaks()
@@ -309,7 +309,8 @@ def run_ours(args):
                          "linear_tops_per_image": linear_ops_per_image(args.model) / 1e12},
             "act_quant": {"achieved_gbs": (quant["bytes"] / (quant["ms"] / 1000.0) / 1e9) if quant["ms"] > 0 else 0.0,
                           "peak_gbs": float(peaks["hbm_gbs"]), "ms_per_step": quant["ms"], "launches_per_step": quant["launches"]},
-            "verify": {"finite": finite, "mean_abs_embedding": checksum},
+            "verify": {"finite": finite, "mean_abs_embedding": checksum, "gathered_images": int(allv.shape[0]),
+                       "per_image_mean_abs_every_8th": fingerprint},
         }
         if not args.no_cpu_baseline and world == 1:
             v, cores, sample = cpu_reference_images_per_s(args.model, budget_s=args.ref_budget)
