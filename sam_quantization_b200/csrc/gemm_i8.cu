@@ -191,6 +191,17 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 ws[epi_tid] = wv; bs[epi_tid] = bv;
                 asm volatile("bar.sync 1, %0;" ::"r"(EPI_WARPS * 32) : "memory");
             }
+            if constexpr (RES) {
+                // pull this warp's 32 x 128 residual block towards L2 while the MMAs of the tile run
+                const int prow = m0 + quad * 32 + lane;
+                if (prow < p.M) {
+                    const char* rp = reinterpret_cast<const char*>(p.residual) +
+                                     ((int64_t)prow * p.ldr + n0 + half_n * 128) * (int64_t)sizeof(OutT);
+#pragma unroll
+                    for (int b = 0; b < (int)(128 * sizeof(OutT)); b += 128)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + b));
+                }
+            }
             // after a failed wait keep visiting the named barrier above so no warp is left behind
             if (ok && !mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag)) ok = false;
             if (!ok) continue;

@@ -340,34 +340,31 @@ def gemm_i8(a_q: torch.Tensor, w_q: torch.Tensor,
     return out.view(*lead, N)
 
 
-_table_cache = {}
+def rel_pos_table(rel_pos_h: torch.Tensor, rel_pos_w: torch.Tensor, dtype, device) -> torch.Tensor:
+    """The rows of ``rel_pos_h`` followed by those of ``rel_pos_w`` as one [J, d] matrix of
+    ``dtype`` (J rounded up to a multiple of 8, zero rows at the end)."""
+    rows = rel_pos_h.shape[0] + rel_pos_w.shape[0]
+    J = (rows + 7) // 8 * 8
+    tab = torch.zeros((J, rel_pos_h.shape[1]), dtype=dtype, device=device)
+    tab[:rel_pos_h.shape[0]] = rel_pos_h.detach().to(device=device, dtype=dtype)
+    tab[rel_pos_h.shape[0]:rows] = rel_pos_w.detach().to(device=device, dtype=dtype)
+    return tab
 
 
-def rel_pos_products(qkv: torch.Tensor, num_heads: int, rel_pos_h: torch.Tensor, rel_pos_w: torch.Tensor) -> torch.Tensor:
-    """rel_all[head, token, j] = q[token, head, :] . table[j, :] for the rows of ``rel_pos_h``
-    followed by those of ``rel_pos_w`` (pitch rounded up to 8): one batched tensor-core GEMM on
+def rel_pos_products(qkv: torch.Tensor, num_heads: int, table: torch.Tensor) -> torch.Tensor:
+    """rel_all[head, token, j] = q[token, head, :] . table[j, :]: one batched tensor-core GEMM on
     strided views of ``qkv`` [tokens, 3C], no copy of q."""
     tokens, three_c = qkv.shape
     d = three_c // 3 // num_heads
-    key = (rel_pos_h.data_ptr(), rel_pos_w.data_ptr(), rel_pos_h._version, rel_pos_w._version, qkv.dtype, str(qkv.device))
-    tab = _table_cache.get(key)
-    if tab is None:
-        rows = rel_pos_h.shape[0] + rel_pos_w.shape[0]
-        J = (rows + 7) // 8 * 8
-        tab = torch.zeros((J, d), dtype=qkv.dtype, device=qkv.device)
-        tab[:rel_pos_h.shape[0]] = rel_pos_h.detach().to(qkv.dtype)
-        tab[rel_pos_h.shape[0]:rows] = rel_pos_w.detach().to(qkv.dtype)
-        if len(_table_cache) > 256:
-            _table_cache.clear()
-        _table_cache[key] = tab
     q_heads = qkv.view(tokens, 3, num_heads, d)[:, 0].permute(1, 0, 2)          # [heads, tokens, d], strides (d, 3C, 1)
-    return torch.matmul(q_heads, tab.t())                                        # [heads, tokens, J]
+    return torch.matmul(q_heads, table.t())                                      # [heads, tokens, J]
 
 
 def attn_window_prep(qkv: torch.Tensor, H: int, W: int, num_heads: int, rel_pos_h: torch.Tensor,
-                     rel_pos_w: torch.Tensor, scale: float, width: int):
+                     rel_pos_w: torch.Tensor, scale: float, width: int, table: Optional[torch.Tensor] = None):
     """Augmented attention inputs for windows (``samq_attn_window_prep``): from ``qkv``
-    [tokens, 3C] returns ``(q_aug, k_aug)``, each [tokens, heads, width]."""
+    [tokens, 3C] returns ``(q_aug, k_aug)``, each [tokens, heads, width].  ``table`` is an
+    optional cached ``rel_pos_table`` of the two tables."""
     _require_cuda(qkv, "qkv")
     lib = _lib.load()
     tokens, three_c = qkv.shape
@@ -376,7 +373,9 @@ def attn_window_prep(qkv: torch.Tensor, H: int, W: int, num_heads: int, rel_pos_
         raise ValueError("qkv must be contiguous")
     if rel_pos_h.shape != (2 * H - 1, d) or rel_pos_w.shape != (2 * W - 1, d):
         raise ValueError("relative position tables must be [2H-1, d] and [2W-1, d]")
-    rel_all = rel_pos_products(qkv, num_heads, rel_pos_h, rel_pos_w)
+    if table is None:
+        table = rel_pos_table(rel_pos_h, rel_pos_w, qkv.dtype, qkv.device)
+    rel_all = rel_pos_products(qkv, num_heads, table)
     if not rel_all.is_contiguous():
         rel_all = rel_all.contiguous()
     qa = torch.empty((tokens, num_heads, width), dtype=qkv.dtype, device=qkv.device)
@@ -388,7 +387,7 @@ def attn_window_prep(qkv: torch.Tensor, H: int, W: int, num_heads: int, rel_pos_
 
 
 def attn_rel_bias(qkv: torch.Tensor, images: int, H: int, W: int, num_heads: int, rel_pos_h: torch.Tensor,
-                  rel_pos_w: torch.Tensor) -> torch.Tensor:
+                  rel_pos_w: torch.Tensor, table: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Explicit relative-position bias [images, heads, H*W, H*W] for global attention
     (``samq_attn_rel_bias``) from ``qkv`` [images*H*W, 3C]."""
     _require_cuda(qkv, "qkv")
@@ -397,7 +396,9 @@ def attn_rel_bias(qkv: torch.Tensor, images: int, H: int, W: int, num_heads: int
     L = H * W
     if tokens != images * L or not qkv.is_contiguous():
         raise ValueError("qkv must be a contiguous [images*H*W, 3C] tensor")
-    rel_all = rel_pos_products(qkv, num_heads, rel_pos_h, rel_pos_w)
+    if table is None:
+        table = rel_pos_table(rel_pos_h, rel_pos_w, qkv.dtype, qkv.device)
+    rel_all = rel_pos_products(qkv, num_heads, table)
     if not rel_all.is_contiguous():
         rel_all = rel_all.contiguous()
     bias = torch.empty((images, num_heads, L, L), dtype=qkv.dtype, device=qkv.device)

@@ -162,6 +162,18 @@ class Attention(nn.Module):
             self._onehot[key] = codes.to(device=device, dtype=dtype)
         return self._onehot[key]
 
+    def _rel_table(self, dtype, device) -> torch.Tensor:
+        """Both relative-position tables as one matrix in the attention dtype, rebuilt only when
+        a table changed (new storage or an in-place update)."""
+        key = (self.rel_pos_h.data_ptr(), self.rel_pos_w.data_ptr(), self.rel_pos_h._version, self.rel_pos_w._version,
+               dtype, str(device))
+        cached = self.__dict__.get("_table_cache")
+        if cached is None or cached[0] != key:
+            from . import ops
+            cached = (key, ops.rel_pos_table(self.rel_pos_h, self.rel_pos_w, dtype, device))
+            self.__dict__["_table_cache"] = cached
+        return cached[1]
+
     def _native(self, qkv: torch.Tensor, d: int, H: int, W: int) -> bool:
         if not (self.native_prep and qkv.is_cuda and qkv.dtype in (torch.float16, torch.bfloat16) and qkv.is_contiguous()):
             return False
@@ -183,7 +195,8 @@ class Attention(nn.Module):
             from . import ops
             if d + extra <= 128:
                 width = (d + extra + 7) // 8 * 8
-                qa, ka = ops.attn_window_prep(qkv, H, W, nh, self.rel_pos_h, self.rel_pos_w, self.scale, width)
+                qa, ka = ops.attn_window_prep(qkv, H, W, nh, self.rel_pos_h, self.rel_pos_w, self.scale, width,
+                                              table=self._rel_table(qkv.dtype, qkv.device))
                 out = F.scaled_dot_product_attention(qa.view(B, L, nh, width).transpose(1, 2), ka.view(B, L, nh, width).transpose(1, 2),
                                                      v.transpose(1, 2), scale=1.0)
                 return out.transpose(1, 2).reshape(B * L, nh * d)
@@ -191,7 +204,8 @@ class Attention(nn.Module):
             step = max(1, self.global_chunk)
             for i in range(0, B, step):
                 b = min(step, B - i)
-                bias = ops.attn_rel_bias(qkv[i * L:(i + b) * L], b, H, W, nh, self.rel_pos_h, self.rel_pos_w)
+                bias = ops.attn_rel_bias(qkv[i * L:(i + b) * L], b, H, W, nh, self.rel_pos_h, self.rel_pos_w,
+                                         table=self._rel_table(qkv.dtype, qkv.device))
                 o = F.scaled_dot_product_attention(q[i:i + b].transpose(1, 2), k[i:i + b].transpose(1, 2),
                                                    v[i:i + b].transpose(1, 2), attn_mask=bias, scale=self.scale)
                 outs.append(o.transpose(1, 2).reshape(b * L, nh * d))
@@ -303,15 +317,26 @@ class Block(nn.Module):
 
 
 class PatchEmbed(nn.Module):
+    """Non-overlapping patch projection.  The parameter lives in a Conv2d (``proj``) as in the
+    original model; because kernel == stride it is evaluated as one matrix product over the
+    unfolded patches, which is what a tensor-core GEMM wants."""
+
     def __init__(self, kernel_size=(16, 16), stride=(16, 16), padding=(0, 0), in_chans=3, embed_dim=768):
         super().__init__()
         self.proj = nn.Conv2d(in_chans, embed_dim, kernel_size=kernel_size, stride=stride, padding=padding)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.proj(x).permute(0, 2, 3, 1)
+        kh, kw = self.proj.kernel_size
+        if tuple(self.proj.stride) != (kh, kw) or tuple(self.proj.padding) != (0, 0) or x.shape[2] % kh or x.shape[3] % kw:
+            return self.proj(x).permute(0, 2, 3, 1)
+        B, C, H, W = x.shape
+        patches = x.view(B, C, H // kh, kh, W // kw, kw).permute(0, 2, 4, 1, 3, 5).reshape(B, H // kh, W // kw, C * kh * kw)
+        return F.linear(patches, self.proj.weight.view(self.proj.out_channels, -1), self.proj.bias)
 
 
 class LayerNorm2d(nn.Module):
+    """LayerNorm over the channel axis of an NCHW tensor."""
+
     def __init__(self, num_channels: int, eps: float = 1e-6):
         super().__init__()
         self.weight = nn.Parameter(torch.ones(num_channels))
@@ -319,10 +344,9 @@ class LayerNorm2d(nn.Module):
         self.eps = eps
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        u = x.mean(1, keepdim=True)
-        s = (x - u).pow(2).mean(1, keepdim=True)
-        x = (x - u) / torch.sqrt(s + self.eps)
-        return self.weight[:, None, None] * x + self.bias[:, None, None]
+        # per pixel over channels; done on the channels-last view so it is one fused kernel
+        y = F.layer_norm(x.permute(0, 2, 3, 1), (x.shape[1],), self.weight, self.bias, self.eps)
+        return y.permute(0, 3, 1, 2)
 
 
 class ImageEncoderViT(nn.Module):
@@ -346,13 +370,22 @@ class ImageEncoderViT(nn.Module):
             nn.Conv2d(embed_dim, out_chans, kernel_size=1, bias=False), LayerNorm2d(out_chans),
             nn.Conv2d(out_chans, out_chans, kernel_size=3, padding=1, bias=False), LayerNorm2d(out_chans))
 
+    def _neck(self, x: torch.Tensor) -> torch.Tensor:
+        """x [B, H, W, C] -> [B, out, H, W].  The 1x1 convolution is a matrix product on the
+        channels-last activations; the 3x3 convolution runs on the channels-last view."""
+        c1, n1, c2, n2 = self.neck
+        y = F.linear(x, c1.weight.view(c1.out_channels, -1), c1.bias)
+        y = F.layer_norm(y, (c1.out_channels,), n1.weight, n1.bias, n1.eps)
+        y = c2(y.permute(0, 3, 1, 2))
+        return n2(y)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x = self.patch_embed(x)
         if self.pos_embed is not None:
             x = x + self.pos_embed
         for blk in self.blocks:
             x = blk(x)
-        return self.neck(x.permute(0, 3, 1, 2))
+        return self._neck(x)
 
 
 class SamEncoderModel(nn.Module):
