@@ -256,6 +256,18 @@ int samq_attn_window_prep(const void* qkv, const void* rel_all, int dtype, int64
 int samq_attn_rel_bias(const void* rel_all, int dtype, int64_t images, int rel_pitch, int H, int W, int num_heads,
                        void* bias, void* stream);
 
+/* Whole windowed attention in one kernel: for every window (H*W tokens, H*W <= 208) and head,
+ *   out[w, l, h, :] = softmax_k( scale * q.k + q.rel_pos_h[qh-kh+H-1] + q.rel_pos_w[qw-kw+W-1] ) v
+ * with q, k, v read in place from `qkv` [windows*H*W, 3*C] (fp16 or bf16, 16-byte aligned) and
+ * `out` [windows*H*W, C] of the same dtype. `rel_table` holds the 2H-1 rows of rel_pos_h followed
+ * by the 2W-1 rows of rel_pos_w, [table_rows, head_dim] with table_rows rounded up to a multiple
+ * of 8 (extra rows zero). It is the attention between qkv and proj of a
+ * windowed block (quarot/model_utils.py:158-170), with the bias never materialised.
+ * head_dim 64 or 80 for windows up to 14x14 (16, 32, 64 for windows of up to 16 tokens);
+ * other shapes return SAMQ_ERR_UNSUPPORTED. */
+int samq_attn_windowed(const void* qkv, int dtype, int64_t windows, int H, int W, int num_heads, int head_dim,
+                       const void* rel_table, int table_rows, float scale, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -29,6 +29,7 @@ EXPORTED_SYMBOLS = (
     "samq_gemm_i8",
     "samq_attn_window_prep",
     "samq_attn_rel_bias",
+    "samq_attn_windowed",
 )
 
 
@@ -132,6 +133,11 @@ def load() -> ctypes.CDLL:
     lib.samq_attn_rel_bias.argtypes = [
         c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int,   # rel_all, dtype, images, rel_pitch, H, W, heads
         c_void_p, c_void_p,                                     # bias, stream
+    ]
+    lib.samq_attn_windowed.restype = c_int
+    lib.samq_attn_windowed.argtypes = [
+        c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int,   # qkv, dtype, windows, H, W, heads, head_dim
+        c_void_p, c_int, c_float, c_void_p, c_void_p,           # rel_table, table_rows, scale, out, stream
     ]
     _lib = lib
     return lib

@@ -44,6 +44,9 @@ int attn_window_prep_dispatch(const void* qkv, const void* rel_all, int dtype, i
 
 int attn_rel_bias_dispatch(const void* rel_all, int dtype, int64_t images, int J, int H, int W, int nh, void* bias, void* stream);
 
+int attn_window_dispatch(const void* qkv, int dtype, int64_t windows, int H, int W, int nh, int d,
+                         const void* table, int table_rows, float scale, void* out, void* stream);
+
 }  // namespace samq
 
 extern "C" {
@@ -98,6 +101,12 @@ int samq_attn_window_prep(const void* qkv, const void* rel_all, int dtype, int64
 {
     return samq::attn_window_prep_dispatch(qkv, rel_all, dtype, tokens, rel_pitch, H, W, num_heads, head_dim, scale,
                                            width, q_aug, k_aug, stream);
+}
+
+int samq_attn_windowed(const void* qkv, int dtype, int64_t windows, int H, int W, int num_heads, int head_dim,
+                       const void* rel_table, int table_rows, float scale, void* out, void* stream)
+{
+    return samq::attn_window_dispatch(qkv, dtype, windows, H, W, num_heads, head_dim, rel_table, table_rows, scale, out, stream);
 }
 
 int samq_attn_rel_bias(const void* rel_all, int dtype, int64_t images, int rel_pitch, int H, int W, int num_heads,

@@ -2,6 +2,7 @@
 
     python -m sam_quantization_b200.kernel_bench gemm  --M 32768 --N 5120 --K 1280 --gelu
     python -m sam_quantization_b200.kernel_bench quant --M 65536 --K 1280 [--ln] [--gather] [--hadamard full]
+    python -m sam_quantization_b200.kernel_bench attn  --windows 200 --H 14 --W 14 --heads 16 --head-dim 80
     python -m sam_quantization_b200.kernel_bench sweep            # the W8A8 GEMM sweep: M x (K, N) x granularity
 
 Each line of output is JSON: the shape, the mean CUDA-event time over ``--iters`` launches after
@@ -95,6 +96,23 @@ def bench_quant(M, K, dtype=torch.float16, ln=False, gather=False, hadamard=None
             "hadamard": hadamard, "granularity": granularity, "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1)}
 
 
+def bench_window_attention(windows, H, W, heads, head_dim, dtype=torch.bfloat16, iters=50, warmup=10):
+    dev = torch.device("cuda")
+    L, C = H * W, heads * head_dim
+    qkv = [torch.randn((windows * L, 3 * C), device=dev, dtype=dtype) for _ in range(2)]
+    rh = (torch.randn((2 * H - 1, head_dim), device=dev) * 0.02).to(dtype)
+    rw = (torch.randn((2 * W - 1, head_dim), device=dev) * 0.02).to(dtype)
+
+    def run(i):
+        ops.attn_windowed(qkv[i % 2], windows, H, W, heads, rh, rw, head_dim ** -0.5)
+
+    ms = _time(run, iters, warmup)
+    nbytes = windows * L * 4 * C * qkv[0].element_size()
+    flops = 4.0 * windows * heads * L * L * head_dim
+    return {"kernel": "attn_window", "windows": windows, "H": H, "W": W, "heads": heads, "head_dim": head_dim,
+            "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), "tflops": round(flops / ms / 1e9, 1)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -117,6 +135,14 @@ def main():
     q.add_argument("--granularity", default="per_token", choices=list(ops.ACT_GRANULARITY))
     q.add_argument("--iters", type=int, default=50)
     q.add_argument("--warmup", type=int, default=10)
+    a = sub.add_parser("attn")
+    a.add_argument("--windows", type=int, default=200)
+    a.add_argument("--H", type=int, default=14)
+    a.add_argument("--W", type=int, default=14)
+    a.add_argument("--heads", type=int, default=16)
+    a.add_argument("--head-dim", dest="head_dim", type=int, default=80)
+    a.add_argument("--iters", type=int, default=50)
+    a.add_argument("--warmup", type=int, default=10)
     s = sub.add_parser("sweep")
     s.add_argument("--iters", type=int, default=100)
     s.add_argument("--warmup", type=int, default=20)
@@ -124,6 +150,8 @@ def main():
     args = ap.parse_args()
     if args.cmd == "gemm":
         print(json.dumps(bench_gemm(args.M, args.N, args.K, args.gelu, args.residual, args.w_gran, iters=args.iters, warmup=args.warmup)))
+    elif args.cmd == "attn":
+        print(json.dumps(bench_window_attention(args.windows, args.H, args.W, args.heads, args.head_dim, iters=args.iters, warmup=args.warmup)))
     elif args.cmd == "quant":
         print(json.dumps(bench_quant(args.M, args.K, getattr(torch, args.dtype), args.ln, args.gather, args.hadamard,
                                      args.granularity, iters=args.iters, warmup=args.warmup)))

@@ -406,3 +406,32 @@ def attn_rel_bias(qkv: torch.Tensor, images: int, H: int, W: int, num_heads: int
         _lib.check(lib.samq_attn_rel_bias(_ptr(rel_all), _DTYPE_CODE[qkv.dtype], images, rel_all.shape[-1], H, W, num_heads,
                                           _ptr(bias), _stream()))
     return bias
+
+
+def attn_windowed_supported(H: int, W: int, head_dim: int) -> bool:
+    """Shapes ``samq_attn_windowed`` has a variant for."""
+    L, J = H * W, 2 * H - 1 + 2 * W - 1
+    return (L <= 16 and J <= 16 and head_dim in (16, 32, 64)) or (L <= 208 and J <= 56 and head_dim in (64, 80))
+
+
+def attn_windowed(qkv: torch.Tensor, windows: int, H: int, W: int, num_heads: int, rel_pos_h: torch.Tensor,
+                  rel_pos_w: torch.Tensor, scale: float, table: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Windowed attention with decomposed relative position bias in one kernel
+    (``samq_attn_windowed``): ``qkv`` [windows*H*W, 3C] -> [windows*H*W, C], same dtype.
+    ``table`` is an optional cached ``rel_pos_table`` of the two tables."""
+    _require_cuda(qkv, "qkv")
+    lib = _lib.load()
+    tokens, three_c = qkv.shape
+    C = three_c // 3
+    d = C // num_heads
+    if tokens != windows * H * W or not qkv.is_contiguous():
+        raise ValueError("qkv must be a contiguous [windows*H*W, 3C] tensor")
+    if rel_pos_h.shape != (2 * H - 1, d) or rel_pos_w.shape != (2 * W - 1, d):
+        raise ValueError("relative position tables must be [2H-1, d] and [2W-1, d]")
+    if table is None:
+        table = rel_pos_table(rel_pos_h, rel_pos_w, qkv.dtype, qkv.device)
+    out = torch.empty((tokens, C), dtype=qkv.dtype, device=qkv.device)
+    with torch.cuda.device(qkv.device), _Timed("attn_window", tokens * 4 * C * qkv.element_size()):
+        _lib.check(lib.samq_attn_windowed(_ptr(qkv), _DTYPE_CODE[qkv.dtype], windows, H, W, num_heads, d,
+                                          _ptr(table), table.shape[0], float(scale), _ptr(out), _stream()))
+    return out

@@ -134,6 +134,10 @@ class Attention(nn.Module):
         self.attn_dtype: Optional[torch.dtype] = None
         self.global_chunk = 4            # images per attention call when the bias is [heads, 4096, 4096]
         self.native_prep = True          # build the attention inputs with the library's CUDA kernels when possible
+        # whole windowed attention in the library's own kernel (samq_attn_windowed).  Off by default: at
+        # 0.43 ms for 200 windows x 16 heads it is still slower than augmented rows + the fused library
+        # attention (0.31 ms); it needs K/V prefetch across windows to hide its load phase
+        self.fused_window_kernel = False
         self._onehot = {}
         if use_rel_pos:
             assert input_size is not None
@@ -193,6 +197,9 @@ class Attention(nn.Module):
         extra = H + W
         if self._native(qkv, d, H, W):
             from . import ops
+            if self.fused_window_kernel and ops.attn_windowed_supported(H, W, d):
+                return ops.attn_windowed(qkv, B, H, W, nh, self.rel_pos_h, self.rel_pos_w, self.scale,
+                                         table=self._rel_table(qkv.dtype, qkv.device))
             if d + extra <= 128:
                 width = (d + extra + 7) // 8 * 8
                 qa, ka = ops.attn_window_prep(qkv, H, W, nh, self.rel_pos_h, self.rel_pos_w, self.scale, width,

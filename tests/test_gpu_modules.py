@@ -265,3 +265,25 @@ def test_attention_prep_kernels_against_torch_path(cuda_device, dtype, H, W, dim
     tol = 3e-2 if dtype == torch.bfloat16 else 4e-3
     assert rel_err(a.float(), b.float()) < tol
     assert cosine(a, b) > 0.9999
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("H,W,dim,nh", [(14, 14, 160, 2), (4, 4, 64, 4), (14, 14, 256, 4), (13, 9, 80, 1)])
+def test_windowed_attention_kernel_variants_agree(cuda_device, dtype, H, W, dim, nh):
+    """Three routes to the same windowed attention: the one-kernel version, the augmented-row
+    version through the library attention, and plain torch ops."""
+    from sam_quantization_b200.sam_encoder import Attention
+    torch.manual_seed(7 * H + dim)
+    attn = Attention(dim, nh, use_rel_pos=True, input_size=(H, W)).to(cuda_device, dtype)
+    with torch.no_grad():
+        attn.rel_pos_h.normal_(0, 0.3)
+        attn.rel_pos_w.normal_(0, 0.3)
+        B = 5
+        qkv = torch.randn(B * H * W, 3 * dim, device=cuda_device, dtype=dtype)
+        outs = []
+        for native, fused in ((True, True), (True, False), (False, False)):
+            attn.native_prep, attn.fused_window_kernel = native, fused
+            outs.append(attn.attend_flat(qkv, B, H, W).float())
+    tol = 3e-2 if dtype == torch.bfloat16 else 4e-3
+    assert rel_err(outs[0], outs[2]) < tol and rel_err(outs[1], outs[2]) < tol
+    assert cosine(outs[0], outs[2]) > 0.9999
