@@ -109,11 +109,16 @@ class RefActQuantWrapper(nn.Module):
         self.had_K, self.K, self.had_dim = None, 1, 0
         self.online_full_had = self.online_partial_had = False
         self.quantize_input = self.quantize_output = False
+        # optional: the online x @ Q of quarot/model_utils.py:146-152 evaluated as
+        # hadU(x * signs) in fp32 (Q = diag(signs) H / sqrt(n), hadamard_utils.py:86-94) and rounded once
+        self.pre_signs, self.pre_hadK, self.pre_K = None, None, 1
         fake_quant(module.weight.data, weight_quant, group_size, n_bit)
 
     @torch.no_grad()
     def forward(self, x):
         dt = x.dtype
+        if self.pre_signs is not None:
+            x = matmul_hadU(x.float() * self.pre_signs.to(x.device).float(), self.pre_hadK, self.pre_K).to(dt)
         if self.online_full_had:
             x = matmul_hadU(x.float(), self.had_K, self.K).to(dt)
         elif self.online_partial_had:
