@@ -27,6 +27,7 @@ EXPORTED_SYMBOLS = (
     "samq_weight_quant_i8",
     "samq_act_quant_per_tensor_static",
     "samq_gemm_i8",
+    "samq_gemm_set_pair_mode",
     "samq_attn_window_prep",
     "samq_attn_rel_bias",
     "samq_attn_windowed",
@@ -123,6 +124,8 @@ def load() -> ctypes.CDLL:
         c_int, c_void_p, c_int, c_int64,                 # activation, out, out_dtype, ldo
         c_void_p, c_void_p,                              # status, stream
     ]
+    lib.samq_gemm_set_pair_mode.restype = c_int
+    lib.samq_gemm_set_pair_mode.argtypes = [c_int]
     lib.samq_attn_window_prep.restype = c_int
     lib.samq_attn_window_prep.argtypes = [
         c_void_p, c_void_p, c_int, c_int64, c_int,              # qkv, rel_all, dtype, tokens, rel_pitch

@@ -2,6 +2,7 @@
 // into the kernels.  Declarations and the reference interfaces they replace: include/samq.h.
 #include "common.cuh"
 #include <string.h>
+#include <atomic>
 
 namespace samq {
 
@@ -33,6 +34,12 @@ int gemm_i8_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
                      const void* bias, const void* residual, int64_t ldr, int activation,
                      void* out, int out_dtype, int64_t ldo, int32_t* status, void* stream);
 
+int gemm_i8_pair_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
+                          int64_t M, int64_t N, int64_t K,
+                          const float* a_scale, int a_gran, const float* w_scale, int w_gran, int group_size,
+                          const void* bias, const void* residual, int64_t ldr, int activation,
+                          void* out, int out_dtype, int64_t ldo, int32_t* status, void* stream);
+
 int gemm_i8_grouped_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
                              int64_t M, int64_t N, int64_t K,
                              const float* a_scale, int a_gran, const float* w_scale, int w_gran, int group_size,
@@ -48,6 +55,10 @@ int attn_window_dispatch(const void* qkv, int dtype, int64_t windows, int H, int
                          const void* table, int table_rows, float scale, void* out, void* stream);
 
 }  // namespace samq
+
+namespace {
+std::atomic<int> g_gemm_pair_mode{SAMQ_GEMM_PAIR_NEVER};
+}
 
 extern "C" {
 
@@ -126,8 +137,19 @@ int samq_gemm_i8(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
     if (a_gran == SAMQ_GRAN_GROUP || w_gran == SAMQ_GRAN_GROUP)
         return samq::gemm_i8_grouped_dispatch(A, lda, W, ldw, M, N, K, a_scale, a_gran, w_scale, w_gran, group_size,
                                               bias, residual, ldr, activation, out, out_dtype, ldo, status, stream);
+    const int mode = g_gemm_pair_mode.load(std::memory_order_relaxed);
+    // CTA pairs pay off once there are enough 256-row tiles to fill the device
+    if (mode == SAMQ_GEMM_PAIR_ALWAYS || (mode == SAMQ_GEMM_PAIR_AUTO && M >= SAMQ_GEMM_PAIR_MIN_ROWS))
+        return samq::gemm_i8_pair_dispatch(A, lda, W, ldw, M, N, K, a_scale, a_gran, w_scale, w_gran, group_size,
+                                           bias, residual, ldr, activation, out, out_dtype, ldo, status, stream);
     return samq::gemm_i8_dispatch(A, lda, W, ldw, M, N, K, a_scale, a_gran, w_scale, w_gran, group_size,
                                   bias, residual, ldr, activation, out, out_dtype, ldo, status, stream);
+}
+
+int samq_gemm_set_pair_mode(int mode)
+{
+    if (mode < SAMQ_GEMM_PAIR_NEVER || mode > SAMQ_GEMM_PAIR_ALWAYS) return -1;
+    return g_gemm_pair_mode.exchange(mode, std::memory_order_relaxed);
 }
 
 }  // extern "C"

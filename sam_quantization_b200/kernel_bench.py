@@ -115,6 +115,8 @@ def bench_window_attention(windows, H, W, heads, head_dim, dtype=torch.bfloat16,
 
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--pair-mode", dest="pair_mode", type=int, default=None, choices=[0, 1, 2],
+                    help="K2 implementation: 0 single CTAs, 1 by size, 2 CTA pairs (default: the library's)")
     sub = ap.add_subparsers(dest="cmd", required=True)
     g = sub.add_parser("gemm")
     g.add_argument("--M", type=int, default=32768)
@@ -148,6 +150,8 @@ def main():
     s.add_argument("--warmup", type=int, default=20)
     s.add_argument("--granularities", default="per_tensor,per_channel")
     args = ap.parse_args()
+    if args.pair_mode is not None:
+        ops.set_gemm_pair_mode(args.pair_mode)
     if args.cmd == "gemm":
         print(json.dumps(bench_gemm(args.M, args.N, args.K, args.gelu, args.residual, args.w_gran, iters=args.iters, warmup=args.warmup)))
     elif args.cmd == "attn":

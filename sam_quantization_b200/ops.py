@@ -288,6 +288,20 @@ def quantize_weight(w: torch.Tensor, granularity: int = GRAN_ROW, group_size: Op
     return out
 
 
+GEMM_PAIR_NEVER, GEMM_PAIR_AUTO, GEMM_PAIR_ALWAYS = 0, 1, 2
+
+
+def set_gemm_pair_mode(mode: int) -> int:
+    """Choose the K2 implementation: single CTAs, CTA pairs (tcgen05 cta_group::2), or by size.
+
+    Returns the previous mode.  Both implementations give bit-identical results.
+    """
+    prev = _lib.load().samq_gemm_set_pair_mode(int(mode))
+    if prev < 0:
+        raise ValueError(f"unknown GEMM pair mode {mode}")
+    return prev
+
+
 def gemm_i8(a_q: torch.Tensor, w_q: torch.Tensor,
             a_scale: Optional[torch.Tensor] = None, w_scale: Optional[torch.Tensor] = None,
             a_gran: int = GRAN_ROW, w_gran: int = GRAN_ROW, group_size: int = 0,

@@ -177,3 +177,68 @@ def test_grouped_gemm_rejects_small_groups(cuda_device):
     w = torch.zeros((8, 256), dtype=torch.int8, device=dev)
     with pytest.raises(SamqError):
         ops.gemm_i8(a, w, torch.ones(8, device=dev), torch.ones((8, 8), device=dev), 0, 2, 32, out_dtype=torch.float16)
+
+
+# ---- CTA-pair implementation (tcgen05 cta_group::2) --------------------------------------------
+
+@pytest.fixture
+def pair_mode(cuda_device):
+    from sam_quantization_b200 import ops
+    prev = ops.set_gemm_pair_mode(ops.GEMM_PAIR_ALWAYS)
+    yield
+    ops.set_gemm_pair_mode(prev)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (1, 8, 16), (196, 2304, 768), (300, 520, 400), (129, 136, 1280),
+                                   (4900, 768, 3072), (4096, 3072, 768), (77, 1280, 5120), (385, 257 * 8, 144)])
+def test_pair_int32_accumulators_exact(cuda_device, pair_mode, M, N, K):
+    from sam_quantization_b200 import ops
+    rng = np.random.default_rng(M * 11 + N)
+    a, w = rand_codes(rng, (M, K)), rand_codes(rng, (N, K))
+    acc = ops.gemm_i8(torch.from_numpy(a).to(cuda_device), torch.from_numpy(w).to(cuda_device), out_dtype=torch.int32)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert np.array_equal(acc.cpu().numpy(), O.int32_accumulators(a, w))
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("act,use_res", [(0, False), (1, False), (0, True), (1, True)])
+def test_pair_matches_single_cta_bit_for_bit(cuda_device, dt, act, use_res):
+    """Same accumulators, same epilogue arithmetic: the two implementations must agree exactly,
+    on a shape with ragged M, N and K and more tiles than CTA pairs."""
+    from sam_quantization_b200 import ops
+    g = torch.Generator(device="cpu").manual_seed(17)
+    M, N, K = 9 * 256 + 77, 2304 + 72, 784
+    dev = cuda_device
+    a = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8).to(dev)
+    w = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8).to(dev)
+    sa = (torch.rand(M, generator=g) * 0.05 + 0.001).to(dev)
+    sw = (torch.rand(N, generator=g) * 0.001 + 0.0001).to(dev)
+    bias = (torch.randn(N, generator=g) * 0.5).to(TDT[dt]).to(dev)
+    res = torch.randn((M, N), generator=g).to(TDT[dt]).to(dev) if use_res else None
+    outs = []
+    for mode in (ops.GEMM_PAIR_NEVER, ops.GEMM_PAIR_ALWAYS):
+        prev = ops.set_gemm_pair_mode(mode)
+        try:
+            outs.append(ops.gemm_i8(a, w, sa, sw, bias=bias, residual=res, activation=act, out_dtype=TDT[dt]))
+            torch.cuda.synchronize()
+            ops.check_status()
+        finally:
+            ops.set_gemm_pair_mode(prev)
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_pair_unaligned_output_takes_direct_stores(cuda_device, pair_mode):
+    from sam_quantization_b200 import ops
+    rng = np.random.default_rng(23)
+    M, N, K = 300, 250, 256                      # N * 2 bytes is not a multiple of 16: no TMA store
+    a, w = rand_codes(rng, (M, K)), rand_codes(rng, (N, K))
+    sa = (rng.random(M) * 0.05 + 0.001).astype(np.float32)
+    sw = (rng.random(N) * 0.001 + 0.0001).astype(np.float32)
+    dev = cuda_device
+    y = ops.gemm_i8(torch.from_numpy(a).to(dev), torch.from_numpy(w).to(dev), torch.from_numpy(sa).to(dev),
+                    torch.from_numpy(sw).to(dev), out_dtype=torch.float16)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = O.dequant_epilogue(O.int32_accumulators(a, w), sa, sw, None, None, None, "f16")
+    assert np.all(np.abs(f32(y) - want) <= 2.0 ** -10 * np.maximum(np.abs(want), 1e-2) + 1e-6)
