@@ -296,6 +296,151 @@ quant_rows_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx, int
 }
 
 // ---------------------------------------------------------------------------
+// Lean row kernel for the cases the encoder's fused block runs: fp16 arithmetic, one scale per
+// row, codes only (no fake-quantized or transformed copy), K a multiple of 256 so that every
+// lane owns exactly NV 16-byte vectors.  Same results as quant_rows_kernel, about a third of its
+// instructions per element: the exact division and the LayerNorm run on packed pairs
+// (fma.rn.f32x2), the absolute maximum and the rounding on packed halves, and gamma / beta sit
+// in shared memory as fp32, converted once per CTA instead of once per row.
+//   SRC_BF16 : x holds bf16 values that the model casts to fp16 first (attention output)
+//   LN       : y = half(gamma * (rstd * (x - mean)) + beta), fp32 two-pass statistics
+// A CTA of 8 warps walks `rows_per_cta` consecutive rows, one row per warp at a time.
+// ---------------------------------------------------------------------------
+template <bool CLAMP>
+__device__ __forceinline__ uint2 codes_of_vector(const uint4& hv, float2 inv2, float2 neg_s2, __half2 lo, __half2 hi) {
+    const __half2* h = reinterpret_cast<const __half2*>(&hv);
+    const __half2 magic = __float2half2_rn(1536.0f);
+    uint32_t hb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        const float2 y0 = __fmul2_rn(f, inv2);
+        const float2 e = __ffma2_rn(y0, neg_s2, f);
+        const float2 y = __ffma2_rn(e, inv2, y0);                 // correctly rounded f / s
+        __half2 q = __floats2half2_rn(y.x, y.y);                  // the fp16 quotient of the reference
+        if (CLAMP) q = __hmin2(__hmax2(q, lo), hi);
+        q = __hadd2(q, magic);                                    // ulp 1 in [1024, 2048): round-half-even
+        hb[j] = *reinterpret_cast<uint32_t*>(&q);
+    }
+    return make_uint2(__byte_perm(hb[0], hb[1], 0x6420), __byte_perm(hb[2], hb[3], 0x6420));
+}
+
+template <bool SRC_BF16, bool LN, int NV>
+__global__ void __launch_bounds__(256)
+quant_rows_fast_kernel(const uint16_t* __restrict__ x, int64_t M, int K, int64_t ldx, int rows_per_cta,
+                       const int32_t* __restrict__ row_map, const __half* __restrict__ gamma,
+                       const __half* __restrict__ beta, float ln_eps, float qmax,
+                       int8_t* __restrict__ q_out, float* __restrict__ scale_out)
+{
+    extern __shared__ float4 ln_smem[];            // LN: [2][nvec] gamma then [2][nvec] beta, as fp32 quads
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nvec = NV * 32;
+    if constexpr (LN) {
+        for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+            float g[8], b[8];
+            unpack<__half>(*reinterpret_cast<const uint4*>(gamma + (int64_t)v * 8), g);
+            unpack<__half>(*reinterpret_cast<const uint4*>(beta + (int64_t)v * 8), b);
+            ln_smem[v] = make_float4(g[0], g[1], g[2], g[3]);
+            ln_smem[nvec + v] = make_float4(g[4], g[5], g[6], g[7]);
+            ln_smem[2 * nvec + v] = make_float4(b[0], b[1], b[2], b[3]);
+            ln_smem[3 * nvec + v] = make_float4(b[4], b[5], b[6], b[7]);
+        }
+        __syncthreads();
+    }
+    const __half2 hi = __float2half2_rn(qmax), lo = __float2half2_rn(-qmax);
+    const int64_t row0 = (int64_t)blockIdx.x * rows_per_cta;
+    for (int r = warp; r < rows_per_cta; r += 8) {
+        const int64_t row = row0 + r;
+        if (row >= M) break;
+        int64_t src = row;
+        if (row_map != nullptr) src = row_map[row];
+        const bool live = src >= 0;
+        const uint16_t* xr = x + (live ? src : 0) * ldx;
+        uint4 raw[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            raw[i] = live ? ld_stream(xr + (int64_t)(i * 32 + lane) * 8) : make_uint4(0, 0, 0, 0);
+
+        if constexpr (SRC_BF16) {
+            // bf16 -> fp32 is a shift; fp32 -> fp16 rounds to nearest even as the cast does
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                uint32_t* w = reinterpret_cast<uint32_t*>(&raw[i]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const __half2 h = __floats2half2_rn(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xFFFF0000u));
+                    w[j] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+            }
+        }
+        if constexpr (LN) {
+            if (live) {                                              // warp-uniform
+                float2 d[NV][4];
+                float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { d[i][j] = __half22float2(h[j]); acc = __fadd2_rn(acc, d[i][j]); }
+                }
+                float sum = acc.x + acc.y;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                const float mean = sum / (float)K;
+                const float2 nmean = make_float2(-mean, -mean);
+                acc = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { d[i][j] = __fadd2_rn(d[i][j], nmean); acc = __ffma2_rn(d[i][j], d[i][j], acc); }
+                }
+                float var = acc.x + acc.y;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+                const float rstd = rsqrtf(var / (float)K + ln_eps);
+                const float2 rstd2 = make_float2(rstd, rstd);
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    const int v = i * 32 + lane;
+                    const float4 g0 = ln_smem[v], g1 = ln_smem[nvec + v], b0 = ln_smem[2 * nvec + v], b1 = ln_smem[3 * nvec + v];
+                    const float2 y0 = __ffma2_rn(make_float2(g0.x, g0.y), __fmul2_rn(rstd2, d[i][0]), make_float2(b0.x, b0.y));
+                    const float2 y1 = __ffma2_rn(make_float2(g0.z, g0.w), __fmul2_rn(rstd2, d[i][1]), make_float2(b0.z, b0.w));
+                    const float2 y2 = __ffma2_rn(make_float2(g1.x, g1.y), __fmul2_rn(rstd2, d[i][2]), make_float2(b1.x, b1.y));
+                    const float2 y3 = __ffma2_rn(make_float2(g1.z, g1.w), __fmul2_rn(rstd2, d[i][3]), make_float2(b1.z, b1.w));
+                    __half2* h = reinterpret_cast<__half2*>(&raw[i]);
+                    h[0] = __floats2half2_rn(y0.x, y0.y); h[1] = __floats2half2_rn(y1.x, y1.y);
+                    h[2] = __floats2half2_rn(y2.x, y2.y); h[3] = __floats2half2_rn(y3.x, y3.y);
+                }
+            }
+        }
+
+        __half2 m2 = __float2half2_rn(0.f);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+            m2 = __hmax2(m2, __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3]))));
+        }
+        const float m = warp_max(fmaxf(__low2float(m2), __high2float(m2)));
+        const float s = scale_from_absmax<__half>(m, qmax);
+        if (lane == 0 && scale_out != nullptr) scale_out[row] = s;
+        const float inv = __frcp_rn(s);
+        const float2 inv2 = make_float2(inv, inv), neg_s2 = make_float2(-s, -s);
+        int8_t* qr = q_out + row * K;
+        // A normal fp16 scale is within 2^-11 of absmax / qmax, so no quotient rounds beyond qmax
+        // and the clamp can go; a subnormal scale (absmax below ~8e-3) keeps it.
+        if (s >= 6.103515625e-05f) {
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+                *reinterpret_cast<uint2*>(qr + (int64_t)(i * 32 + lane) * 8) = codes_of_vector<false>(raw[i], inv2, neg_s2, lo, hi);
+        } else {
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+                *reinterpret_cast<uint2*>(qr + (int64_t)(i * 32 + lane) * 8) = codes_of_vector<true>(raw[i], inv2, neg_s2, lo, hi);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Generic kernel: one warp per (row, group) unit, scalar accesses, two passes.
 // Covers every shape the vector kernel does not (odd K, unaligned rows,
 // very long rows, group sizes that are not 8 * 2^j).
@@ -524,6 +669,54 @@ static int launch_rows(const SrcT* x, int64_t M, int K, int64_t ldx, const Prolo
     const int nvec = K / E;
     if (ln && !(vec_ok && nvec <= 320))
         return fail(SAMQ_ERR_UNSUPPORTED, "fused LayerNorm needs 16-byte aligned rows of at most %d elements (K=%d)", 320 * E, K);
+    if constexpr (std::is_same<T, __half>::value) {
+        // the lean kernel: fp16 arithmetic, per-row scale, codes only, whole vectors per lane
+        const bool src_bf16 = std::is_same<SrcT, __nv_bfloat16>::value;
+        if (vec_ok && gran == SAMQ_GRAN_ROW && divisor == nullptr && fq == nullptr && tx == nullptr && q != nullptr &&
+            nvec % 32 == 0 && !(ln && src_bf16)) {
+            const int nv = nvec / 32;
+            const uint16_t* xs = reinterpret_cast<const uint16_t*>(x);
+            const __half* g = static_cast<const __half*>(pro.ln_gamma);
+            const __half* b = static_cast<const __half*>(pro.ln_beta);
+            const int rows_per_cta = ln ? 32 : 8;
+            const unsigned grid = (unsigned)((M + rows_per_cta - 1) / rows_per_cta);
+            const size_t smem = ln ? (size_t)nvec * 64 : 0;
+            bool launched = true;
+#define SAMQ_FAST(BF, LN_, NVAL)                                                                            \
+            quant_rows_fast_kernel<BF, LN_, NVAL><<<grid, 256, smem, st>>>(xs, M, K, ldx, rows_per_cta, pro.row_map, \
+                                                                           g, b, pro.ln_eps, qmax, q, scale)
+            if (ln) {
+                switch (nv) {
+                case 3: SAMQ_FAST(false, true, 3); break;
+                case 4: SAMQ_FAST(false, true, 4); break;
+                case 5: SAMQ_FAST(false, true, 5); break;
+                default: launched = false;
+                }
+            } else if (src_bf16) {
+                switch (nv) {
+                case 3: SAMQ_FAST(true, false, 3); break;
+                case 4: SAMQ_FAST(true, false, 4); break;
+                case 5: SAMQ_FAST(true, false, 5); break;
+                default: launched = false;
+                }
+            } else {
+                switch (nv) {
+                case 3: SAMQ_FAST(false, false, 3); break;
+                case 4: SAMQ_FAST(false, false, 4); break;
+                case 5: SAMQ_FAST(false, false, 5); break;
+                case 12: SAMQ_FAST(false, false, 12); break;
+                case 16: SAMQ_FAST(false, false, 16); break;
+                case 20: SAMQ_FAST(false, false, 20); break;
+                default: launched = false;
+                }
+            }
+#undef SAMQ_FAST
+            if (launched) {
+                SAMQ_CUDA_TRY(cudaGetLastError());
+                return SAMQ_OK;
+            }
+        }
+    }
     if (vec_ok) {
 #define SAMQ_LAUNCH(NVAL, MULTI_, LN_, TPR, GRID, BLOCK)                                               \
         quant_rows_kernel<T, SrcT, NVAL, MULTI_, LN_><<<GRID, BLOCK, 0, st>>>(x, M, K, ldx, TPR, pro,    \

@@ -274,3 +274,77 @@ def test_sign_of_zero_survives(cuda_device):
         _, _, fq = O.quantize(O.rnd(x, dt), "per_token", dt)
         got = f32(out["fq"])
         assert np.array_equal(got, fq) and np.array_equal(np.signbit(got), np.signbit(fq))
+
+
+# ---- the lean kernel (fp16, per-row scale, codes only, K % 256 == 0) ----------------------------
+
+def _lean_rows(M, K, seed):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    x[:, rng.permutation(K)[: max(1, K // 100)]] *= 20
+    x[3] = 0                                   # scale floor 1e-5 / 127
+    x[4] *= 1e-4                               # subnormal fp16 scale: quotients beyond 127 must saturate
+    x[5] *= 3e-3
+    x[6] *= 200                                # large values, still finite in fp16
+    x[8, 1:] = 0                               # a single non-zero element
+    return x
+
+
+@pytest.mark.parametrize("K", [768, 1024, 1280, 3072, 4096, 5120])
+def test_lean_kernel_bit_exact(cuda_device, K):
+    from sam_quantization_b200 import ops
+    x_np = _lean_rows(301, K, K + 1)
+    x = to_dev(x_np, "f16", cuda_device)
+    out = ops.quantize(x, 0)                                   # codes + scales only: the lean kernel
+    general = ops.quantize(x, 0, fake_quant=True)              # any extra output takes the general kernel
+    q, s, _ = O.quantize(O.rnd(x_np, "f16"), "per_token", "f16")
+    assert np.array_equal(out["q"].cpu().numpy(), O.saturate_codes(q))
+    assert np.array_equal(f32(out["scale"]), np.asarray(s, np.float32))
+    assert torch.equal(out["q"], general["q"]) and torch.equal(out["scale"], general["scale"])
+
+
+@pytest.mark.parametrize("K", [768, 1280])
+def test_lean_kernel_gather_and_bf16_source(cuda_device, K):
+    from sam_quantization_b200 import ops
+    x_np = _lean_rows(64, K, K + 2)
+    x = to_dev(x_np, "f16", cuda_device)
+    rm = torch.tensor([63, -1, 0, 4, 4, 3, -1, 17, 25, 8, 6], dtype=torch.int32, device=cuda_device)
+    out = ops.quantize(x, 0, row_map=rm)
+    ref = ops.quantize(x, 0, row_map=rm, transformed=True)
+    assert torch.equal(out["q"], ref["q"]) and torch.equal(out["scale"], ref["scale"])
+    assert int(out["q"][1].abs().max()) == 0
+    xb = to_dev(x_np, "bf16", cuda_device)
+    xb[7] *= 1e-3                                              # values that lose bits in the cast to fp16
+    out = ops.quantize(xb, 0, as_dtype=torch.float16, row_map=rm)
+    ref = ops.quantize(xb.to(torch.float16), 0, row_map=rm, transformed=True)
+    assert torch.equal(out["q"], ref["q"]) and torch.equal(out["scale"], ref["scale"])
+
+
+@pytest.mark.parametrize("K", [768, 1024, 1280])
+def test_lean_kernel_layernorm(cuda_device, K):
+    """The lean kernel's LayerNorm sums pairs of lanes' partial sums in another order than the
+    general kernel: statistics agree to a few fp32 ulps, codes to one step on a handful of
+    elements, padding rows are exact zeros."""
+    from sam_quantization_b200 import ops
+    g = torch.Generator().manual_seed(K + 3)
+    x = (torch.randn(300, K, generator=g) * 2 + 0.3).half().to(cuda_device)
+    x[:, 11] *= 30
+    w = (1 + 0.2 * torch.randn(K, generator=g)).half().to(cuda_device)
+    b = (0.1 * torch.randn(K, generator=g)).half().to(cuda_device)
+    rm = torch.arange(299, -1, -1, dtype=torch.int32, device=cuda_device)
+    rm[5] = -1
+    for row_map in (None, rm):
+        out = ops.quantize(x, 0, layer_norm=(w, b, 1e-6), row_map=row_map)
+        ref = ops.quantize(x, 0, layer_norm=(w, b, 1e-6), row_map=row_map, transformed=True)
+        dq = (out["q"].int() - ref["q"].int()).abs()
+        assert int(dq.max()) <= 1 and float((dq > 0).float().mean()) < 1e-3
+        assert float(((out["scale"] - ref["scale"]).abs() / ref["scale"]).max()) <= 2.0 ** -10
+        if row_map is not None:
+            assert int(out["q"][5].abs().max()) == 0
+        # against torch's LayerNorm followed by the plain kernel
+        ln = torch.nn.functional.layer_norm(x, (K,), w, b, 1e-6)
+        if row_map is not None:
+            ln = torch.where(row_map[:, None] >= 0, ln[row_map.clamp(min=0).long()], torch.zeros((), dtype=ln.dtype, device=ln.device))
+        plain = ops.quantize(ln, 0)
+        dq = (out["q"].int() - plain["q"].int()).abs()
+        assert int(dq.max()) <= 1 and float((dq > 0).float().mean()) < 2e-3
