@@ -235,12 +235,14 @@ int samq_gemm_i8(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
  *   NEVER  - one CTA per 128 x 256 output tile;
  *   ALWAYS - CTA pairs (thread-block clusters of two, tcgen05 cta_group::2) per 256 x 256 tile,
  *            each CTA loading half of the W tile;
- *   AUTO   - pairs when M >= SAMQ_GEMM_PAIR_MIN_ROWS, single CTAs below.
+ *   AUTO   - (the default) pairs when M >= SAMQ_GEMM_PAIR_MIN_ROWS and K >= SAMQ_GEMM_PAIR_MIN_K,
+ *            single CTAs otherwise.
  * Both give bit-identical results.  Returns the previous mode, or -1 for an unknown mode. */
 #define SAMQ_GEMM_PAIR_NEVER  0
 #define SAMQ_GEMM_PAIR_AUTO   1
 #define SAMQ_GEMM_PAIR_ALWAYS 2
 #define SAMQ_GEMM_PAIR_MIN_ROWS 2048
+#define SAMQ_GEMM_PAIR_MIN_K 4096
 int samq_gemm_set_pair_mode(int mode);
 
 /* ---- attention-side helpers (the step between qkv and proj) -------------------------------

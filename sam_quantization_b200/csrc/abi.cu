@@ -57,7 +57,7 @@ int attn_window_dispatch(const void* qkv, int dtype, int64_t windows, int H, int
 }  // namespace samq
 
 namespace {
-std::atomic<int> g_gemm_pair_mode{SAMQ_GEMM_PAIR_NEVER};
+std::atomic<int> g_gemm_pair_mode{SAMQ_GEMM_PAIR_AUTO};
 }
 
 extern "C" {
@@ -138,8 +138,11 @@ int samq_gemm_i8(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
         return samq::gemm_i8_grouped_dispatch(A, lda, W, ldw, M, N, K, a_scale, a_gran, w_scale, w_gran, group_size,
                                               bias, residual, ldr, activation, out, out_dtype, ldo, status, stream);
     const int mode = g_gemm_pair_mode.load(std::memory_order_relaxed);
-    // CTA pairs pay off once there are enough 256-row tiles to fill the device
-    if (mode == SAMQ_GEMM_PAIR_ALWAYS || (mode == SAMQ_GEMM_PAIR_AUTO && M >= SAMQ_GEMM_PAIR_MIN_ROWS))
+    // CTA pairs pay off on long reductions (operand traffic dominates; measured +1.5 % at
+    // K = 5120, -4 % at K = 1280 where the epilogue hand-off across the pair costs more) and
+    // once there are enough 256-row tiles to fill the device
+    if (mode == SAMQ_GEMM_PAIR_ALWAYS ||
+        (mode == SAMQ_GEMM_PAIR_AUTO && M >= SAMQ_GEMM_PAIR_MIN_ROWS && K >= SAMQ_GEMM_PAIR_MIN_K))
         return samq::gemm_i8_pair_dispatch(A, lda, W, ldw, M, N, K, a_scale, a_gran, w_scale, w_gran, group_size,
                                            bias, residual, ldr, activation, out, out_dtype, ldo, status, stream);
     return samq::gemm_i8_dispatch(A, lda, W, ldw, M, N, K, a_scale, a_gran, w_scale, w_gran, group_size,

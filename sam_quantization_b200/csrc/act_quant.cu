@@ -530,46 +530,206 @@ absmax_kernel(const T* __restrict__ x, int64_t M, int K, int64_t ldx,
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ int padded(int i) { return i + (i >> 4); }
 
-template <typename T, typename SrcT>
-__global__ void __launch_bounds__(1024)
+// in-register butterflies over the 4 low index bits of 16 values, strides 1, 2, 4, 8 in that order.
+// Values j and j + 8 travel as one fp32 pair, so the first three stages are packed adds; a - c is
+// formed as fma(c, -1, a), which rounds exactly as the subtraction does.
+__device__ __forceinline__ void butterfly16(float (&v)[16]) {
+    float2 p[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) p[i] = make_float2(v[i], v[i + 8]);
+    const float2 neg1 = make_float2(-1.f, -1.f);
+#pragma unroll
+    for (int s = 1; s < 8; s <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if ((i & s) == 0) {
+                const float2 a = p[i], c = p[i | s];
+                p[i] = __fadd2_rn(a, c);
+                p[i | s] = __ffma2_rn(c, neg1, a);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { v[i] = p[i].x + p[i].y; v[i + 8] = p[i].x - p[i].y; }
+}
+
+// The last arithmetic step of the transform: divide by sqrt(axis) (a true division), round once
+// to T, and track the absolute maximum.
+template <typename T>
+__device__ __forceinline__ float finish_value(float v, const Divider& root, float& m) {
+    v = round_to<T>(div_exact(v, root));
+    m = fmaxf(m, fabsf(v));
+    return v;
+}
+// the same for a pair (fp16: packed division, one conversion each way for both values)
+template <typename T>
+__device__ __forceinline__ float2 finish_pair(float2 v, const Divider& root, float& m) {
+    if constexpr (std::is_same<T, __half>::value) {
+        const float2 inv2 = make_float2(root.inv, root.inv), ns2 = make_float2(-root.s, -root.s);
+        const float2 y0 = __fmul2_rn(v, inv2);
+        const float2 e = __ffma2_rn(y0, ns2, v);
+        const float2 y = __ffma2_rn(e, inv2, y0);
+        const __half2 h = __floats2half2_rn(y.x, y.y);
+        const __half2 a = __habs2(h);
+        m = fmaxf(m, fmaxf(__low2float(a), __high2float(a)));
+        return __half22float2(h);
+    } else {
+        return make_float2(finish_value<T>(v.x, root, m), finish_value<T>(v.y, root, m));
+    }
+}
+
+// The HK x HK mix across chunks for two adjacent columns at a time: the inputs of both columns
+// sit in registers as pairs, the +-1 entries come from shared memory (each stored twice, so one
+// 16-byte load feeds two packed multiply-adds).  `ld` is the row pitch of the stored matrix,
+// `halves` the number of independent HK-chunk blocks the mix is applied to (2 when an order-2HK
+// factor is evaluated as [[A, A], [A, -A]]).  FINISH: also scale, round and track the maximum.
+template <typename T, int HK, bool FINISH>
+__device__ __forceinline__ void mix_columns(float* sm, const float4* hk4, int ld, int cols, int halves,
+                                            int tid, int nthr, const Divider& root, float& m) {
+    const int pairs = cols >> 1;
+    for (int p = tid; p < pairs * halves; p += nthr) {
+        const int half = p / pairs;
+        const int c = (p - half * pairs) << 1;
+        float* col = sm;
+        const int k0 = half * HK;
+        float2 in2[HK];
+#pragma unroll
+        for (int k = 0; k < HK; ++k) in2[k] = make_float2(col[padded((k0 + k) * cols + c)], col[padded((k0 + k) * cols + c + 1)]);
+#pragma unroll 1
+        for (int k = 0; k < HK; ++k) {                   // not unrolled: the inputs alone fill the registers
+            float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int k2 = 0; k2 < HK; k2 += 2) {
+                const float4 h = hk4[(k * ld + k2) >> 1];
+                acc = __ffma2_rn(make_float2(h.x, h.y), in2[k2], acc);
+                acc = __ffma2_rn(make_float2(h.z, h.w), in2[k2 + 1], acc);
+            }
+            if (FINISH) acc = finish_pair<T>(acc, root, m);
+            col[padded((k0 + k) * cols + c)] = acc.x;
+            col[padded((k0 + k) * cols + c + 1)] = acc.y;
+        }
+    }
+}
+
+// `vec` != 0: K % 16 == 0 and every pointer / row pitch allows 16-byte accesses; each thread then
+// moves 16 consecutive elements at a time (two 16-byte loads of fp16, one 16-byte store of codes).
+// HK: the explicit factor this instance is compiled for (1 = none, 12, 20, 40; 0 = any, read at
+// run time).  An order-40 factor of the form [[A, A], [A, -A]] (checked in the kernel) runs as one
+// butterfly across the two halves followed by the order-20 mix with A on each half.
+template <typename T, typename SrcT, int HK>
+__global__ void __launch_bounds__(512)
 hadamard_quant_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx, const int32_t* __restrict__ row_map,
                       const T* __restrict__ divisor, const int8_t* __restrict__ signs,
                       int inner, int axis, int had_k, int log2_pow,
                       const float* __restrict__ hadk, float qmax,
                       int8_t* __restrict__ q_out, float* __restrict__ scale_out,
-                      T* __restrict__ fq_out, T* __restrict__ tx_out)
+                      T* __restrict__ fq_out, T* __restrict__ tx_out, int vec)
 {
-    extern __shared__ float sm[];          // padded(K) floats, then had_k*had_k signs, then 32 floats
-    float* hk = sm + padded(K) + 1;
-    float* red = hk + had_k * had_k;
+    extern __shared__ float4 sm4[];        // padded(K) floats, then the had_k matrix, then 32 floats
+    float* sm = reinterpret_cast<float*>(sm4);
+    const int hk_off = (padded(K) + 1 + 3) & ~3;                      // 16-byte aligned
+    float4* hk4 = reinterpret_cast<float4*>(sm + hk_off);             // entries stored twice: (h, h)
+    float* hk = sm + hk_off;
+    float* red = hk + 2 * had_k * had_k + 4;
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int64_t row = blockIdx.x;
     const int64_t src = row_map != nullptr ? (int64_t)row_map[row] : row;
     const SrcT* xr = x + (src >= 0 ? src : 0) * ldx;
+    constexpr int E = Elem<T>::kPerVec;                               // elements per 16 bytes: 8 or 4
+    const int chunks = K >> 4;
+    const Divider root = make_divider(sqrtf((float)axis));
+    float m = 0.f;                                                    // running |value| maximum of this thread
+    bool finished = false;                                            // the scaling has been folded into a phase
+    // the first four butterfly stages act on 16 consecutive elements: do them before the values
+    // ever reach shared memory
+    const bool first_in_regs = vec && inner == 1 && log2_pow >= 4;
+    const bool only_round = first_in_regs && log2_pow == 4 && HK == 1;
 
     // (a) load (gathered row, or zeros for a padding row), SmoothQuant divisor, sign flip
-    for (int c = tid; c < K; c += nthr) {
-        float v = src >= 0 ? round_to<T>(Elem<SrcT>::up(xr[c])) : 0.f;
-        if (divisor != nullptr) v = round_to<T>(__fdiv_rn(v, Elem<T>::up(divisor[c])));
-        if (signs != nullptr && signs[c] < 0) v = -v;
-        sm[padded(c)] = v;
+    if (vec) {
+        for (int g = tid; g < chunks; g += nthr) {
+            const int c0 = g << 4;
+            float v[16];
+            if (src >= 0) {
+#pragma unroll
+                for (int i = 0; i < 16 / E; ++i) {
+                    float f[E];
+                    unpack<SrcT>(ld_stream(xr + c0 + i * E), f);
+                    if (!std::is_same<SrcT, T>::value) RoundVec<T, E>::run(f);
+#pragma unroll
+                    for (int e = 0; e < E; ++e) v[i * E + e] = f[e];
+                }
+                if (divisor != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 16 / E; ++i) {
+                        float d[E];
+                        unpack<T>(*reinterpret_cast<const uint4*>(divisor + c0 + i * E), d);
+#pragma unroll
+                        for (int e = 0; e < E; ++e) v[i * E + e] = round_to<T>(__fdiv_rn(v[i * E + e], d[e]));
+                    }
+                }
+                if (signs != nullptr) {
+                    const uint4 sg = *reinterpret_cast<const uint4*>(signs + c0);
+                    const uint32_t w[4] = {sg.x, sg.y, sg.z, sg.w};
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if ((w[j >> 2] >> (8 * (j & 3))) & 0x80u) v[j] = -v[j];
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = 0.f;
+            }
+            if (first_in_regs) butterfly16(v);
+            if (only_round) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    const float2 f = finish_pair<T>(make_float2(v[j], v[j + 1]), root, m);
+                    v[j] = f.x; v[j + 1] = f.y;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sm[c0 + g + j] = v[j];       // = padded(c0 + j)
+        }
+        finished = only_round;
+    } else {
+        for (int c = tid; c < K; c += nthr) {
+            float v = src >= 0 ? round_to<T>(Elem<SrcT>::up(xr[c])) : 0.f;
+            if (divisor != nullptr) v = round_to<T>(__fdiv_rn(v, Elem<T>::up(divisor[c])));
+            if (signs != nullptr && signs[c] < 0) v = -v;
+            sm[padded(c)] = v;
+        }
     }
-    if (had_k > 1)
-        for (int i = tid; i < had_k * had_k; i += nthr) hk[i] = hadk[i];
-    __syncthreads();
+    bool blocked40 = false;
+    if constexpr (HK != 1) {
+        for (int i = tid; i < had_k * had_k; i += nthr) { const float h = hadk[i]; hk[2 * i] = h; hk[2 * i + 1] = h; }
+        if constexpr (HK == 40) {
+            // is the matrix [[A, A], [A, -A]] ?
+            int ok = 1;
+            for (int i = tid; i < 400; i += nthr) {
+                const int k = i / 20, k2 = i - k * 20;
+                const float a = hadk[k * 40 + k2];
+                ok &= (hadk[k * 40 + k2 + 20] == a) & (hadk[(k + 20) * 40 + k2] == a) & (hadk[(k + 20) * 40 + k2 + 20] == -a);
+            }
+            blocked40 = __syncthreads_and(ok) != 0;
+        }
+    }
+    // The second round (index bits 4..7) only mixes chunks written by threads of the same
+    // half-warp when every thread owns exactly one chunk and one group: a warp barrier suffices.
+    if (first_in_regs && chunks <= nthr && log2_pow >= 8) __syncwarp(); else __syncthreads();
 
     // (b) butterflies over the power-of-two part of the axis, 4 bits per round
     const int pow_len = 1 << log2_pow;
-    for (int b = 0; b < log2_pow; b += 4) {
+    for (int b = first_in_regs ? 4 : 0; b < log2_pow; b += 4) {
         const int r = min(4, log2_pow - b);
         const int R = 1 << r;
         const int groups = K >> r;
         const int rest_len = pow_len >> r;               // values of the axis index without the r bits
+        const bool last = (HK == 1) && (b + 4 >= log2_pow);
         for (int g = tid; g < groups; g += nthr) {
             // g enumerates (k_chunk, rest, in) with `in` fastest
-            const int in = g % inner;
-            int t = g / inner;
-            const int rest = t % rest_len;
+            int in = 0, t = g;
+            if (inner != 1) { in = g % inner; t = g / inner; }
+            const int rest = t & (rest_len - 1);
             const int kc = t / rest_len;                 // chunk of the had_k part (and outer)
             const int lo = rest & ((1 << b) - 1);
             const int hi = rest >> b;
@@ -579,69 +739,155 @@ hadamard_quant_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx,
             float v[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) if (j < R) v[j] = sm[padded(base + j * step)];
+            if (R == 16) {
+                butterfly16(v);
+            } else {
 #pragma unroll
-            for (int s = 1; s < 16; s <<= 1) {
-                if (s < R) {
+                for (int s = 1; s < 16; s <<= 1) {
+                    if (s < R) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if ((j & s) == 0 && j < R) {
-                            const float a = v[j], c = v[j | s];
-                            v[j] = a + c;
-                            v[j | s] = a - c;
+                        for (int j = 0; j < 16; ++j) {
+                            if ((j & s) == 0 && j < R) {
+                                const float a = v[j], c = v[j | s];
+                                v[j] = a + c;
+                                v[j | s] = a - c;
+                            }
                         }
                     }
+                }
+            }
+            if (last) {
+                if (R == 16) {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) {
+                        const float2 f = finish_pair<T>(make_float2(v[j], v[j + 1]), root, m);
+                        v[j] = f.x; v[j + 1] = f.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) if (j < R) v[j] = finish_value<T>(v[j], root, m);
                 }
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) if (j < R) sm[padded(base + j * step)] = v[j];
         }
-        __syncthreads();
+        if (last) finished = true;
+        else __syncthreads();                            // the closing barrier below follows the last round
     }
 
     // (c) explicit had_k x had_k mix across the chunks
-    if (had_k > 1) {
+    if constexpr (HK != 1) {
         const int cols = pow_len * inner;                // positions inside one chunk
-        // each thread owns whole columns: reads had_k inputs, writes had_k outputs
-        for (int c = tid; c < cols; c += nthr) {
+        int done = 0;                                    // columns handled two at a time
+        if constexpr (HK == 12 || HK == 20) {
+            mix_columns<T, HK, true>(sm, hk4, HK, cols, 1, tid, nthr, root, m);
+            done = cols & ~1;
+        }
+        if constexpr (HK == 40) {
+            if (blocked40 && (cols & 1) == 0) {
+                for (int i = tid; i < 20 * cols; i += nthr) {       // chunk k with chunk k + 20
+                    const float a = sm[padded(i)], c = sm[padded(i + 20 * cols)];
+                    sm[padded(i)] = a + c;
+                    sm[padded(i + 20 * cols)] = a - c;
+                }
+                __syncthreads();
+                mix_columns<T, 20, true>(sm, hk4, 40, cols, 2, tid, nthr, root, m);
+                done = cols;
+            }
+        }
+        // any other factor (and an odd last column): each thread owns whole columns
+        for (int c = done + tid; c < cols; c += nthr) {
             float in_v[64];
             for (int k = 0; k < had_k; ++k) in_v[k] = sm[padded(k * cols + c)];
             for (int k = 0; k < had_k; ++k) {
                 float acc = 0.f;
-                for (int k2 = 0; k2 < had_k; ++k2) acc += hk[k * had_k + k2] * in_v[k2];
-                sm[padded(k * cols + c)] = acc;
+                for (int k2 = 0; k2 < had_k; ++k2) acc += hk[2 * (k * had_k + k2)] * in_v[k2];
+                sm[padded(k * cols + c)] = finish_value<T>(acc, root, m);
             }
         }
-        __syncthreads();
+        finished = true;
     }
 
-    // (d) scale by 1/sqrt(axis) with a true division, round once to T, absmax
-    const Divider root = make_divider(sqrtf((float)axis));
-    float m = 0.f;
-    for (int c = tid; c < K; c += nthr) {
-        const float v = round_to<T>(div_exact(sm[padded(c)], root));
-        sm[padded(c)] = v;
-        m = fmaxf(m, fabsf(v));
+    // (d) a transform of length one has no phase above to carry the scaling
+    if (!finished) {
+        __syncthreads();
+        for (int c = tid; c < K; c += nthr) sm[padded(c)] = finish_value<T>(sm[padded(c)], root, m);
     }
     m = warp_max(m);
     if ((tid & 31) == 0) red[tid >> 5] = m;
-    __syncthreads();
-    if (tid < 32) {
-        float t = (tid < ((nthr + 31) >> 5)) ? red[tid] : 0.f;
-        t = warp_max(t);
-        if (tid == 0) red[0] = t;
+    __syncthreads();                                     // values and per-warp maxima are in shared memory
+    {
+        float t = 0.f;
+        for (int w = 0; w < ((nthr + 31) >> 5); ++w) t = fmaxf(t, red[w]);
+        m = t;
     }
-    __syncthreads();
-    const float s = scale_from_absmax<T>(red[0], qmax);
+    const float s = scale_from_absmax<T>(m, qmax);
     if (tid == 0 && scale_out != nullptr) scale_out[row] = s;
 
     // (e) quantize and store
     const Divider dv = make_divider(s);
-    for (int c = tid; c < K; c += nthr) {
-        const float v = sm[padded(c)];
-        const float q = quant_value<T>(v, dv);
-        if (q_out != nullptr) q_out[row * K + c] = saturate_i8(q, qmax);
-        if (tx_out != nullptr) tx_out[row * K + c] = Elem<T>::down(v);
-        if (fq_out != nullptr) fq_out[row * K + c] = Elem<T>::down(q * s);
+    if (vec) {
+        for (int g = tid; g < chunks; g += nthr) {
+            const int c0 = g << 4;
+            float v16[16], q[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v16[j] = sm[c0 + g + j];
+            if constexpr (std::is_same<T, __half>::value) {
+                if (fq_out == nullptr && tx_out == nullptr && q_out != nullptr) {
+                    // codes only: packed exact division, fp16 rounding of the quotient, clamp, and
+                    // the round-half-even of an fp16 addition of 1536 (see quant_rows_fast_kernel)
+                    const float2 inv2 = make_float2(dv.inv, dv.inv), ns2 = make_float2(-s, -s);
+                    const __half2 hi2 = __float2half2_rn(qmax), lo2 = __float2half2_rn(-qmax), magic = __float2half2_rn(1536.0f);
+                    uint32_t hb[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float2 f = make_float2(v16[2 * j], v16[2 * j + 1]);
+                        const float2 y0 = __fmul2_rn(f, inv2);
+                        const float2 e = __ffma2_rn(y0, ns2, f);
+                        const float2 y = __ffma2_rn(e, inv2, y0);
+                        __half2 h = __floats2half2_rn(y.x, y.y);
+                        h = __hadd2(__hmin2(__hmax2(h, lo2), hi2), magic);
+                        hb[j] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                    *reinterpret_cast<uint4*>(q_out + row * K + c0) =
+                        make_uint4(__byte_perm(hb[0], hb[1], 0x6420), __byte_perm(hb[2], hb[3], 0x6420),
+                                   __byte_perm(hb[4], hb[5], 0x6420), __byte_perm(hb[6], hb[7], 0x6420));
+                    continue;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) q[j] = quant_value<T>(v16[j], dv);
+            if (q_out != nullptr) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    w[i] = code_byte(q[4 * i], qmax) | (code_byte(q[4 * i + 1], qmax) << 8) |
+                           (code_byte(q[4 * i + 2], qmax) << 16) | (code_byte(q[4 * i + 3], qmax) << 24);
+                *reinterpret_cast<uint4*>(q_out + row * K + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+#pragma unroll
+            for (int i = 0; i < 16 / E; ++i) {
+                float f[E];
+                if (tx_out != nullptr) {
+#pragma unroll
+                    for (int e = 0; e < E; ++e) f[e] = v16[i * E + e];
+                    *reinterpret_cast<uint4*>(tx_out + row * K + c0 + i * E) = pack<T>(f);
+                }
+                if (fq_out != nullptr) {
+#pragma unroll
+                    for (int e = 0; e < E; ++e) f[e] = q[i * E + e] * s;      // rounded to T by pack()
+                    *reinterpret_cast<uint4*>(fq_out + row * K + c0 + i * E) = pack<T>(f);
+                }
+            }
+        }
+    } else {
+        for (int c = tid; c < K; c += nthr) {
+            const float v = sm[padded(c)];
+            const float q = quant_value<T>(v, dv);
+            if (q_out != nullptr) q_out[row * K + c] = saturate_i8(q, qmax);
+            if (tx_out != nullptr) tx_out[row * K + c] = Elem<T>::down(v);
+            if (fq_out != nullptr) fq_out[row * K + c] = Elem<T>::down(q * s);
+        }
     }
 }
 
@@ -794,15 +1040,27 @@ static int quant_typed(const SrcT* x, int64_t M, int K, int64_t ldx, const Prolo
         if (hk > 1 && had->hadk == nullptr)
             return fail(SAMQ_ERR_BAD_ARG, "had_k=%d needs the hadk matrix", hk);
         int log2_pow = 0; while ((1 << log2_pow) < pw) ++log2_pow;
-        const size_t smem = (size_t)(K + (K >> 4) + 2 + hk * hk + 32) * sizeof(float);
+        const size_t smem = (size_t)(K + (K >> 4) + 8 + 2 * hk * hk + 4 + 32) * sizeof(float);
         if (smem > 200 * 1024) return fail(SAMQ_ERR_TOO_LARGE, "row of K=%d does not fit in shared memory", K);
-        if (smem > 48 * 1024)
-            SAMQ_CUDA_TRY(cudaFuncSetAttribute(hadamard_quant_kernel<T, SrcT>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         int threads = ((K / 16 + 31) / 32) * 32;
-        threads = threads < 32 ? 32 : (threads > 1024 ? 1024 : threads);
-        hadamard_quant_kernel<T, SrcT><<<(unsigned)M, threads, smem, st>>>(x, M, K, ldx, pro.row_map, divisor, had->signs,
-            inner, axis, hk, log2_pow, had->hadk, qmax, q, scale, fq, tx);
+        threads = threads < 32 ? 32 : (threads > 512 ? 512 : threads);
+        auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+        const int vec = (K % 16 == 0) && (ldx % Elem<T>::kPerVec == 0) && al16(x) && al16(divisor) && al16(had->signs) &&
+                        al16(q) && al16(fq) && al16(tx);
+#define SAMQ_HAD(HKV)                                                                                                  \
+        do {                                                                                                           \
+            if (smem > 48 * 1024)                                                                                      \
+                SAMQ_CUDA_TRY(cudaFuncSetAttribute(hadamard_quant_kernel<T, SrcT, HKV>,                                \
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));           \
+            hadamard_quant_kernel<T, SrcT, HKV><<<(unsigned)M, threads, smem, st>>>(x, M, K, ldx, pro.row_map, divisor, \
+                had->signs, inner, axis, hk, log2_pow, had->hadk, qmax, q, scale, fq, tx, vec);                         \
+        } while (0)
+        if (hk == 1) SAMQ_HAD(1);
+        else if (hk == 12) SAMQ_HAD(12);
+        else if (hk == 20) SAMQ_HAD(20);
+        else if (hk == 40) SAMQ_HAD(40);
+        else SAMQ_HAD(0);
+#undef SAMQ_HAD
         SAMQ_CUDA_TRY(cudaGetLastError());
         return SAMQ_OK;
     }

@@ -31,18 +31,90 @@ __device__ __forceinline__ float gelu_erf(float x) {
     return fmaf(-fabsf(x), h, fmaxf(x, 0.f));
 }
 
+// The same function on two values at once: the polynomial and the final multiply-add run as
+// packed fp32x2 FMAs (same roundings as the scalar form, so the results are identical).
+__device__ __forceinline__ float2 gelu_erf2(float2 x) {
+    const float2 u = make_float2(fminf(fabsf(x.x), 6.08f), fminf(fabsf(x.y), 6.08f));
+    float2 q = make_float2(3.586083039e-05f, 3.586083039e-05f);
+    q = __ffma2_rn(q, u, make_float2(-7.942179800e-04f, -7.942179800e-04f));
+    q = __ffma2_rn(q, u, make_float2(8.166280575e-03f, 8.166280575e-03f));
+    q = __ffma2_rn(q, u, make_float2(-5.355186760e-02f, -5.355186760e-02f));
+    q = __ffma2_rn(q, u, make_float2(-4.586586654e-01f, -4.586586654e-01f));
+    q = __ffma2_rn(q, u, make_float2(-1.151242375e+00f, -1.151242375e+00f));
+    q = __ffma2_rn(q, u, make_float2(-9.999881387e-01f, -9.999881387e-01f));
+    float2 h;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(h.x) : "f"(q.x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(h.y) : "f"(q.y));
+    return __ffma2_rn(make_float2(-fabsf(x.x), -fabsf(x.y)), h, make_float2(fmaxf(x.x, 0.f), fmaxf(x.y, 0.f)));
+}
+
+// y[j] = float(acc[j]) * a_s * w[j] + b[j] for 32 accumulator columns, two columns per instruction
+// (the multiply and the fused multiply-add round exactly as their scalar forms do)
+__device__ __forceinline__ void dequant32(const uint32_t (&r)[32], float a_s, const float* __restrict__ ws,
+                                          const float* __restrict__ bs, float (&y)[32]) {
+    const float2 a2 = make_float2(a_s, a_s);
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const float4 w4 = *reinterpret_cast<const float4*>(ws + j);
+        const float4 b4 = *reinterpret_cast<const float4*>(bs + j);
+        const float2 lo = __ffma2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[j + 0]), __int2float_rn((int)r[j + 1])), a2),
+                                     make_float2(w4.x, w4.y), make_float2(b4.x, b4.y));
+        const float2 hi = __ffma2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[j + 2]), __int2float_rn((int)r[j + 3])), a2),
+                                     make_float2(w4.z, w4.w), make_float2(b4.z, b4.w));
+        y[j + 0] = lo.x; y[j + 1] = lo.y; y[j + 2] = hi.x; y[j + 3] = hi.y;
+    }
+}
+
+__device__ __forceinline__ void gelu32(float (&y)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+        const float2 g = gelu_erf2(make_float2(y[j], y[j + 1]));
+        y[j] = g.x; y[j + 1] = g.y;
+    }
+}
+
 template <typename OutT> struct OutOps;
 template <> struct OutOps<__half> {
     static __device__ __forceinline__ float up(__half v) { return __half2float(v); }
     static __device__ __forceinline__ __half down(float v) { return __float2half_rn(v); }
+    // 32 values -> four 16-byte vectors, two values per conversion
+    static __device__ __forceinline__ void pack32(const float (&y)[32], uint4 (&packed)[4]) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const __half2 h = __floats2half2_rn(y[8 * j + 2 * e], y[8 * j + 2 * e + 1]);
+                w[e] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            packed[j] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
 };
 template <> struct OutOps<__nv_bfloat16> {
     static __device__ __forceinline__ float up(__nv_bfloat16 v) { return __bfloat162float(v); }
     static __device__ __forceinline__ __nv_bfloat16 down(float v) { return __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ void pack32(const float (&y)[32], uint4 (&packed)[4]) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(y[8 * j + 2 * e], y[8 * j + 2 * e + 1]);
+                w[e] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            packed[j] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
 };
 template <> struct OutOps<float> {
     static __device__ __forceinline__ float up(float v) { return v; }
     static __device__ __forceinline__ float down(float v) { return v; }
+    static __device__ __forceinline__ void pack32(const float (&y)[32], uint4 (&packed)[8]) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            packed[j] = make_uint4(__float_as_uint(y[4 * j]), __float_as_uint(y[4 * j + 1]), __float_as_uint(y[4 * j + 2]), __float_as_uint(y[4 * j + 3]));
+    }
 };
 
 // ---- host side -----------------------------------------------------------------

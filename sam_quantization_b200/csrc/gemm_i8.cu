@@ -245,19 +245,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (int j = 0; j < 8; ++j) packed[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
                 } else {
                     float y[32];
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const float4 w4 = *reinterpret_cast<const float4*>(ws + col0 + j);
-                        const float4 b4 = *reinterpret_cast<const float4*>(bs + col0 + j);
-                        y[j + 0] = fmaf(__int2float_rn((int)r[j + 0]) * a_s, w4.x, b4.x);
-                        y[j + 1] = fmaf(__int2float_rn((int)r[j + 1]) * a_s, w4.y, b4.y);
-                        y[j + 2] = fmaf(__int2float_rn((int)r[j + 2]) * a_s, w4.z, b4.z);
-                        y[j + 3] = fmaf(__int2float_rn((int)r[j + 3]) * a_s, w4.w, b4.w);
-                    }
-                    if constexpr (GELU) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) y[j] = gelu_erf(y[j]);
-                    }
+                    dequant32(r, a_s, ws + col0, bs + col0, y);
+                    if constexpr (GELU) gelu32(y);
                     if constexpr (RES) {
                         const OutT* res_base = reinterpret_cast<const OutT*>(p.residual);
                         if (p.tma_store && p.vec_ok && n_valid == 32) {
@@ -315,13 +304,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             }
                         }
                     }
-#pragma unroll
-                    for (int j = 0; j < NVEC; ++j) {
-                        OutT tmp[PER16];
-#pragma unroll
-                        for (int e = 0; e < PER16; ++e) tmp[e] = OutOps<OutT>::down(y[j * PER16 + e]);
-                        packed[j] = *reinterpret_cast<const uint4*>(tmp);
-                    }
+                    OutOps<OutT>::pack32(y, packed);
                 }
                 if (p.tma_store) {
                     // rows of 64 bytes per box: 32 columns of a 2-byte type, 16 columns of a 4-byte type

@@ -84,7 +84,11 @@ def bench_quant(M, K, dtype=torch.float16, ln=False, gather=False, hadamard=None
     if gather:
         kw["row_map"] = torch.randperm(M, device=dev).to(torch.int32)
     if hadamard:
-        kw["hadamard"] = ops.Hadamard(hadamard, had_dim=K // 16 if hadamard == "partial" else 0)
+        from .quarot.hadamard_utils import get_hadK
+        heads = 12 if K % 768 == 0 and hadamard == "partial" else 16
+        hadk, had_k = get_hadK(heads if hadamard == "partial" else K)
+        kw["hadamard"] = ops.Hadamard(hadamard, had_k=had_k, hadk=None if hadk is None else hadk.to(dev),
+                                      had_dim=K // heads if hadamard == "partial" else 0)
     gran = ops.ACT_GRANULARITY[granularity]
 
     def run(i):
