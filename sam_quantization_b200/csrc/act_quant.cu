@@ -594,7 +594,10 @@ __device__ __forceinline__ void mix_columns(float* sm, const float4* hk4, int ld
         const int k0 = half * HK;
         float2 in2[HK];
 #pragma unroll
-        for (int k = 0; k < HK; ++k) in2[k] = make_float2(col[padded((k0 + k) * cols + c)], col[padded((k0 + k) * cols + c + 1)]);
+        for (int k = 0; k < HK; ++k) {                  // c is even: c and c + 1 share a 16-group, so their padded slots are adjacent
+            const int a = padded((k0 + k) * cols + c);
+            in2[k] = make_float2(col[a], col[a + 1]);
+        }
 #pragma unroll 1
         for (int k = 0; k < HK; ++k) {                   // not unrolled: the inputs alone fill the registers
             float2 acc = make_float2(0.f, 0.f);
@@ -605,8 +608,9 @@ __device__ __forceinline__ void mix_columns(float* sm, const float4* hk4, int ld
                 acc = __ffma2_rn(make_float2(h.z, h.w), in2[k2 + 1], acc);
             }
             if (FINISH) acc = finish_pair<T>(acc, root, m);
-            col[padded((k0 + k) * cols + c)] = acc.x;
-            col[padded((k0 + k) * cols + c + 1)] = acc.y;
+            const int a = padded((k0 + k) * cols + c);
+            col[a] = acc.x;
+            col[a + 1] = acc.y;
         }
     }
 }
@@ -736,9 +740,12 @@ hadamard_quant_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx,
             const int a0 = kc * pow_len + ((hi << (b + r)) | lo);
             const int base = a0 * inner + in;
             const int step = inner << b;
+            // padded(base + j * step) is linear in j when the step is a multiple of 16
+            const bool lin = (step & 15) == 0;
+            const int pbase = padded(base), pstep = step + (step >> 4);
             float v[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) if (j < R) v[j] = sm[padded(base + j * step)];
+            for (int j = 0; j < 16; ++j) if (j < R) v[j] = sm[lin ? pbase + j * pstep : padded(base + j * step)];
             if (R == 16) {
                 butterfly16(v);
             } else {
@@ -769,7 +776,7 @@ hadamard_quant_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx,
                 }
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) if (j < R) sm[padded(base + j * step)] = v[j];
+            for (int j = 0; j < 16; ++j) if (j < R) sm[lin ? pbase + j * pstep : padded(base + j * step)] = v[j];
         }
         if (last) finished = true;
         else __syncthreads();                            // the closing barrier below follows the last round

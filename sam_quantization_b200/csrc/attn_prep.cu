@@ -26,11 +26,17 @@ namespace {
 template <typename T> __device__ __forceinline__ float ld(const T* p) { return Elem<T>::up(*p); }
 
 template <typename T>
-__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-    uint4 r;
-    T* h = reinterpret_cast<T*>(&r);
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]);
+template <> __device__ __forceinline__ uint4 pack8<__half>(const float (&f)[8]) {
+    uint4 r; __half2* h = reinterpret_cast<__half2*>(&r);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) h[i] = Elem<T>::down(f[i]);
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    return r;
+}
+template <> __device__ __forceinline__ uint4 pack8<__nv_bfloat16>(const float (&f)[8]) {
+    uint4 r; __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
     return r;
 }
 template <typename T>
@@ -51,38 +57,55 @@ window_prep_kernel(const T* __restrict__ qkv, const T* __restrict__ rel_all, int
     if (token >= tokens) return;
     const int L = H * W, C = nh * d;
     const int l = (int)(token % L), qh = l / W, qw = l - qh * W;
-    const int cpr = width >> 3;                        // 16-byte chunks per head row
-    const int dch = d >> 3;                            // chunks holding q / k themselves
+    const int dch = d >> 3;                            // 16-byte chunks holding q / k themselves, per head
+    const int rch = (width - d) >> 3;                  // chunks holding the bias terms / one-hot codes
     const T* qrow = qkv + token * 3 * C;
     T* qo = q_aug + token * nh * width;
     T* ko = k_aug + token * nh * width;
     const int rows_h = 2 * H - 1;
-    for (int ch = lane; ch < nh * cpr; ch += 32) {
-        const int head = ch / cpr, part = ch - head * cpr;
-        uint4 qv, kv;
-        if (part < dch) {
-            float f[8];
-            unpack8<T>(*reinterpret_cast<const uint4*>(qrow + head * d + part * 8), f);
+
+    // (1) q * scale and k: the token's C values of each are contiguous in qkv; five chunks per lane
+    // are loaded before any is stored so that a warp keeps 5 KB in flight
+    const int nchunks = nh * dch;
+    for (int c0 = 0; c0 < nchunks; c0 += 5 * 32) {
+        uint4 qv[5], kv[5];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] *= scale;
-            qv = pack8<T>(f);
-            kv = *reinterpret_cast<const uint4*>(qrow + C + head * d + part * 8);
-        } else {
-            const T* rel = rel_all + ((int64_t)head * tokens + token) * J;
-            float fq[8], fk[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const int j = (part - dch) * 8 + e;
-                float a = 0.f, b = 0.f;
-                if (j < H) { a = ld(rel + (qh - j + H - 1)); b = (j == qh) ? 1.f : 0.f; }
-                else if (j < H + W) { const int kw = j - H; a = ld(rel + rows_h + (qw - kw + W - 1)); b = (kw == qw) ? 1.f : 0.f; }
-                fq[e] = a; fk[e] = b;
+        for (int i = 0; i < 5; ++i) {
+            const int c = c0 + i * 32 + lane;
+            if (c < nchunks) {
+                qv[i] = *reinterpret_cast<const uint4*>(qrow + c * 8);
+                kv[i] = *reinterpret_cast<const uint4*>(qrow + C + c * 8);
             }
-            qv = pack8<T>(fq);
-            kv = pack8<T>(fk);
         }
-        *reinterpret_cast<uint4*>(qo + (int64_t)ch * 8) = qv;
-        *reinterpret_cast<uint4*>(ko + (int64_t)ch * 8) = kv;
+#pragma unroll
+        for (int i = 0; i < 5; ++i) {
+            const int c = c0 + i * 32 + lane;
+            if (c < nchunks) {
+                const int head = c / dch, part = c - head * dch;
+                float f[8];
+                unpack8<T>(qv[i], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] *= scale;
+                *reinterpret_cast<uint4*>(qo + head * width + part * 8) = pack8<T>(f);
+                *reinterpret_cast<uint4*>(ko + head * width + part * 8) = kv[i];
+            }
+        }
+    }
+    // (2) the bias terms behind q and the one-hot position codes behind k
+    for (int id = lane; id < nh * rch; id += 32) {
+        const int head = id / rch, r = id - head * rch;
+        const T* rel = rel_all + ((int64_t)head * tokens + token) * J;
+        float fq[8], fk[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int j = r * 8 + e;
+            float a = 0.f, b = 0.f;
+            if (j < H) { a = ld(rel + (qh - j + H - 1)); b = (j == qh) ? 1.f : 0.f; }
+            else if (j < H + W) { const int kw = j - H; a = ld(rel + rows_h + (qw - kw + W - 1)); b = (kw == qw) ? 1.f : 0.f; }
+            fq[e] = a; fk[e] = b;
+        }
+        *reinterpret_cast<uint4*>(qo + head * width + d + r * 8) = pack8<T>(fq);
+        *reinterpret_cast<uint4*>(ko + head * width + d + r * 8) = pack8<T>(fk);
     }
 }
 
@@ -106,6 +129,24 @@ rel_bias_kernel(const T* __restrict__ rel_all, int64_t tokens, int J, int H, int
     __syncwarp();
     const int wch = W >> 3;                            // 16-byte chunks per key row
     T* out = bias + ((image * nh + head) * L + l) * (int64_t)L;
+    if (32 % wch == 0) {
+        // a lane keeps the same 8 key columns on every pass: their terms are loaded once, and a
+        // pass is one shared-memory read, four packed adds, the conversions and a 16-byte store
+        const int kw0 = (lane % wch) * 8;
+        float2 tw[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            tw[e] = make_float2(ld(rel + rows_h + (qw - (kw0 + 2 * e) + W - 1)), ld(rel + rows_h + (qw - (kw0 + 2 * e + 1) + W - 1)));
+        for (int kh = lane / wch; kh < H; kh += 32 / wch) {
+            const float a = th_s[warp][kh];
+            const float2 a2 = make_float2(a, a);
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 t = __fadd2_rn(a2, tw[e]); v[2 * e] = t.x; v[2 * e + 1] = t.y; }
+            *reinterpret_cast<uint4*>(out + (int64_t)kh * W + kw0) = pack8<T>(v);
+        }
+        return;
+    }
     for (int c0 = lane; c0 < H * wch; c0 += 32) {
         const int kh = c0 / wch, kw0 = (c0 - kh * wch) * 8;
         const float a = th_s[warp][kh];
