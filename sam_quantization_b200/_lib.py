@@ -31,6 +31,8 @@ EXPORTED_SYMBOLS = (
     "samq_attn_window_prep",
     "samq_attn_rel_bias",
     "samq_attn_windowed",
+    "samq_attn_transpose_v",
+    "samq_attn_global",
 )
 
 
@@ -126,6 +128,14 @@ def load() -> ctypes.CDLL:
     ]
     lib.samq_gemm_set_pair_mode.restype = c_int
     lib.samq_gemm_set_pair_mode.argtypes = [c_int]
+    lib.samq_attn_transpose_v.restype = c_int
+    lib.samq_attn_transpose_v.argtypes = [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p]
+    lib.samq_attn_global.restype = c_int
+    lib.samq_attn_global.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int,     # qkv, vt, rel_all, dtype, images, rel_pitch
+        c_int, c_int, c_int, c_int, c_float,                     # H, W, heads, head_dim, scale
+        c_void_p, c_void_p, c_void_p,                            # out, status, stream
+    ]
     lib.samq_attn_window_prep.restype = c_int
     lib.samq_attn_window_prep.argtypes = [
         c_void_p, c_void_p, c_int, c_int64, c_int,              # qkv, rel_all, dtype, tokens, rel_pitch

@@ -13,7 +13,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libsamq.so")
-SOURCES = ["abi.cu", "act_quant.cu", "gemm_i8.cu", "gemm_i8_pair.cu", "gemm_i8_grouped.cu", "attn_prep.cu", "attn_window.cu"]
+SOURCES = ["abi.cu", "act_quant.cu", "gemm_i8.cu", "gemm_i8_pair.cu", "gemm_i8_grouped.cu", "attn_prep.cu", "attn_window.cu", "attn_global.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-lineinfo", "-std=c++17",

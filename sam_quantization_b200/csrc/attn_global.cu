@@ -1,0 +1,461 @@
+// Global (full-image) attention of SAM's encoder blocks with the decomposed relative position
+// bias, on the 5th-generation tensor cores.  It replaces, for the 64 x 64-token global blocks,
+// the `(q * scale) @ k^T + rel_pos -> softmax -> @ v` of quarot/model_utils.py:158-170 without
+// ever writing the [heads, L, L] score or bias tensors to memory.
+//
+//   bias[(qh,qw),(kh,kw)] = rel_h[q, qh - kh + H - 1] + rel_w[q, qw - kw + W - 1]
+//
+// where rel_h / rel_w are the dot products of the query with the relative-position tables (one
+// small GEMM done by the caller: rel_all[head, token, j]).  The key axis is walked one key ROW
+// at a time (W = 64 keys per block), so inside a block the rel_h term is one scalar per query
+// and the rel_w terms are the same 64 values in every block: they live in registers.
+//
+// One CTA owns 128 queries of one (image, head); two CTAs are resident per SM so that one's
+// softmax overlaps the other's matrix products.  Roles (192 threads):
+//   warps 0-3  softmax: thread r owns query row r (= TMEM lane r).  Per key block: load the 64
+//              scores from tensor memory, t = s * scale * log2e + bias, row maximum, p = 2^(t - m),
+//              row sum, P as bf16/fp16 into shared memory in the 128-byte-swizzled operand layout.
+//              The maximum m is only raised when a row's new maximum exceeds it by more than 8
+//              (p stays below 2^8); the output accumulator in tensor memory is then rescaled in place.
+//   warp 4     TMA producer: Q once, then per block the K rows and the matching V^T columns
+//              (two stages).
+//   warp 5     MMA issuer: S = Q K^T (M128 N64 K=D) into one of two score buffers, and
+//              O += P V (M128 N=D K64), both tcgen05.mma kind::f16 with fp32 accumulation.
+// V is consumed K-major (V^T [D, L] per head), written by attn_transpose_v below.
+// Every wait is bounded; a wait that runs out sets the abort flag, the roles drain, and the
+// status word is set.
+#include "gemm_common.cuh"
+
+namespace samq {
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BQ = 128;                 // queries per CTA
+constexpr int BKEY = 64;                // keys per block = one row of the key grid
+constexpr int AT_THREADS = 192;
+constexpr int TMEM_COLS_AT = 256;       // S0 at 0, S1 at 64, O at 128
+constexpr int O_COL = 128;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnControl {
+    uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, pv_done;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+struct AttnParams {
+    const void* rel_all;     // [heads, tokens, rel_pitch]
+    void* out;               // [tokens, C]
+    int64_t tokens;          // images * L
+    int rel_pitch;
+    int H, L, heads, qtiles;
+    float scale;
+    int32_t* status;
+};
+
+template <typename T> struct AtOps;
+template <> struct AtOps<__nv_bfloat16> {
+    static constexpr uint32_t kFormat = 1;
+    static __device__ __forceinline__ float up(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    static __device__ __forceinline__ uint32_t pack(float a, float b) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+};
+template <> struct AtOps<__half> {
+    static constexpr uint32_t kFormat = 0;
+    static __device__ __forceinline__ float up(const __half* p) { return __half2float(*p); }
+    static __device__ __forceinline__ uint32_t pack(float a, float b) {
+        const __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+};
+
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// kind::f16 instruction descriptor: fp32 accumulator, A and B of format `fmt` (0 fp16, 1 bf16),
+// both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+__host__ __device__ constexpr uint32_t f16_idesc(uint32_t fmt, int M, int N) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+template <int D> struct AtSmem {
+    static constexpr int NATOM = (D + 63) / 64;            // 128-byte swizzle rows per operand row
+    static constexpr int Q_BYTES = NATOM * BQ * 128;
+    static constexpr int K_BYTES = NATOM * BKEY * 128;
+    static constexpr int VT_BYTES = D * 128;               // D rows of 64 keys
+    static constexpr int STAGE_BYTES = K_BYTES + VT_BYTES;
+    static constexpr int P_BYTES = BQ * 128;
+    static constexpr int TOTAL = 1024 + Q_BYTES + 2 * STAGE_BYTES + P_BYTES + (int)sizeof(AttnControl) + 64;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_vt, const AttnParams p)
+{
+    using SM = AtSmem<D>;
+    static_assert(D % 16 == 0 && D <= 128, "head_dim must be a multiple of 16 up to 128");
+    extern __shared__ uint8_t at_smem_raw[];
+    const uint32_t raw_addr = smem_u32(at_smem_raw);
+    const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
+    uint8_t* q_tile = at_smem_raw + pad;                                 // 1024-byte aligned, like every tile below
+    uint8_t* stages = q_tile + SM::Q_BYTES;
+    uint8_t* p_tile = stages + 2 * SM::STAGE_BYTES;
+    AttnControl* ctl = reinterpret_cast<AttnControl*>(p_tile + SM::P_BYTES);
+    volatile uint32_t* abort_flag = &ctl->abort_flag;
+
+    // a CTA of this launch already gave up on a wait: do not start more work
+    if (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qt = blockIdx.x % p.qtiles;
+    const int bh = blockIdx.x / p.qtiles;
+    const int head = bh % p.heads;
+    const int image = bh / p.heads;
+    const int C = p.heads * D;
+    const int64_t token0 = (int64_t)image * p.L + (int64_t)qt * BQ;      // first query row of this CTA in qkv
+    const int nblocks = p.H;                                             // one key row per block
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&ctl->q_full), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&ctl->kv_full[s]), 1); mbar_init(smem_u32(&ctl->kv_empty[s]), 1);
+            mbar_init(smem_u32(&ctl->s_full[s]), 1);  mbar_init(smem_u32(&ctl->s_empty[s]), 4);
+        }
+        mbar_init(smem_u32(&ctl->p_full), 4);
+        mbar_init(smem_u32(&ctl->pv_done), 1);
+        ctl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_vt) : "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&ctl->tmem_base)), "r"((uint32_t)TMEM_COLS_AT) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    if (warp == 4) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            const uint32_t qbar = smem_u32(&ctl->q_full);
+            mbar_expect_tx(qbar, SM::Q_BYTES);
+#pragma unroll
+            for (int a = 0; a < SM::NATOM; ++a)
+                tma_load_2d(smem_u32(q_tile + a * BQ * 128), &map_q, qbar, head * D + a * 64, (int)token0);
+            bool ok = true;
+            for (int i = 0; i < nblocks && ok; ++i) {
+                const int st = i & 1;
+                if (!mbar_wait(smem_u32(&ctl->kv_empty[st]), ((i >> 1) & 1) ^ 1u, abort_flag)) { ok = false; break; }
+                const uint32_t bar = smem_u32(&ctl->kv_full[st]);
+                uint8_t* sb = stages + st * SM::STAGE_BYTES;
+                mbar_expect_tx(bar, SM::STAGE_BYTES);
+#pragma unroll
+                for (int a = 0; a < SM::NATOM; ++a)
+                    tma_load_2d(smem_u32(sb + a * BKEY * 128), &map_k, bar, C + head * D + a * 64, image * p.L + i * BKEY);
+                tma_load_2d(smem_u32(sb + SM::K_BYTES), &map_vt, bar, i * BKEY, bh * D);
+            }
+            if (!ok) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000LL) { }          // let copies in flight land before the CTA retires
+            }
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = f16_idesc(AtOps<T>::kFormat, BQ, BKEY);
+            constexpr uint32_t idesc_o = f16_idesc(AtOps<T>::kFormat, BQ, D);
+            bool ok = mbar_wait(smem_u32(&ctl->q_full), 0, abort_flag);
+            auto issue_s = [&](int j) -> bool {
+                const int st = j & 1;
+                const uint32_t ph = (uint32_t)((j >> 1) & 1);
+                if (!mbar_wait(smem_u32(&ctl->kv_full[st]), ph, abort_flag)) return false;
+                if (!mbar_wait(smem_u32(&ctl->s_empty[st]), ph ^ 1u, abort_flag)) return false;
+                tcgen05_fence_after();
+                const uint32_t kb = smem_u32(stages + st * SM::STAGE_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    // 16 elements = 32 bytes along K: +2 in the descriptor's (address >> 4) field; a new
+                    // 128-byte swizzle row group every 64 elements
+                    const uint64_t adesc = make_smem_desc(smem_u32(q_tile) + (ks >> 2) * BQ * 128) + (uint64_t)((ks & 3) * 2);
+                    const uint64_t bdesc = make_smem_desc(kb + (ks >> 2) * BKEY * 128) + (uint64_t)((ks & 3) * 2);
+                    mma_f16(tmem_base + (uint32_t)(st * BKEY), adesc, bdesc, idesc_s, ks != 0 ? 1u : 0u);
+                }
+                tcgen05_commit(smem_u32(&ctl->s_full[st]));
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int i = 0; i < nblocks && ok; ++i) {
+                if (i + 1 < nblocks && !issue_s(i + 1)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&ctl->p_full), (uint32_t)(i & 1), abort_flag)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t vb = smem_u32(stages + (i & 1) * SM::STAGE_BYTES + SM::K_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < BKEY / 16; ++ks) {
+                    const uint64_t adesc = make_smem_desc(smem_u32(p_tile)) + (uint64_t)(ks * 2);
+                    const uint64_t bdesc = make_smem_desc(vb) + (uint64_t)(ks * 2);
+                    mma_f16(tmem_base + (uint32_t)O_COL, adesc, bdesc, idesc_o, (i | ks) != 0 ? 1u : 0u);
+                }
+                tcgen05_commit(smem_u32(&ctl->kv_empty[i & 1]));      // K / V^T stage may be refilled
+                tcgen05_commit(smem_u32(&ctl->pv_done));              // P may be overwritten, O is current
+            }
+        }
+    } else {
+        // ---------------- softmax + output ----------------
+        const int row = warp * 32 + lane;                          // query row in the tile = TMEM lane
+        const int lq = qt * BQ + row;                              // query index inside the image
+        const int qh = lq >> 6, qw = lq & 63;
+        const T* rel = reinterpret_cast<const T*>(p.rel_all) + ((int64_t)head * p.tokens + token0 + row) * p.rel_pitch;
+        const int rows_h = 2 * p.H - 1;
+        float rwl[BKEY];                                           // rel_w term of key column j, times log2(e)
+#pragma unroll
+        for (int j = 0; j < BKEY; ++j) rwl[j] = AtOps<T>::up(rel + rows_h + (qw - j + BKEY - 1)) * LOG2E;
+        const float c = p.scale * LOG2E;
+        const float2 c2 = make_float2(c, c);
+        float m_used = -INFINITY, l_sum = 0.f;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+        uint8_t* prow = p_tile + row * 128;
+        const uint32_t sw = (uint32_t)(row & 7);
+        bool ok = true;
+        for (int i = 0; i < nblocks; ++i) {
+            const float rh = AtOps<T>::up(rel + (qh - i + p.H - 1)) * LOG2E;
+            if (ok && !mbar_wait(smem_u32(&ctl->s_full[i & 1]), (uint32_t)((i >> 1) & 1), abort_flag)) ok = false;
+            if (!ok) break;
+            tcgen05_fence_after();
+            uint32_t s0[32], s1[32];
+            tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY), s0);
+            tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY + 32), s1);
+            tmem_ld_wait();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[i & 1]));   // the score buffer may be overwritten
+
+            // t = s * scale * log2e + (rel_h + rel_w) * log2e, two columns per instruction
+            float t[BKEY];
+            const float2 rh2 = make_float2(rh, rh);
+            float mi = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+                const float2 b0 = __fadd2_rn(make_float2(rwl[j], rwl[j + 1]), rh2);
+                const float2 b1 = __fadd2_rn(make_float2(rwl[32 + j], rwl[32 + j + 1]), rh2);
+                const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(s0[j]), __uint_as_float(s0[j + 1])), c2, b0);
+                const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(s1[j]), __uint_as_float(s1[j + 1])), c2, b1);
+                t[j] = t0.x; t[j + 1] = t0.y; t[32 + j] = t1.x; t[32 + j + 1] = t1.y;
+                mi = fmaxf(mi, fmaxf(fmaxf(t0.x, t0.y), fmaxf(t1.x, t1.y)));
+            }
+            // raise the running maximum only when some row of the warp needs it
+            const bool raise = __any_sync(0xffffffffu, mi > m_used + 8.0f);
+            float alpha = 1.0f;
+            if (raise) {
+                const float m_new = fmaxf(m_used, mi);
+                alpha = ex2(m_used - m_new);                       // 0 on the first block (m_used = -inf)
+                m_used = m_new;
+                l_sum *= alpha;
+            }
+            const float2 nm2 = make_float2(-m_used, -m_used);
+            uint32_t pk[BKEY / 2];
+            float2 ls2 = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < BKEY; j += 2) {
+                const float2 e = __fadd2_rn(make_float2(t[j], t[j + 1]), nm2);
+                const float2 pv = make_float2(ex2(e.x), ex2(e.y));
+                ls2 = __fadd2_rn(ls2, pv);
+                pk[j >> 1] = AtOps<T>::pack(pv.x, pv.y);
+            }
+            l_sum += ls2.x + ls2.y;
+
+            if (i > 0) {
+                // the previous P V product has left P and has been added into O
+                if (!mbar_wait(smem_u32(&ctl->pv_done), (uint32_t)((i - 1) & 1), abort_flag)) { ok = false; break; }
+                tcgen05_fence_after();
+                if (raise) {                                       // warp-uniform
+#pragma unroll
+                    for (int cc = 0; cc < D / 16; ++cc) {
+                        uint32_t o[16];
+                        tmem_ld16(lane_base + (uint32_t)(O_COL + cc * 16), o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                        tmem_st16(lane_base + (uint32_t)(O_COL + cc * 16), o);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // P row -> shared memory, the layout tcgen05.mma reads with the 128-byte swizzle:
+            // 16-byte chunk index XOR (row mod 8)
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+                *reinterpret_cast<uint4*>(prow + (((uint32_t)ch ^ sw) << 4)) =
+                    make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+            fence_async_smem();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full));
+        }
+        if (ok && mbar_wait(smem_u32(&ctl->pv_done), (uint32_t)((nblocks - 1) & 1), abort_flag)) {
+            tcgen05_fence_after();
+            const float inv_l = 1.0f / l_sum;
+            T* orow = reinterpret_cast<T*>(p.out) + (token0 + row) * (int64_t)C + head * D;
+#pragma unroll
+            for (int cc = 0; cc < D / 16; ++cc) {
+                uint32_t o[16];
+                tmem_ld16(lane_base + (uint32_t)(O_COL + cc * 16), o);
+                tmem_ld_wait();
+                uint32_t w[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    w[e] = AtOps<T>::pack(__uint_as_float(o[2 * e]) * inv_l, __uint_as_float(o[2 * e + 1]) * inv_l);
+                *reinterpret_cast<uint4*>(orow + cc * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(orow + cc * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    if (warp == 5) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS_AT) : "memory");
+    }
+    if (threadIdx.x == 0 && ctl->abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+// V of every (image, head) as [D, L] (keys contiguous): the K-major B operand of O += P V.
+// One CTA transposes 64 tokens x D values through shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256)
+transpose_v_kernel(const T* __restrict__ qkv, int L, int heads, int D, T* __restrict__ vt)
+{
+    __shared__ T tile[128][BKEY + 2];                               // [dv][token], padded against bank conflicts
+    const int l0 = blockIdx.x * BKEY;
+    const int bh = blockIdx.y;
+    const int head = bh % heads, image = bh / heads;
+    const int C = heads * D;
+    const int chunks = D >> 3;                                      // 16-byte chunks per token
+    const T* src = qkv + ((int64_t)image * L + l0) * 3 * C + 2 * C + head * D;
+    for (int idx = threadIdx.x; idx < BKEY * chunks; idx += blockDim.x) {
+        const int tok = idx / chunks, ch = idx - tok * chunks;
+        const uint4 v = *reinterpret_cast<const uint4*>(src + (int64_t)tok * 3 * C + ch * 8);
+        const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) tile[ch * 8 + k][tok] = e[k];
+    }
+    __syncthreads();
+    T* dst = vt + (int64_t)bh * D * L + l0;
+    for (int idx = threadIdx.x; idx < D * (BKEY / 2); idx += blockDim.x) {
+        const int dv = idx / (BKEY / 2), pr = idx - dv * (BKEY / 2);
+        *reinterpret_cast<uint32_t*>(dst + (int64_t)dv * L + pr * 2) = *reinterpret_cast<const uint32_t*>(&tile[dv][pr * 2]);
+    }
+}
+
+// bf16 / fp16 [rows, cols] row-major, box = box_rows x 64 elements (128 bytes), 128-byte swizzle
+int make_map_16bit(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t pitch_elems, int box_rows, bool bf16) {
+    gemm::EncodeTiledFn fn = gemm::encode_tiled_fn();
+    if (fn == nullptr) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(pitch_elems * 2)};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base),
+                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return SAMQ_OK;
+}
+
+template <typename T, int D>
+int launch_attn_global(const void* qkv, const void* vt, const AttnParams& p, int64_t images, cudaStream_t st) {
+    const bool bf16 = std::is_same<T, __nv_bfloat16>::value;
+    const int C = p.heads * D;
+    CUtensorMap mq, mk, mv;
+    int rc = make_map_16bit(&mq, qkv, p.tokens, 3 * C, 3 * C, BQ, bf16);
+    if (rc != SAMQ_OK) return rc;
+    rc = make_map_16bit(&mk, qkv, p.tokens, 3 * C, 3 * C, BKEY, bf16);
+    if (rc != SAMQ_OK) return rc;
+    rc = make_map_16bit(&mv, vt, images * p.heads * D, p.L, p.L, D, bf16);
+    if (rc != SAMQ_OK) return rc;
+    auto kernel = attn_global_kernel<T, D>;
+    SAMQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AtSmem<D>::TOTAL));
+    const unsigned grid = (unsigned)(images * p.heads * p.qtiles);
+    kernel<<<grid, AT_THREADS, AtSmem<D>::TOTAL, st>>>(mq, mk, mv, p);
+    SAMQ_CUDA_TRY(cudaGetLastError());
+    return SAMQ_OK;
+}
+
+}  // namespace
+
+int attn_transpose_v_dispatch(const void* qkv, int dtype, int64_t images, int L, int heads, int head_dim, void* vt, void* stream)
+{
+    if (qkv == nullptr || vt == nullptr) return fail(SAMQ_ERR_BAD_ARG, "null pointer");
+    if (images < 0 || L <= 0 || heads <= 0 || head_dim <= 0 || head_dim > 128 || (head_dim & 7) || (L % BKEY) != 0)
+        return fail(SAMQ_ERR_BAD_ARG, "bad shape images=%lld L=%d heads=%d head_dim=%d", (long long)images, L, heads, head_dim);
+    if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(vt) & 3))
+        return fail(SAMQ_ERR_ALIGNMENT, "qkv must be 16-byte aligned");
+    if (dtype != SAMQ_F16 && dtype != SAMQ_BF16) return fail(SAMQ_ERR_UNSUPPORTED, "attention helpers take fp16 or bf16");
+    if (images == 0) return SAMQ_OK;
+    dim3 grid((unsigned)(L / BKEY), (unsigned)(images * heads));
+    // both types are 16-bit: the transpose only moves bits
+    transpose_v_kernel<__half><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(qkv), L, heads, head_dim, static_cast<__half*>(vt));
+    SAMQ_CUDA_TRY(cudaGetLastError());
+    return SAMQ_OK;
+}
+
+int attn_global_dispatch(const void* qkv, const void* vt, const void* rel_all, int dtype, int64_t images, int rel_pitch,
+                         int H, int W, int heads, int head_dim, float scale, void* out, int32_t* status, void* stream)
+{
+    if (qkv == nullptr || vt == nullptr || rel_all == nullptr || out == nullptr) return fail(SAMQ_ERR_BAD_ARG, "null pointer");
+    if (W != BKEY) return fail(SAMQ_ERR_UNSUPPORTED, "the global attention kernel walks key rows of %d tokens (W=%d)", BKEY, W);
+    if (images < 0 || H <= 0 || heads <= 0 || (H * W) % BQ != 0 || rel_pitch < 2 * H - 1 + 2 * W - 1)
+        return fail(SAMQ_ERR_BAD_ARG, "bad shape images=%lld H=%d W=%d heads=%d rel_pitch=%d", (long long)images, H, W, heads, rel_pitch);
+    if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(vt) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+        return fail(SAMQ_ERR_ALIGNMENT, "qkv, vt and out must be 16-byte aligned");
+    if (dtype != SAMQ_F16 && dtype != SAMQ_BF16) return fail(SAMQ_ERR_UNSUPPORTED, "attention takes fp16 or bf16");
+    if (images == 0) return SAMQ_OK;
+    AttnParams p;
+    p.rel_all = rel_all; p.out = out; p.tokens = images * (int64_t)H * W; p.rel_pitch = rel_pitch;
+    p.H = H; p.L = H * W; p.heads = heads; p.qtiles = (H * W) / BQ; p.scale = scale; p.status = status;
+    if (p.tokens > 2147483647LL) return fail(SAMQ_ERR_TOO_LARGE, "too many tokens");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool bf = dtype == SAMQ_BF16;
+    switch (head_dim) {
+    case 64: return bf ? launch_attn_global<__nv_bfloat16, 64>(qkv, vt, p, images, st) : launch_attn_global<__half, 64>(qkv, vt, p, images, st);
+    case 80: return bf ? launch_attn_global<__nv_bfloat16, 80>(qkv, vt, p, images, st) : launch_attn_global<__half, 80>(qkv, vt, p, images, st);
+    default: return fail(SAMQ_ERR_UNSUPPORTED, "global attention kernel is built for head_dim 64 and 80 (got %d)", head_dim);
+    }
+}
+
+}  // namespace samq

@@ -264,7 +264,8 @@ def test_attention_prep_kernels_against_torch_path(cuda_device, dtype, H, W, dim
     assert a.shape == b.shape == (B * H * W, dim)
     tol = 3e-2 if dtype == torch.bfloat16 else 4e-3
     assert rel_err(a.float(), b.float()) < tol
-    assert cosine(a, b) > 0.9999
+    # over 4096 keys the torch route rounds rel_h + rel_w to 16 bits before the softmax, the kernels do not
+    assert cosine(a, b) > (0.9998 if H * W >= 4096 else 0.9999)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -287,3 +288,48 @@ def test_windowed_attention_kernel_variants_agree(cuda_device, dtype, H, W, dim,
     tol = 3e-2 if dtype == torch.bfloat16 else 4e-3
     assert rel_err(outs[0], outs[2]) < tol and rel_err(outs[1], outs[2]) < tol
     assert cosine(outs[0], outs[2]) > 0.9999
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("H,dim,nh,B", [(64, 160, 2, 2), (64, 128, 2, 1), (2, 80, 1, 3), (6, 64, 1, 2)])
+def test_global_attention_kernel_against_fp32_reference(cuda_device, dtype, H, dim, nh, B):
+    """The tensor-core global attention (scores and bias on chip, online softmax) against the
+    same attention in fp32 torch ops, and against the route through the explicit bias tensor."""
+    from sam_quantization_b200 import ops
+    from sam_quantization_b200.sam_encoder import Attention
+    W = 64
+    torch.manual_seed(H + dim)
+    attn = Attention(dim, nh, use_rel_pos=True, input_size=(H, W)).to(cuda_device, dtype)
+    d = dim // nh
+    with torch.no_grad():
+        attn.rel_pos_h.normal_(0, 0.3)
+        attn.rel_pos_w.normal_(0, 0.3)
+        qkv = torch.randn(B * H * W, 3 * dim, device=cuda_device, dtype=dtype)
+        qkv[:, :dim] *= 2.0                                        # sharper rows: the running maximum must move
+        attn.fused_global_kernel = True
+        a = attn.attend_flat(qkv, B, H, W)
+        torch.cuda.synchronize()
+        ops.check_status()
+        attn.fused_global_kernel = False
+        b = attn.attend_flat(qkv, B, H, W)
+        # fp32 reference from the 16-bit inputs
+        q, k, v = qkv.float().view(B, H * W, 3, nh, d).permute(2, 0, 3, 1, 4)
+        s = (q * attn.scale) @ k.transpose(-1, -2)
+        rq = q.view(B, nh, H, W, d)
+        Rh = attn.rel_pos_h.float()[(torch.arange(H)[:, None] - torch.arange(H)[None, :] + H - 1).to(cuda_device)]
+        Rw = attn.rel_pos_w.float()[(torch.arange(W)[:, None] - torch.arange(W)[None, :] + W - 1).to(cuda_device)]
+        rel_h = torch.einsum("bnhwc,hkc->bnhwk", rq, Rh)
+        rel_w = torch.einsum("bnhwc,wkc->bnhwk", rq, Rw)
+        s = (s.view(B, nh, H, W, H, W) + rel_h[..., :, None] + rel_w[..., None, :]).view(B, nh, H * W, H * W)
+        ref = (s.softmax(-1) @ v).permute(0, 2, 1, 3).reshape(B * H * W, dim)
+    assert a.shape == (B * H * W, dim) and a.dtype == dtype
+    # the bias terms themselves are 16-bit products (|rel| ~ 5 -> 1e-2 absolute in the logits)
+    tol = 3e-2 if dtype == torch.bfloat16 else 4e-3
+    assert rel_err(a.float(), ref) < tol
+    # the explicit-bias route also rounds rel_h + rel_w to 16 bits in memory: looser on these sharp rows
+    tol_b = 8e-2 if dtype == torch.bfloat16 else 1e-2
+    assert rel_err(b.float(), ref) < tol_b
+    assert rel_err(a.float(), b.float()) < tol_b
+    assert cosine(a, ref) > 0.9999
+    # keeping the bias in fp32 on chip must not be less accurate than rounding it to 16 bits in memory
+    assert 1.0 - cosine(a, ref) <= 1.25 * (1.0 - cosine(b, ref)) + 1e-6
