@@ -271,22 +271,25 @@ int samq_attn_window_prep(const void* qkv, const void* rel_all, int dtype, int64
 int samq_attn_rel_bias(const void* rel_all, int dtype, int64_t images, int rel_pitch, int H, int W, int num_heads,
                        void* bias, void* stream);
 
-/* ---- global attention on the tensor cores ---------------------------------
+/* ---- attention on the tensor cores ----------------------------------------
  *
- * Replaces, for blocks that attend over the whole H x W token grid (W = 64), the
- * attention of quarot/model_utils.py:158-170 (`(q * scale) @ k^T`, `add_decomposed_rel_pos`,
- * softmax, `@ v`): scores, bias and probabilities never leave the SM (tcgen05.mma kind::f16,
+ * Replaces the attention of quarot/model_utils.py:158-170 (`(q * scale) @ k^T`,
+ * `add_decomposed_rel_pos`, softmax, `@ v`) for one "unit" of H x W tokens at a time:
+ * a whole image (global blocks: W = 64, H * 64 a multiple of 128) or a window
+ * (H, W <= 16).  Scores, bias and probabilities never leave the SM (tcgen05.mma kind::f16,
  * scores and the output accumulator in tensor memory, online softmax in fp32).
  *
- * samq_attn_transpose_v : vt[(image * heads + head) * head_dim + c, l] = v[image, l, head, c]
- *                         from qkv [images * L, 3C]; vt is [images * heads * head_dim, L].
- * samq_attn_global      : out [images * L, C] (same 16-bit dtype) from qkv, vt and
- *                         rel_all [heads, images * L, rel_pitch] (see samq_attn_window_prep).
- *                         head_dim 64 or 80; L = H * 64 a multiple of 128.
+ * samq_attn_transpose_v : V of every (unit, head) as [head_dim, keys], keys contiguous, from
+ *                         qkv [units * H * W, 3C].  keys = H * W for images; for windows the key
+ *                         (kh, kw) sits at kh * 16 + kw and the row is zero-padded to a multiple
+ *                         of 64.  vt is [units * heads * head_dim, keys].
+ * samq_attn_global      : out [units * H * W, C] (same 16-bit dtype) from qkv, vt and
+ *                         rel_all [heads, units * H * W, rel_pitch] (see samq_attn_window_prep).
+ *                         head_dim 64 or 80.
  * status : optional device int32, set non-zero if a bounded wait inside the kernel ran out. */
-int samq_attn_transpose_v(const void* qkv, int dtype, int64_t images, int tokens_per_image, int num_heads, int head_dim,
+int samq_attn_transpose_v(const void* qkv, int dtype, int64_t units, int H, int W, int num_heads, int head_dim,
                           void* vt, void* stream);
-int samq_attn_global(const void* qkv, const void* vt, const void* rel_all, int dtype, int64_t images, int rel_pitch,
+int samq_attn_global(const void* qkv, const void* vt, const void* rel_all, int dtype, int64_t units, int rel_pitch,
                      int H, int W, int num_heads, int head_dim, float scale, void* out, int32_t* status, void* stream);
 
 /* Whole windowed attention in one kernel: for every window (H*W tokens, H*W <= 208) and head,

@@ -129,7 +129,7 @@ def load() -> ctypes.CDLL:
     lib.samq_gemm_set_pair_mode.restype = c_int
     lib.samq_gemm_set_pair_mode.argtypes = [c_int]
     lib.samq_attn_transpose_v.restype = c_int
-    lib.samq_attn_transpose_v.argtypes = [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p]
+    lib.samq_attn_transpose_v.argtypes = [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     lib.samq_attn_global.restype = c_int
     lib.samq_attn_global.argtypes = [
         c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int,     # qkv, vt, rel_all, dtype, images, rel_pitch

@@ -51,7 +51,7 @@ int attn_window_prep_dispatch(const void* qkv, const void* rel_all, int dtype, i
 
 int attn_rel_bias_dispatch(const void* rel_all, int dtype, int64_t images, int J, int H, int W, int nh, void* bias, void* stream);
 
-int attn_transpose_v_dispatch(const void* qkv, int dtype, int64_t images, int L, int heads, int head_dim, void* vt, void* stream);
+int attn_transpose_v_dispatch(const void* qkv, int dtype, int64_t units, int H, int W, int heads, int head_dim, void* vt, void* stream);
 
 int attn_global_dispatch(const void* qkv, const void* vt, const void* rel_all, int dtype, int64_t images, int rel_pitch,
                          int H, int W, int heads, int head_dim, float scale, void* out, int32_t* status, void* stream);
@@ -131,10 +131,10 @@ int samq_attn_rel_bias(const void* rel_all, int dtype, int64_t images, int rel_p
     return samq::attn_rel_bias_dispatch(rel_all, dtype, images, rel_pitch, H, W, num_heads, bias, stream);
 }
 
-int samq_attn_transpose_v(const void* qkv, int dtype, int64_t images, int tokens_per_image, int num_heads, int head_dim,
+int samq_attn_transpose_v(const void* qkv, int dtype, int64_t units, int H, int W, int num_heads, int head_dim,
                           void* vt, void* stream)
 {
-    return samq::attn_transpose_v_dispatch(qkv, dtype, images, tokens_per_image, num_heads, head_dim, vt, stream);
+    return samq::attn_transpose_v_dispatch(qkv, dtype, units, H, W, num_heads, head_dim, vt, stream);
 }
 
 int samq_attn_global(const void* qkv, const void* vt, const void* rel_all, int dtype, int64_t images, int rel_pitch,

@@ -11,15 +11,16 @@
 // and the rel_w terms are the same 64 values in every block: they live in registers.
 //
 // One CTA owns 128 queries of one (image, head); two CTAs are resident per SM so that one's
-// softmax overlaps the other's matrix products.  Roles (192 threads):
-//   warps 0-3  softmax: thread r owns query row r (= TMEM lane r).  Per key block: load the 64
-//              scores from tensor memory, t = s * scale * log2e + bias, row maximum, p = 2^(t - m),
+// softmax overlaps the other's matrix products.  Roles (320 threads):
+//   warps 0-7  softmax: warps w and w + 4 share the 32 query rows of TMEM lane quadrant w, a thread
+//              owns one row and half of its 64 key columns.  Per key block: load the scores
+//              from tensor memory, t = s * scale * log2e + bias, row maximum, p = 2^(t - m),
 //              row sum, P as bf16/fp16 into shared memory in the 128-byte-swizzled operand layout.
 //              The maximum m is only raised when a row's new maximum exceeds it by more than 8
 //              (p stays below 2^8); the output accumulator in tensor memory is then rescaled in place.
-//   warp 4     TMA producer: Q once, then per block the K rows and the matching V^T columns
+//   warp 8     TMA producer: Q once, then per block the K rows and the matching V^T columns
 //              (two stages).
-//   warp 5     MMA issuer: S = Q K^T (M128 N64 K=D) into one of two score buffers, and
+//   warp 9     MMA issuer: S = Q K^T (M128 N64 K=D) into one of two score buffers, and
 //              O += P V (M128 N=D K64), both tcgen05.mma kind::f16 with fp32 accumulation.
 // V is consumed K-major (V^T [D, L] per head), written by attn_transpose_v below.
 // Every wait is bounded; a wait that runs out sets the abort flag, the roles drain, and the
@@ -34,23 +35,25 @@ namespace {
 
 constexpr int BQ = 128;                 // queries per CTA
 constexpr int BKEY = 64;                // keys per block = one row of the key grid
-constexpr int AT_THREADS = 192;
+constexpr int AT_THREADS = 320;        // 8 softmax warps, the TMA warp, the MMA warp
 constexpr int TMEM_COLS_AT = 256;       // S0 at 0, S1 at 64, O at 128
 constexpr int O_COL = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnControl {
-    uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, pv_done;
+    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_done;
     uint32_t tmem_base;
     uint32_t abort_flag;
+    float xchg[2][2 * BQ];   // per-row partial maxima / sums swapped between the two halves of a row
 };
 
 struct AttnParams {
     const void* rel_all;     // [heads, tokens, rel_pitch]
     void* out;               // [tokens, C]
-    int64_t tokens;          // images * L
+    int64_t tokens;          // units * L
     int rel_pitch;
-    int H, L, heads, qtiles;
+    int H, W, L, heads, qtiles;   // token grid of one attention unit (image or window), L = H * W
+    int nblocks;             // 64-key blocks per unit
     float scale;
     int32_t* status;
 };
@@ -78,6 +81,11 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_
                  "setp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -115,7 +123,12 @@ template <int D> struct AtSmem {
     static constexpr int TOTAL = 1024 + Q_BYTES + 2 * STAGE_BYTES + P_BYTES + (int)sizeof(AttnControl) + 64;
 };
 
-template <typename T, int D>
+// WINDOW = false: one unit is an image of H x 64 tokens, a key block is one key row.
+// WINDOW = true : one unit is a window of H x W tokens (H, W <= 16); keys are addressed as
+//                 [H, 16] with the columns W..15 of every row (and rows >= H) absent: TMA fills
+//                 them with zeros through a 4-D view of qkv, their bias is -inf, and a key block
+//                 is four key rows.
+template <typename T, int D, bool WINDOW>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_vt, const AttnParams p)
@@ -138,18 +151,19 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int qt = blockIdx.x % p.qtiles;
     const int bh = blockIdx.x / p.qtiles;
     const int head = bh % p.heads;
-    const int image = bh / p.heads;
+    const int image = bh / p.heads;                                      // the attention unit: image or window
     const int C = p.heads * D;
     const int64_t token0 = (int64_t)image * p.L + (int64_t)qt * BQ;      // first query row of this CTA in qkv
-    const int nblocks = p.H;                                             // one key row per block
+    const int nblocks = p.nblocks;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&ctl->q_full), 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(smem_u32(&ctl->kv_full[s]), 1); mbar_init(smem_u32(&ctl->kv_empty[s]), 1);
-            mbar_init(smem_u32(&ctl->s_full[s]), 1);  mbar_init(smem_u32(&ctl->s_empty[s]), 4);
+            mbar_init(smem_u32(&ctl->k_full[s]), 1); mbar_init(smem_u32(&ctl->k_empty[s]), 1);
+            mbar_init(smem_u32(&ctl->v_full[s]), 1); mbar_init(smem_u32(&ctl->v_empty[s]), 1);
+            mbar_init(smem_u32(&ctl->s_full[s]), 1);  mbar_init(smem_u32(&ctl->s_empty[s]), 8);
         }
-        mbar_init(smem_u32(&ctl->p_full), 4);
+        mbar_init(smem_u32(&ctl->p_full), 8);
         mbar_init(smem_u32(&ctl->pv_done), 1);
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -157,7 +171,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_vt) : "memory");
     }
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(&ctl->tmem_base)), "r"((uint32_t)TMEM_COLS_AT) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -167,7 +181,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     tcgen05_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             const uint32_t qbar = smem_u32(&ctl->q_full);
@@ -175,24 +189,41 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
             for (int a = 0; a < SM::NATOM; ++a)
                 tma_load_2d(smem_u32(q_tile + a * BQ * 128), &map_q, qbar, head * D + a * 64, (int)token0);
+            // K rows are released as soon as their score product has run, V^T columns only after the
+            // P V product two blocks later: K is fetched first and runs further ahead
             bool ok = true;
-            for (int i = 0; i < nblocks && ok; ++i) {
+            auto load_k = [&](int i) -> bool {
                 const int st = i & 1;
-                if (!mbar_wait(smem_u32(&ctl->kv_empty[st]), ((i >> 1) & 1) ^ 1u, abort_flag)) { ok = false; break; }
-                const uint32_t bar = smem_u32(&ctl->kv_full[st]);
+                if (!mbar_wait(smem_u32(&ctl->k_empty[st]), ((i >> 1) & 1) ^ 1u, abort_flag)) return false;
+                const uint32_t bar = smem_u32(&ctl->k_full[st]);
                 uint8_t* sb = stages + st * SM::STAGE_BYTES;
-                mbar_expect_tx(bar, SM::STAGE_BYTES);
+                mbar_expect_tx(bar, SM::K_BYTES);
 #pragma unroll
-                for (int a = 0; a < SM::NATOM; ++a)
-                    tma_load_2d(smem_u32(sb + a * BKEY * 128), &map_k, bar, C + head * D + a * 64, image * p.L + i * BKEY);
-                tma_load_2d(smem_u32(sb + SM::K_BYTES), &map_vt, bar, i * BKEY, bh * D);
+                for (int a = 0; a < SM::NATOM; ++a) {
+                    if (WINDOW) tma_load_4d(smem_u32(sb + a * BKEY * 128), &map_k, bar, C + head * D + a * 64, 0, 4 * i, image);
+                    else tma_load_2d(smem_u32(sb + a * BKEY * 128), &map_k, bar, C + head * D + a * 64, image * p.L + i * BKEY);
+                }
+                return true;
+            };
+            auto load_v = [&](int i) -> bool {
+                const int st = i & 1;
+                if (!mbar_wait(smem_u32(&ctl->v_empty[st]), ((i >> 1) & 1) ^ 1u, abort_flag)) return false;
+                const uint32_t bar = smem_u32(&ctl->v_full[st]);
+                mbar_expect_tx(bar, SM::VT_BYTES);
+                tma_load_2d(smem_u32(stages + st * SM::STAGE_BYTES + SM::K_BYTES), &map_vt, bar, i * BKEY, bh * D);
+                return true;
+            };
+            for (int i = 0; i < nblocks && ok; ++i) {
+                ok = load_k(i);
+                if (ok && i >= 1) ok = load_v(i - 1);
             }
+            if (ok) ok = load_v(nblocks - 1);
             if (!ok) {
                 const long long t0 = clock64();
                 while (clock64() - t0 < 2000000LL) { }          // let copies in flight land before the CTA retires
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc_s = f16_idesc(AtOps<T>::kFormat, BQ, BKEY);
@@ -201,7 +232,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             auto issue_s = [&](int j) -> bool {
                 const int st = j & 1;
                 const uint32_t ph = (uint32_t)((j >> 1) & 1);
-                if (!mbar_wait(smem_u32(&ctl->kv_full[st]), ph, abort_flag)) return false;
+                if (!mbar_wait(smem_u32(&ctl->k_full[st]), ph, abort_flag)) return false;
                 if (!mbar_wait(smem_u32(&ctl->s_empty[st]), ph ^ 1u, abort_flag)) return false;
                 tcgen05_fence_after();
                 const uint32_t kb = smem_u32(stages + st * SM::STAGE_BYTES);
@@ -213,12 +244,14 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     const uint64_t bdesc = make_smem_desc(kb + (ks >> 2) * BKEY * 128) + (uint64_t)((ks & 3) * 2);
                     mma_f16(tmem_base + (uint32_t)(st * BKEY), adesc, bdesc, idesc_s, ks != 0 ? 1u : 0u);
                 }
+                tcgen05_commit(smem_u32(&ctl->k_empty[st]));          // the K rows may be refilled
                 tcgen05_commit(smem_u32(&ctl->s_full[st]));
                 return true;
             };
             if (ok) ok = issue_s(0);
             for (int i = 0; i < nblocks && ok; ++i) {
                 if (i + 1 < nblocks && !issue_s(i + 1)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&ctl->v_full[i & 1]), (uint32_t)((i >> 1) & 1), abort_flag)) { ok = false; break; }
                 if (!mbar_wait(smem_u32(&ctl->p_full), (uint32_t)(i & 1), abort_flag)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t vb = smem_u32(stages + (i & 1) * SM::STAGE_BYTES + SM::K_BYTES);
@@ -228,54 +261,86 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     const uint64_t bdesc = make_smem_desc(vb) + (uint64_t)(ks * 2);
                     mma_f16(tmem_base + (uint32_t)O_COL, adesc, bdesc, idesc_o, (i | ks) != 0 ? 1u : 0u);
                 }
-                tcgen05_commit(smem_u32(&ctl->kv_empty[i & 1]));      // K / V^T stage may be refilled
+                tcgen05_commit(smem_u32(&ctl->v_empty[i & 1]));       // the V^T columns may be refilled
                 tcgen05_commit(smem_u32(&ctl->pv_done));              // P may be overwritten, O is current
             }
         }
     } else {
         // ---------------- softmax + output ----------------
-        const int row = warp * 32 + lane;                          // query row in the tile = TMEM lane
-        const int lq = qt * BQ + row;                              // query index inside the image
-        const int qh = lq >> 6, qw = lq & 63;
-        const T* rel = reinterpret_cast<const T*>(p.rel_all) + ((int64_t)head * p.tokens + token0 + row) * p.rel_pitch;
+        // Warps w and w + 4 share the 32 query rows of TMEM lane quadrant w: each thread owns one
+        // row and HALF of its 64 key columns.  The two halves of a row exchange their partial
+        // maxima through shared memory once per block (and their partial sums once at the end).
+        const int quad = warp & 3, half = warp >> 2;
+        const int row = quad * 32 + lane;                          // query row in the tile = TMEM lane
+        const int lq = qt * BQ + row;                              // query index inside the unit
+        const bool valid_q = lq < p.L;                             // the last tile of a window runs past its 196 tokens
+        const int lqc = valid_q ? lq : p.L - 1;
+        const int qh = lqc / p.W, qw = lqc - qh * p.W;
+        const T* rel = reinterpret_cast<const T*>(p.rel_all) +
+                       ((int64_t)head * p.tokens + (int64_t)image * p.L + lqc) * p.rel_pitch;
         const int rows_h = 2 * p.H - 1;
-        float rwl[BKEY];                                           // rel_w term of key column j, times log2(e)
+        constexpr int HC = BKEY / 2;                               // key columns per thread
+        const int col0 = half * HC;
+        // rel_w term of this thread's key columns, times log2(e); -inf for absent columns
+        constexpr int NRW = WINDOW ? 16 : HC;
+        float rwl[NRW];
 #pragma unroll
-        for (int j = 0; j < BKEY; ++j) rwl[j] = AtOps<T>::up(rel + rows_h + (qw - j + BKEY - 1)) * LOG2E;
+        for (int j = 0; j < NRW; ++j) {
+            const int kw = WINDOW ? j : col0 + j;
+            rwl[j] = kw < p.W ? AtOps<T>::up(rel + rows_h + (qw - kw + p.W - 1)) * LOG2E : -INFINITY;
+        }
         const float c = p.scale * LOG2E;
         const float2 c2 = make_float2(c, c);
         float m_used = -INFINITY, l_sum = 0.f;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
         uint8_t* prow = p_tile + row * 128;
         const uint32_t sw = (uint32_t)(row & 7);
+        const int pair_bar = 1 + quad;                             // named barrier of the two warps of a quadrant
         bool ok = true;
         for (int i = 0; i < nblocks; ++i) {
-            const float rh = AtOps<T>::up(rel + (qh - i + p.H - 1)) * LOG2E;
-            if (ok && !mbar_wait(smem_u32(&ctl->s_full[i & 1]), (uint32_t)((i >> 1) & 1), abort_flag)) ok = false;
-            if (!ok) break;
-            tcgen05_fence_after();
-            uint32_t s0[32], s1[32];
-            tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY), s0);
-            tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY + 32), s1);
-            tmem_ld_wait();
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[i & 1]));   // the score buffer may be overwritten
-
-            // t = s * scale * log2e + (rel_h + rel_w) * log2e, two columns per instruction
-            float t[BKEY];
-            const float2 rh2 = make_float2(rh, rh);
-            float mi = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-                const float2 b0 = __fadd2_rn(make_float2(rwl[j], rwl[j + 1]), rh2);
-                const float2 b1 = __fadd2_rn(make_float2(rwl[32 + j], rwl[32 + j + 1]), rh2);
-                const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(s0[j]), __uint_as_float(s0[j + 1])), c2, b0);
-                const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(s1[j]), __uint_as_float(s1[j + 1])), c2, b1);
-                t[j] = t0.x; t[j + 1] = t0.y; t[32 + j] = t1.x; t[32 + j + 1] = t1.y;
-                mi = fmaxf(mi, fmaxf(fmaxf(t0.x, t0.y), fmaxf(t1.x, t1.y)));
+            // rel_h term of the key row(s) this thread sees in block i: one row for images, two of
+            // the block's four rows for windows (-inf for rows beyond the window)
+            float rh, rh_b = 0.f;
+            if (WINDOW) {
+                const int kh = 4 * i + 2 * half;
+                rh = kh < p.H ? AtOps<T>::up(rel + (qh - kh + p.H - 1)) * LOG2E : -INFINITY;
+                rh_b = kh + 1 < p.H ? AtOps<T>::up(rel + (qh - kh - 1 + p.H - 1)) * LOG2E : -INFINITY;
+            } else {
+                rh = AtOps<T>::up(rel + (qh - i + p.H - 1)) * LOG2E;
             }
-            // raise the running maximum only when some row of the warp needs it
+            if (ok && !mbar_wait(smem_u32(&ctl->s_full[i & 1]), (uint32_t)((i >> 1) & 1), abort_flag)) ok = false;
+            float t[HC];
+            float mi = -INFINITY;
+            if (ok) {                                              // warp-uniform
+                tcgen05_fence_after();
+                uint32_t sc[HC];
+                tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY + col0), sc);
+                tmem_ld_wait();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[i & 1]));   // the score buffer may be overwritten
+
+                // t = s * scale * log2e + (rel_h + rel_w) * log2e, two columns per instruction
+                const float2 rh2 = make_float2(rh, rh), rh2_b = make_float2(rh_b, rh_b);
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // independent chains
+#pragma unroll
+                for (int j = 0; j < HC; j += 2) {
+                    const float2 b0 = WINDOW ? __fadd2_rn(make_float2(rwl[j & 15], rwl[(j & 15) + 1]), j < 16 ? rh2 : rh2_b)
+                                             : __fadd2_rn(make_float2(rwl[j % NRW], rwl[(j + 1) % NRW]), rh2);
+                    const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(sc[j]), __uint_as_float(sc[j + 1])), c2, b0);
+                    t[j] = t0.x; t[j + 1] = t0.y;
+                    mx[(j >> 1) & 3] = fmaxf(mx[(j >> 1) & 3], fmaxf(t0.x, t0.y));
+                }
+                mi = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            }
+            // the other half's maximum (buffers alternate per block so a write never overtakes a read).
+            // A warp that gave up on a wait still visits this barrier every block: its partner is never left waiting.
+            float* xb = ctl->xchg[i & 1];
+            xb[half * BQ + row] = mi;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            if (!ok) continue;
+            mi = fmaxf(mi, xb[(half ^ 1) * BQ + row]);
+            // raise the running maximum only when some row of the warp needs it (both halves agree)
             const bool raise = __any_sync(0xffffffffu, mi > m_used + 8.0f);
             float alpha = 1.0f;
             if (raise) {
@@ -285,24 +350,28 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 l_sum *= alpha;
             }
             const float2 nm2 = make_float2(-m_used, -m_used);
-            uint32_t pk[BKEY / 2];
-            float2 ls2 = make_float2(0.f, 0.f);
+            uint32_t pk[HC / 2];
+            float2 ls2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int j = 0; j < BKEY; j += 2) {
+            for (int j = 0; j < HC; j += 2) {
                 const float2 e = __fadd2_rn(make_float2(t[j], t[j + 1]), nm2);
                 const float2 pv = make_float2(ex2(e.x), ex2(e.y));
-                ls2 = __fadd2_rn(ls2, pv);
+                ls2[(j >> 1) & 3] = __fadd2_rn(ls2[(j >> 1) & 3], pv);
                 pk[j >> 1] = AtOps<T>::pack(pv.x, pv.y);
             }
-            l_sum += ls2.x + ls2.y;
+            {
+                const float2 a = __fadd2_rn(__fadd2_rn(ls2[0], ls2[1]), __fadd2_rn(ls2[2], ls2[3]));
+                l_sum += a.x + a.y;
+            }
 
             if (i > 0) {
                 // the previous P V product has left P and has been added into O
-                if (!mbar_wait(smem_u32(&ctl->pv_done), (uint32_t)((i - 1) & 1), abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&ctl->pv_done), (uint32_t)((i - 1) & 1), abort_flag)) { ok = false; continue; }
                 tcgen05_fence_after();
-                if (raise) {                                       // warp-uniform
+                if (raise) {                                       // warp-uniform; the halves take alternate 16-column chunks
 #pragma unroll
                     for (int cc = 0; cc < D / 16; ++cc) {
+                        if ((cc & 1) != half) continue;
                         uint32_t o[16];
                         tmem_ld16(lane_base + (uint32_t)(O_COL + cc * 16), o);
                         tmem_ld_wait();
@@ -316,13 +385,20 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             // P row -> shared memory, the layout tcgen05.mma reads with the 128-byte swizzle:
             // 16-byte chunk index XOR (row mod 8)
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-                *reinterpret_cast<uint4*>(prow + (((uint32_t)ch ^ sw) << 4)) =
+            for (int ch = 0; ch < 4; ++ch)
+                *reinterpret_cast<uint4*>(prow + (((uint32_t)(half * 4 + ch) ^ sw) << 4)) =
                     make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
             fence_async_smem();
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full));
+        }
+        {
+            // whole-row sum: the two halves swap their partial sums
+            float* xb = ctl->xchg[nblocks & 1];
+            xb[half * BQ + row] = l_sum;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            l_sum += xb[(half ^ 1) * BQ + row];
         }
         if (ok && mbar_wait(smem_u32(&ctl->pv_done), (uint32_t)((nblocks - 1) & 1), abort_flag)) {
             tcgen05_fence_after();
@@ -330,6 +406,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             T* orow = reinterpret_cast<T*>(p.out) + (token0 + row) * (int64_t)C + head * D;
 #pragma unroll
             for (int cc = 0; cc < D / 16; ++cc) {
+                if ((cc & 1) != half) continue;
                 uint32_t o[16];
                 tmem_ld16(lane_base + (uint32_t)(O_COL + cc * 16), o);
                 tmem_ld_wait();
@@ -337,8 +414,10 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
                 for (int e = 0; e < 8; ++e)
                     w[e] = AtOps<T>::pack(__uint_as_float(o[2 * e]) * inv_l, __uint_as_float(o[2 * e + 1]) * inv_l);
-                *reinterpret_cast<uint4*>(orow + cc * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-                *reinterpret_cast<uint4*>(orow + cc * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                if (valid_q) {
+                    *reinterpret_cast<uint4*>(orow + cc * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(orow + cc * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
             }
         }
     }
@@ -346,40 +425,47 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
-    if (warp == 5) {
+    if (warp == 9) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS_AT) : "memory");
     }
     if (threadIdx.x == 0 && ctl->abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
 }
 
-// V of every (image, head) as [D, L] (keys contiguous): the K-major B operand of O += P V.
-// One CTA transposes 64 tokens x D values through shared memory.
+// V of every (unit, head) as [D, keys] (keys contiguous): the K-major B operand of O += P V.
+// Keys are laid out as [H, key_pitch] (key_pitch = W for images; 16 for windows, the columns
+// W..15 zero) and padded with zeros to a multiple of 64.  One CTA transposes 64 key slots x D
+// values through shared memory.
 template <typename T>
 __global__ void __launch_bounds__(256)
-transpose_v_kernel(const T* __restrict__ qkv, int L, int heads, int D, T* __restrict__ vt)
+transpose_v_kernel(const T* __restrict__ qkv, int H, int W, int key_pitch, int vt_len, int heads, int D, T* __restrict__ vt)
 {
-    __shared__ T tile[128][BKEY + 2];                               // [dv][token], padded against bank conflicts
-    const int l0 = blockIdx.x * BKEY;
+    __shared__ T tile[128][BKEY + 2];                               // [dv][key slot], padded against bank conflicts
+    const int s0 = blockIdx.x * BKEY;                               // first key slot of this CTA
     const int bh = blockIdx.y;
-    const int head = bh % heads, image = bh / heads;
+    const int head = bh % heads, unit = bh / heads;
     const int C = heads * D;
+    const int L = H * W;
     const int chunks = D >> 3;                                      // 16-byte chunks per token
-    const T* src = qkv + ((int64_t)image * L + l0) * 3 * C + 2 * C + head * D;
+    const T* src = qkv + (int64_t)unit * L * 3 * C + 2 * C + head * D;
     for (int idx = threadIdx.x; idx < BKEY * chunks; idx += blockDim.x) {
-        const int tok = idx / chunks, ch = idx - tok * chunks;
-        const uint4 v = *reinterpret_cast<const uint4*>(src + (int64_t)tok * 3 * C + ch * 8);
+        const int slot = idx / chunks, ch = idx - slot * chunks;
+        const int kh = (s0 + slot) / key_pitch, kw = (s0 + slot) - kh * key_pitch;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (kh < H && kw < W) v = *reinterpret_cast<const uint4*>(src + (int64_t)(kh * W + kw) * 3 * C + ch * 8);
         const T* e = reinterpret_cast<const T*>(&v);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) tile[ch * 8 + k][tok] = e[k];
+        for (int k = 0; k < 8; ++k) tile[ch * 8 + k][slot] = e[k];
     }
     __syncthreads();
-    T* dst = vt + (int64_t)bh * D * L + l0;
+    T* dst = vt + (int64_t)bh * D * vt_len + s0;
     for (int idx = threadIdx.x; idx < D * (BKEY / 2); idx += blockDim.x) {
         const int dv = idx / (BKEY / 2), pr = idx - dv * (BKEY / 2);
-        *reinterpret_cast<uint32_t*>(dst + (int64_t)dv * L + pr * 2) = *reinterpret_cast<const uint32_t*>(&tile[dv][pr * 2]);
+        *reinterpret_cast<uint32_t*>(dst + (int64_t)dv * vt_len + pr * 2) = *reinterpret_cast<const uint32_t*>(&tile[dv][pr * 2]);
     }
 }
+
+CUtensorMapDataType map_type(bool bf16) { return bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16; }
 
 // bf16 / fp16 [rows, cols] row-major, box = box_rows x 64 elements (128 bytes), 128-byte swizzle
 int make_map_16bit(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t pitch_elems, int box_rows, bool bf16) {
@@ -389,73 +475,104 @@ int make_map_16bit(CUtensorMap* map, const void* base, int64_t rows, int64_t col
     cuuint64_t strides[1] = {(cuuint64_t)(pitch_elems * 2)};
     cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base),
+    CUresult r = fn(map, map_type(bf16), 2, const_cast<void*>(base),
                     dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return SAMQ_OK;
 }
 
-template <typename T, int D>
-int launch_attn_global(const void* qkv, const void* vt, const AttnParams& p, int64_t images, cudaStream_t st) {
+// qkv [units * H * W, cols] seen as [units, H, W, cols]; box = 64 columns x 16 key columns x 4 key
+// rows of one unit: key columns W..15 and key rows >= H lie outside the view and read as zeros
+int make_map_window_keys(CUtensorMap* map, const void* base, int64_t units, int H, int W, int64_t cols, bool bf16) {
+    gemm::EncodeTiledFn fn = gemm::encode_tiled_fn();
+    if (fn == nullptr) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)units};
+    cuuint64_t strides[3] = {(cuuint64_t)(cols * 2), (cuuint64_t)(cols * 2 * W), (cuuint64_t)(cols * 2 * W * H)};
+    cuuint32_t box[4] = {64u, 16u, 4u, 1u};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, map_type(bf16), 4, const_cast<void*>(base),
+                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed with CUresult %d", (int)r);
+    return SAMQ_OK;
+}
+
+template <typename T, int D, bool WINDOW>
+int launch_attn(const void* qkv, const void* vt, const AttnParams& p, int64_t units, int vt_len, cudaStream_t st) {
     const bool bf16 = std::is_same<T, __nv_bfloat16>::value;
     const int C = p.heads * D;
     CUtensorMap mq, mk, mv;
     int rc = make_map_16bit(&mq, qkv, p.tokens, 3 * C, 3 * C, BQ, bf16);
     if (rc != SAMQ_OK) return rc;
-    rc = make_map_16bit(&mk, qkv, p.tokens, 3 * C, 3 * C, BKEY, bf16);
+    rc = WINDOW ? make_map_window_keys(&mk, qkv, units, p.H, p.W, 3 * C, bf16)
+                : make_map_16bit(&mk, qkv, p.tokens, 3 * C, 3 * C, BKEY, bf16);
     if (rc != SAMQ_OK) return rc;
-    rc = make_map_16bit(&mv, vt, images * p.heads * D, p.L, p.L, D, bf16);
+    rc = make_map_16bit(&mv, vt, units * p.heads * D, vt_len, vt_len, D, bf16);
     if (rc != SAMQ_OK) return rc;
-    auto kernel = attn_global_kernel<T, D>;
+    auto kernel = attn_global_kernel<T, D, WINDOW>;
     SAMQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AtSmem<D>::TOTAL));
-    const unsigned grid = (unsigned)(images * p.heads * p.qtiles);
+    const unsigned grid = (unsigned)(units * p.heads * p.qtiles);
     kernel<<<grid, AT_THREADS, AtSmem<D>::TOTAL, st>>>(mq, mk, mv, p);
     SAMQ_CUDA_TRY(cudaGetLastError());
     return SAMQ_OK;
 }
 
+// key slots per unit, padded to whole 64-key blocks
+int padded_keys(int H, int W) { return W == BKEY ? H * W : ((H * 16 + BKEY - 1) / BKEY) * BKEY; }
+
 }  // namespace
 
-int attn_transpose_v_dispatch(const void* qkv, int dtype, int64_t images, int L, int heads, int head_dim, void* vt, void* stream)
+int attn_transpose_v_dispatch(const void* qkv, int dtype, int64_t units, int H, int W, int heads, int head_dim, void* vt, void* stream)
 {
     if (qkv == nullptr || vt == nullptr) return fail(SAMQ_ERR_BAD_ARG, "null pointer");
-    if (images < 0 || L <= 0 || heads <= 0 || head_dim <= 0 || head_dim > 128 || (head_dim & 7) || (L % BKEY) != 0)
-        return fail(SAMQ_ERR_BAD_ARG, "bad shape images=%lld L=%d heads=%d head_dim=%d", (long long)images, L, heads, head_dim);
+    if (units < 0 || H <= 0 || W <= 0 || heads <= 0 || head_dim <= 0 || head_dim > 128 || (head_dim & 7) || !(W == BKEY || (W <= 16 && H <= 16)))
+        return fail(SAMQ_ERR_BAD_ARG, "bad shape units=%lld H=%d W=%d heads=%d head_dim=%d", (long long)units, H, W, heads, head_dim);
     if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(vt) & 3))
         return fail(SAMQ_ERR_ALIGNMENT, "qkv must be 16-byte aligned");
     if (dtype != SAMQ_F16 && dtype != SAMQ_BF16) return fail(SAMQ_ERR_UNSUPPORTED, "attention helpers take fp16 or bf16");
-    if (images == 0) return SAMQ_OK;
-    dim3 grid((unsigned)(L / BKEY), (unsigned)(images * heads));
+    if (units == 0) return SAMQ_OK;
+    const int vt_len = padded_keys(H, W);
+    dim3 grid((unsigned)(vt_len / BKEY), (unsigned)(units * heads));
     // both types are 16-bit: the transpose only moves bits
     transpose_v_kernel<__half><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(qkv), L, heads, head_dim, static_cast<__half*>(vt));
+        static_cast<const __half*>(qkv), H, W, W == BKEY ? BKEY : 16, vt_len, heads, head_dim, static_cast<__half*>(vt));
     SAMQ_CUDA_TRY(cudaGetLastError());
     return SAMQ_OK;
 }
 
-int attn_global_dispatch(const void* qkv, const void* vt, const void* rel_all, int dtype, int64_t images, int rel_pitch,
+int attn_global_dispatch(const void* qkv, const void* vt, const void* rel_all, int dtype, int64_t units, int rel_pitch,
                          int H, int W, int heads, int head_dim, float scale, void* out, int32_t* status, void* stream)
 {
     if (qkv == nullptr || vt == nullptr || rel_all == nullptr || out == nullptr) return fail(SAMQ_ERR_BAD_ARG, "null pointer");
-    if (W != BKEY) return fail(SAMQ_ERR_UNSUPPORTED, "the global attention kernel walks key rows of %d tokens (W=%d)", BKEY, W);
-    if (images < 0 || H <= 0 || heads <= 0 || (H * W) % BQ != 0 || rel_pitch < 2 * H - 1 + 2 * W - 1)
-        return fail(SAMQ_ERR_BAD_ARG, "bad shape images=%lld H=%d W=%d heads=%d rel_pitch=%d", (long long)images, H, W, heads, rel_pitch);
+    const bool window = W != BKEY;
+    if (window ? !(W <= 16 && H <= 16 && W >= 1 && H >= 1) : ((H * W) % BQ != 0 || H <= 0))
+        return fail(SAMQ_ERR_UNSUPPORTED, "the attention kernel takes images of H x %d tokens or windows of at most 16 x 16 (H=%d W=%d)", BKEY, H, W);
+    if (units < 0 || heads <= 0 || rel_pitch < 2 * H - 1 + 2 * W - 1)
+        return fail(SAMQ_ERR_BAD_ARG, "bad shape units=%lld H=%d W=%d heads=%d rel_pitch=%d", (long long)units, H, W, heads, rel_pitch);
     if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(vt) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
         return fail(SAMQ_ERR_ALIGNMENT, "qkv, vt and out must be 16-byte aligned");
     if (dtype != SAMQ_F16 && dtype != SAMQ_BF16) return fail(SAMQ_ERR_UNSUPPORTED, "attention takes fp16 or bf16");
-    if (images == 0) return SAMQ_OK;
+    if (units == 0) return SAMQ_OK;
     AttnParams p;
-    p.rel_all = rel_all; p.out = out; p.tokens = images * (int64_t)H * W; p.rel_pitch = rel_pitch;
-    p.H = H; p.L = H * W; p.heads = heads; p.qtiles = (H * W) / BQ; p.scale = scale; p.status = status;
+    p.rel_all = rel_all; p.out = out; p.tokens = units * (int64_t)H * W; p.rel_pitch = rel_pitch;
+    p.H = H; p.W = W; p.L = H * W; p.heads = heads; p.qtiles = (H * W + BQ - 1) / BQ; p.scale = scale; p.status = status;
+    const int vt_len = padded_keys(H, W);
+    p.nblocks = vt_len / BKEY;
     if (p.tokens > 2147483647LL) return fail(SAMQ_ERR_TOO_LARGE, "too many tokens");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool bf = dtype == SAMQ_BF16;
+#define SAMQ_ATTN(DV)                                                                                                   \
+    (window ? (bf ? launch_attn<__nv_bfloat16, DV, true>(qkv, vt, p, units, vt_len, st)                                  \
+                  : launch_attn<__half, DV, true>(qkv, vt, p, units, vt_len, st))                                        \
+            : (bf ? launch_attn<__nv_bfloat16, DV, false>(qkv, vt, p, units, vt_len, st)                                 \
+                  : launch_attn<__half, DV, false>(qkv, vt, p, units, vt_len, st)))
     switch (head_dim) {
-    case 64: return bf ? launch_attn_global<__nv_bfloat16, 64>(qkv, vt, p, images, st) : launch_attn_global<__half, 64>(qkv, vt, p, images, st);
-    case 80: return bf ? launch_attn_global<__nv_bfloat16, 80>(qkv, vt, p, images, st) : launch_attn_global<__half, 80>(qkv, vt, p, images, st);
-    default: return fail(SAMQ_ERR_UNSUPPORTED, "global attention kernel is built for head_dim 64 and 80 (got %d)", head_dim);
+    case 64: return SAMQ_ATTN(64);
+    case 80: return SAMQ_ATTN(80);
+    default: return fail(SAMQ_ERR_UNSUPPORTED, "the attention kernel is built for head_dim 64 and 80 (got %d)", head_dim);
     }
+#undef SAMQ_ATTN
 }
 
 }  // namespace samq

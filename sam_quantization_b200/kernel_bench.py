@@ -3,6 +3,7 @@
     python -m sam_quantization_b200.kernel_bench gemm  --M 32768 --N 5120 --K 1280 --gelu
     python -m sam_quantization_b200.kernel_bench quant --M 65536 --K 1280 [--ln] [--gather] [--hadamard full]
     python -m sam_quantization_b200.kernel_bench attn  --windows 200 --H 14 --W 14 --heads 16 --head-dim 80
+    python -m sam_quantization_b200.kernel_bench attn-global --images 8 --H 64 --heads 16 --head-dim 80
     python -m sam_quantization_b200.kernel_bench sweep            # the W8A8 GEMM sweep: M x (K, N) x granularity
 
 Each line of output is JSON: the shape, the mean CUDA-event time over ``--iters`` launches after
@@ -117,6 +118,25 @@ def bench_window_attention(windows, H, W, heads, head_dim, dtype=torch.bfloat16,
             "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), "tflops": round(flops / ms / 1e9, 1)}
 
 
+def bench_global_attention(images, H, heads, head_dim, dtype=torch.bfloat16, iters=20, warmup=5):
+    dev = torch.device("cuda")
+    W = 64
+    L, C = H * W, heads * head_dim
+    qkv = [torch.randn((images * L, 3 * C), device=dev, dtype=dtype) for _ in range(2)]
+    rh = (torch.randn((2 * H - 1, head_dim), device=dev) * 0.02).to(dtype)
+    rw = (torch.randn((2 * W - 1, head_dim), device=dev) * 0.02).to(dtype)
+    table = ops.rel_pos_table(rh, rw, dtype, dev)
+
+    def run(i):
+        ops.attn_global(qkv[i % 2], images, H, W, heads, rh, rw, head_dim ** -0.5, table=table)
+
+    ms = _time(run, iters, warmup)
+    ops.check_status()
+    flops = 4.0 * images * heads * L * L * head_dim
+    return {"kernel": "attn_global (+ transpose_v + rel products)", "images": images, "H": H, "W": W, "heads": heads,
+            "head_dim": head_dim, "ms": round(ms, 5), "tflops": round(flops / ms / 1e9, 1)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--pair-mode", dest="pair_mode", type=int, default=None, choices=[0, 1, 2],
@@ -149,6 +169,13 @@ def main():
     a.add_argument("--head-dim", dest="head_dim", type=int, default=80)
     a.add_argument("--iters", type=int, default=50)
     a.add_argument("--warmup", type=int, default=10)
+    ag = sub.add_parser("attn-global")
+    ag.add_argument("--images", type=int, default=8)
+    ag.add_argument("--H", type=int, default=64)
+    ag.add_argument("--heads", type=int, default=16)
+    ag.add_argument("--head-dim", dest="head_dim", type=int, default=80)
+    ag.add_argument("--iters", type=int, default=20)
+    ag.add_argument("--warmup", type=int, default=5)
     s = sub.add_parser("sweep")
     s.add_argument("--iters", type=int, default=100)
     s.add_argument("--warmup", type=int, default=20)
@@ -160,6 +187,8 @@ def main():
         print(json.dumps(bench_gemm(args.M, args.N, args.K, args.gelu, args.residual, args.w_gran, iters=args.iters, warmup=args.warmup)))
     elif args.cmd == "attn":
         print(json.dumps(bench_window_attention(args.windows, args.H, args.W, args.heads, args.head_dim, iters=args.iters, warmup=args.warmup)))
+    elif args.cmd == "attn-global":
+        print(json.dumps(bench_global_attention(args.images, args.H, args.heads, args.head_dim, iters=args.iters, warmup=args.warmup)))
     elif args.cmd == "quant":
         print(json.dumps(bench_quant(args.M, args.K, getattr(torch, args.dtype), args.ln, args.gather, args.hadamard,
                                      args.granularity, iters=args.iters, warmup=args.warmup)))

@@ -423,22 +423,24 @@ def attn_rel_bias(qkv: torch.Tensor, images: int, H: int, W: int, num_heads: int
 
 
 def attn_global_supported(H: int, W: int, head_dim: int, dtype) -> bool:
-    """Shapes ``samq_attn_global`` is built for."""
-    return W == 64 and (H * W) % 128 == 0 and head_dim in (64, 80) and dtype in (torch.float16, torch.bfloat16)
+    """Shapes ``samq_attn_global`` is built for: images of H x 64 tokens or windows up to 16 x 16."""
+    shape_ok = (W == 64 and (H * W) % 128 == 0) or (W <= 16 and H <= 16)
+    return shape_ok and head_dim in (64, 80) and dtype in (torch.float16, torch.bfloat16)
 
 
-def attn_global(qkv: torch.Tensor, images: int, H: int, W: int, num_heads: int, rel_pos_h: torch.Tensor,
+def attn_global(qkv: torch.Tensor, units: int, H: int, W: int, num_heads: int, rel_pos_h: torch.Tensor,
                 rel_pos_w: torch.Tensor, scale: float, table: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Global attention with the decomposed relative-position bias (``samq_attn_global``):
-    ``qkv`` [images*H*W, 3C] -> [images*H*W, C], heads side by side.  Scores and bias stay on chip."""
+    """Attention with the decomposed relative-position bias on the tensor cores (``samq_attn_global``):
+    ``qkv`` [units*H*W, 3C] -> [units*H*W, C], heads side by side; a unit is an image (W = 64) or a
+    window (H, W <= 16).  Scores and bias stay on chip."""
     _require_cuda(qkv, "qkv")
     lib = _lib.load()
     tokens, three_c = qkv.shape
     C = three_c // 3
     d = C // num_heads
     L = H * W
-    if tokens != images * L or not qkv.is_contiguous():
-        raise ValueError("qkv must be a contiguous [images*H*W, 3C] tensor")
+    if tokens != units * L or not qkv.is_contiguous():
+        raise ValueError("qkv must be a contiguous [units*H*W, 3C] tensor")
     if rel_pos_h.shape != (2 * H - 1, d) or rel_pos_w.shape != (2 * W - 1, d):
         raise ValueError("relative position tables must be [2H-1, d] and [2W-1, d]")
     if table is None:
@@ -446,14 +448,15 @@ def attn_global(qkv: torch.Tensor, images: int, H: int, W: int, num_heads: int, 
     rel_all = rel_pos_products(qkv, num_heads, table)
     if not rel_all.is_contiguous():
         rel_all = rel_all.contiguous()
-    vt = torch.empty((images * num_heads * d, L), dtype=qkv.dtype, device=qkv.device)
+    keys = L if W == 64 else (H * 16 + 63) // 64 * 64
+    vt = torch.empty((units * num_heads * d, keys), dtype=qkv.dtype, device=qkv.device)
     out = torch.empty((tokens, C), dtype=qkv.dtype, device=qkv.device)
     esz = qkv.element_size()
     with torch.cuda.device(qkv.device):
         with _Timed("attn_transpose_v", 2 * tokens * C * esz):
-            _lib.check(lib.samq_attn_transpose_v(_ptr(qkv), _DTYPE_CODE[qkv.dtype], images, L, num_heads, d, _ptr(vt), _stream()))
+            _lib.check(lib.samq_attn_transpose_v(_ptr(qkv), _DTYPE_CODE[qkv.dtype], units, H, W, num_heads, d, _ptr(vt), _stream()))
         with _Timed("attn_global", 4 * tokens * C * esz):
-            _lib.check(lib.samq_attn_global(_ptr(qkv), _ptr(vt), _ptr(rel_all), _DTYPE_CODE[qkv.dtype], images, rel_all.shape[-1],
+            _lib.check(lib.samq_attn_global(_ptr(qkv), _ptr(vt), _ptr(rel_all), _DTYPE_CODE[qkv.dtype], units, rel_all.shape[-1],
                                             H, W, num_heads, d, float(scale), _ptr(out), _ptr(status_word(qkv.device)), _stream()))
     return out
 

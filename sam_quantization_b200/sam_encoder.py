@@ -138,8 +138,9 @@ class Attention(nn.Module):
         # 0.43 ms for 200 windows x 16 heads it is still slower than augmented rows + the fused library
         # attention (0.31 ms); it needs K/V prefetch across windows to hide its load phase
         self.fused_window_kernel = False
-        # global (64-token-wide) attention in the library's tensor-core kernel (samq_attn_global): scores and the
-        # relative-position bias stay on chip instead of going through a [heads, L, L] bias tensor
+        # attention of whole images (64 tokens wide) and of windows up to 16 x 16 in the library's tensor-core
+        # kernel (samq_attn_global): scores and the relative-position bias stay on chip instead of going through
+        # a [heads, L, L] bias tensor or augmented q / k rows
         self.fused_global_kernel = True
         self._onehot = {}
         if use_rel_pos:
@@ -203,6 +204,9 @@ class Attention(nn.Module):
             if self.fused_window_kernel and ops.attn_windowed_supported(H, W, d):
                 return ops.attn_windowed(qkv, B, H, W, nh, self.rel_pos_h, self.rel_pos_w, self.scale,
                                          table=self._rel_table(qkv.dtype, qkv.device))
+            if self.fused_global_kernel and ops.attn_global_supported(H, W, d, qkv.dtype):
+                return ops.attn_global(qkv, B, H, W, nh, self.rel_pos_h, self.rel_pos_w, self.scale,
+                                       table=self._rel_table(qkv.dtype, qkv.device))
             if d + extra <= 128:
                 width = (d + extra + 7) // 8 * 8
                 qa, ka = ops.attn_window_prep(qkv, H, W, nh, self.rel_pos_h, self.rel_pos_w, self.scale, width,
@@ -210,9 +214,6 @@ class Attention(nn.Module):
                 out = F.scaled_dot_product_attention(qa.view(B, L, nh, width).transpose(1, 2), ka.view(B, L, nh, width).transpose(1, 2),
                                                      v.transpose(1, 2), scale=1.0)
                 return out.transpose(1, 2).reshape(B * L, nh * d)
-            if self.fused_global_kernel and ops.attn_global_supported(H, W, d, qkv.dtype):
-                return ops.attn_global(qkv, B, H, W, nh, self.rel_pos_h, self.rel_pos_w, self.scale,
-                                       table=self._rel_table(qkv.dtype, qkv.device))
             outs = []
             step = max(1, self.global_chunk)
             for i in range(0, B, step):

@@ -291,14 +291,16 @@ def test_windowed_attention_kernel_variants_agree(cuda_device, dtype, H, W, dim,
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("H,dim,nh,B", [(64, 160, 2, 2), (64, 128, 2, 1), (2, 80, 1, 3), (6, 64, 1, 2)])
-def test_global_attention_kernel_against_fp32_reference(cuda_device, dtype, H, dim, nh, B):
-    """The tensor-core global attention (scores and bias on chip, online softmax) against the
-    same attention in fp32 torch ops, and against the route through the explicit bias tensor."""
+@pytest.mark.parametrize("H,W,dim,nh,B", [(64, 64, 160, 2, 2), (64, 64, 128, 2, 1), (2, 64, 80, 1, 3), (6, 64, 64, 1, 2),
+                                          (14, 14, 160, 2, 7), (14, 14, 128, 2, 3), (16, 16, 80, 1, 2), (5, 3, 64, 1, 4),
+                                          (13, 9, 160, 2, 3), (1, 1, 80, 1, 2)])
+def test_global_attention_kernel_against_fp32_reference(cuda_device, dtype, H, W, dim, nh, B):
+    """The tensor-core attention (scores and bias on chip, online softmax), for whole images and for
+    windows, against the same attention in fp32 torch ops and against the library-attention route
+    (explicit bias tensor for images, augmented q / k rows for windows)."""
     from sam_quantization_b200 import ops
     from sam_quantization_b200.sam_encoder import Attention
-    W = 64
-    torch.manual_seed(H + dim)
+    torch.manual_seed(H + dim + W)
     attn = Attention(dim, nh, use_rel_pos=True, input_size=(H, W)).to(cuda_device, dtype)
     d = dim // nh
     with torch.no_grad():
