@@ -11,16 +11,15 @@
 // and the rel_w terms are the same 64 values in every block: they live in registers.
 //
 // One CTA owns 128 queries of one (image, head); two CTAs are resident per SM so that one's
-// softmax overlaps the other's matrix products.  Roles (320 threads):
-//   warps 0-7  softmax: warps w and w + 4 share the 32 query rows of TMEM lane quadrant w, a thread
-//              owns one row and half of its 64 key columns.  Per key block: load the scores
-//              from tensor memory, t = s * scale * log2e + bias, row maximum, p = 2^(t - m),
+// softmax overlaps the other's matrix products.  Roles (192 threads):
+//   warps 0-3  softmax: thread r owns query row r (= TMEM lane r).  Per key block: load the 64
+//              scores from tensor memory, t = s * scale * log2e + bias, row maximum, p = 2^(t - m),
 //              row sum, P as bf16/fp16 into shared memory in the 128-byte-swizzled operand layout.
 //              The maximum m is only raised when a row's new maximum exceeds it by more than 8
 //              (p stays below 2^8); the output accumulator in tensor memory is then rescaled in place.
-//   warp 8     TMA producer: Q once, then per block the K rows and the matching V^T columns
+//   warp 4     TMA producer: Q once, then per block the K rows and the matching V^T columns
 //              (two stages).
-//   warp 9     MMA issuer: S = Q K^T (M128 N64 K=D) into one of two score buffers, and
+//   warp 5     MMA issuer: S = Q K^T (M128 N64 K=D) into one of two score buffers, and
 //              O += P V (M128 N=D K64), both tcgen05.mma kind::f16 with fp32 accumulation.
 // V is consumed K-major (V^T [D, L] per head), written by attn_transpose_v below.
 // Every wait is bounded; a wait that runs out sets the abort flag, the roles drain, and the
@@ -35,7 +34,7 @@ namespace {
 
 constexpr int BQ = 128;                 // queries per CTA
 constexpr int BKEY = 64;                // keys per block = one row of the key grid
-constexpr int AT_THREADS = 320;        // 8 softmax warps, the TMA warp, the MMA warp
+constexpr int AT_THREADS = 192;        // 4 softmax warps, the TMA warp, the MMA warp
 constexpr int TMEM_COLS_AT = 256;       // S0 at 0, S1 at 64, O at 128
 constexpr int O_COL = 128;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -44,7 +43,6 @@ struct AttnControl {
     uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_done;
     uint32_t tmem_base;
     uint32_t abort_flag;
-    float xchg[2][2 * BQ];   // per-row partial maxima / sums swapped between the two halves of a row
 };
 
 struct AttnParams {
@@ -117,7 +115,8 @@ template <int D> struct AtSmem {
     static constexpr int NATOM = (D + 63) / 64;            // 128-byte swizzle rows per operand row
     static constexpr int Q_BYTES = NATOM * BQ * 128;
     static constexpr int K_BYTES = NATOM * BKEY * 128;
-    static constexpr int VT_BYTES = D * 128;               // D rows of 64 keys
+    static constexpr int DV = D;                           // V^T rows
+    static constexpr int VT_BYTES = DV * 128;              // DV rows of 64 keys
     static constexpr int STAGE_BYTES = K_BYTES + VT_BYTES;
     static constexpr int P_BYTES = BQ * 128;
     static constexpr int TOTAL = 1024 + Q_BYTES + 2 * STAGE_BYTES + P_BYTES + (int)sizeof(AttnControl) + 64;
@@ -161,9 +160,9 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&ctl->k_full[s]), 1); mbar_init(smem_u32(&ctl->k_empty[s]), 1);
             mbar_init(smem_u32(&ctl->v_full[s]), 1); mbar_init(smem_u32(&ctl->v_empty[s]), 1);
-            mbar_init(smem_u32(&ctl->s_full[s]), 1);  mbar_init(smem_u32(&ctl->s_empty[s]), 8);
+            mbar_init(smem_u32(&ctl->s_full[s]), 1);  mbar_init(smem_u32(&ctl->s_empty[s]), 4);
         }
-        mbar_init(smem_u32(&ctl->p_full), 8);
+        mbar_init(smem_u32(&ctl->p_full), 4);
         mbar_init(smem_u32(&ctl->pv_done), 1);
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -171,7 +170,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_vt) : "memory");
     }
-    if (warp == 9) {
+    if (warp == 5) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(&ctl->tmem_base)), "r"((uint32_t)TMEM_COLS_AT) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -181,7 +180,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     tcgen05_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    if (warp == 8) {
+    if (warp == 4) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             const uint32_t qbar = smem_u32(&ctl->q_full);
@@ -210,7 +209,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (!mbar_wait(smem_u32(&ctl->v_empty[st]), ((i >> 1) & 1) ^ 1u, abort_flag)) return false;
                 const uint32_t bar = smem_u32(&ctl->v_full[st]);
                 mbar_expect_tx(bar, SM::VT_BYTES);
-                tma_load_2d(smem_u32(stages + st * SM::STAGE_BYTES + SM::K_BYTES), &map_vt, bar, i * BKEY, bh * D);
+                tma_load_2d(smem_u32(stages + st * SM::STAGE_BYTES + SM::K_BYTES), &map_vt, bar, i * BKEY, bh * SM::DV);
                 return true;
             };
             for (int i = 0; i < nblocks && ok; ++i) {
@@ -223,11 +222,11 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 while (clock64() - t0 < 2000000LL) { }          // let copies in flight land before the CTA retires
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == 5) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc_s = f16_idesc(AtOps<T>::kFormat, BQ, BKEY);
-            constexpr uint32_t idesc_o = f16_idesc(AtOps<T>::kFormat, BQ, D);
+            constexpr uint32_t idesc_o = f16_idesc(AtOps<T>::kFormat, BQ, SM::DV);
             bool ok = mbar_wait(smem_u32(&ctl->q_full), 0, abort_flag);
             auto issue_s = [&](int j) -> bool {
                 const int st = j & 1;
@@ -267,80 +266,67 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
     } else {
         // ---------------- softmax + output ----------------
-        // Warps w and w + 4 share the 32 query rows of TMEM lane quadrant w: each thread owns one
-        // row and HALF of its 64 key columns.  The two halves of a row exchange their partial
-        // maxima through shared memory once per block (and their partial sums once at the end).
-        const int quad = warp & 3, half = warp >> 2;
-        const int row = quad * 32 + lane;                          // query row in the tile = TMEM lane
+        const int row = warp * 32 + lane;                          // query row in the tile = TMEM lane
         const int lq = qt * BQ + row;                              // query index inside the unit
-        const bool valid_q = lq < p.L;                             // the last tile of a window runs past its 196 tokens
+        const bool valid_q = lq < p.L;                             // the last tile of a window runs past its tokens
         const int lqc = valid_q ? lq : p.L - 1;
         const int qh = lqc / p.W, qw = lqc - qh * p.W;
         const T* rel = reinterpret_cast<const T*>(p.rel_all) +
                        ((int64_t)head * p.tokens + (int64_t)image * p.L + lqc) * p.rel_pitch;
         const int rows_h = 2 * p.H - 1;
-        constexpr int HC = BKEY / 2;                               // key columns per thread
-        const int col0 = half * HC;
-        // rel_w term of this thread's key columns, times log2(e); -inf for absent columns
-        constexpr int NRW = WINDOW ? 16 : HC;
+        // rel_w term of the key columns, times log2(e); -inf for absent columns
+        constexpr int NRW = WINDOW ? 16 : BKEY;
         float rwl[NRW];
 #pragma unroll
-        for (int j = 0; j < NRW; ++j) {
-            const int kw = WINDOW ? j : col0 + j;
-            rwl[j] = kw < p.W ? AtOps<T>::up(rel + rows_h + (qw - kw + p.W - 1)) * LOG2E : -INFINITY;
-        }
+        for (int j = 0; j < NRW; ++j)
+            rwl[j] = j < p.W ? AtOps<T>::up(rel + rows_h + (qw - j + p.W - 1)) * LOG2E : -INFINITY;
         const float c = p.scale * LOG2E;
         const float2 c2 = make_float2(c, c);
         float m_used = -INFINITY, l_sum = 0.f;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
         uint8_t* prow = p_tile + row * 128;
         const uint32_t sw = (uint32_t)(row & 7);
-        const int pair_bar = 1 + quad;                             // named barrier of the two warps of a quadrant
         bool ok = true;
         for (int i = 0; i < nblocks; ++i) {
-            // rel_h term of the key row(s) this thread sees in block i: one row for images, two of
-            // the block's four rows for windows (-inf for rows beyond the window)
-            float rh, rh_b = 0.f;
-            if (WINDOW) {
-                const int kh = 4 * i + 2 * half;
-                rh = kh < p.H ? AtOps<T>::up(rel + (qh - kh + p.H - 1)) * LOG2E : -INFINITY;
-                rh_b = kh + 1 < p.H ? AtOps<T>::up(rel + (qh - kh - 1 + p.H - 1)) * LOG2E : -INFINITY;
-            } else {
-                rh = AtOps<T>::up(rel + (qh - i + p.H - 1)) * LOG2E;
-            }
-            if (ok && !mbar_wait(smem_u32(&ctl->s_full[i & 1]), (uint32_t)((i >> 1) & 1), abort_flag)) ok = false;
-            float t[HC];
-            float mi = -INFINITY;
-            if (ok) {                                              // warp-uniform
-                tcgen05_fence_after();
-                uint32_t sc[HC];
-                tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY + col0), sc);
-                tmem_ld_wait();
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[i & 1]));   // the score buffer may be overwritten
-
-                // t = s * scale * log2e + (rel_h + rel_w) * log2e, two columns per instruction
-                const float2 rh2 = make_float2(rh, rh), rh2_b = make_float2(rh_b, rh_b);
-                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // independent chains
+            // rel_h term of the key row(s) of block i: one row for images, four for windows
+            // (-inf for rows beyond the window)
+            constexpr int NRH = WINDOW ? 4 : 1;
+            float2 rh2[NRH];
 #pragma unroll
-                for (int j = 0; j < HC; j += 2) {
-                    const float2 b0 = WINDOW ? __fadd2_rn(make_float2(rwl[j & 15], rwl[(j & 15) + 1]), j < 16 ? rh2 : rh2_b)
-                                             : __fadd2_rn(make_float2(rwl[j % NRW], rwl[(j + 1) % NRW]), rh2);
-                    const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(sc[j]), __uint_as_float(sc[j + 1])), c2, b0);
-                    t[j] = t0.x; t[j + 1] = t0.y;
-                    mx[(j >> 1) & 3] = fmaxf(mx[(j >> 1) & 3], fmaxf(t0.x, t0.y));
-                }
-                mi = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            for (int r = 0; r < NRH; ++r) {
+                const int kh = NRH * i + r;
+                const float v = kh < p.H ? AtOps<T>::up(rel + (qh - kh + p.H - 1)) * LOG2E : -INFINITY;
+                rh2[r] = make_float2(v, v);
             }
-            // the other half's maximum (buffers alternate per block so a write never overtakes a read).
-            // A warp that gave up on a wait still visits this barrier every block: its partner is never left waiting.
-            float* xb = ctl->xchg[i & 1];
-            xb[half * BQ + row] = mi;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-            if (!ok) continue;
-            mi = fmaxf(mi, xb[(half ^ 1) * BQ + row]);
-            // raise the running maximum only when some row of the warp needs it (both halves agree)
+            if (!mbar_wait(smem_u32(&ctl->s_full[i & 1]), (uint32_t)((i >> 1) & 1), abort_flag)) { ok = false; break; }
+            tcgen05_fence_after();
+            uint32_t s0[32], s1[32];
+            tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY), s0);
+            tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY + 32), s1);
+            tmem_ld_wait();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[i & 1]));   // the score buffer may be overwritten
+
+            // t = s * scale * log2e + (rel_h + rel_w) * log2e, two columns per instruction
+            float t[BKEY];
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // independent chains
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+                // column j of the first half and column 32 + j of the second
+                const float2 w0 = make_float2(rwl[j % NRW], rwl[(j + 1) % NRW]);
+                const float2 w1 = make_float2(rwl[(32 + j) % NRW], rwl[(33 + j) % NRW]);
+                const float2 b0 = __fadd2_rn(w0, rh2[WINDOW ? (j >> 4) : 0]);
+                const float2 b1 = __fadd2_rn(w1, rh2[WINDOW ? 2 + (j >> 4) : 0]);
+                const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(s0[j]), __uint_as_float(s0[j + 1])), c2, b0);
+                const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(s1[j]), __uint_as_float(s1[j + 1])), c2, b1);
+                t[j] = t0.x; t[j + 1] = t0.y; t[32 + j] = t1.x; t[32 + j + 1] = t1.y;
+                const int a = (j >> 1) & 1;
+                mx[2 * a] = fmaxf(mx[2 * a], fmaxf(t0.x, t0.y));
+                mx[2 * a + 1] = fmaxf(mx[2 * a + 1], fmaxf(t1.x, t1.y));
+            }
+            const float mi = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            // raise the running maximum only when some row of the warp needs it
             const bool raise = __any_sync(0xffffffffu, mi > m_used + 8.0f);
             float alpha = 1.0f;
             if (raise) {
@@ -350,10 +336,10 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 l_sum *= alpha;
             }
             const float2 nm2 = make_float2(-m_used, -m_used);
-            uint32_t pk[HC / 2];
+            uint32_t pk[BKEY / 2];
             float2 ls2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int j = 0; j < HC; j += 2) {
+            for (int j = 0; j < BKEY; j += 2) {
                 const float2 e = __fadd2_rn(make_float2(t[j], t[j + 1]), nm2);
                 const float2 pv = make_float2(ex2(e.x), ex2(e.y));
                 ls2[(j >> 1) & 3] = __fadd2_rn(ls2[(j >> 1) & 3], pv);
@@ -366,12 +352,11 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
             if (i > 0) {
                 // the previous P V product has left P and has been added into O
-                if (!mbar_wait(smem_u32(&ctl->pv_done), (uint32_t)((i - 1) & 1), abort_flag)) { ok = false; continue; }
+                if (!mbar_wait(smem_u32(&ctl->pv_done), (uint32_t)((i - 1) & 1), abort_flag)) { ok = false; break; }
                 tcgen05_fence_after();
-                if (raise) {                                       // warp-uniform; the halves take alternate 16-column chunks
+                if (raise) {                                       // warp-uniform
 #pragma unroll
-                    for (int cc = 0; cc < D / 16; ++cc) {
-                        if ((cc & 1) != half) continue;
+                    for (int cc = 0; cc < SM::DV / 16; ++cc) {
                         uint32_t o[16];
                         tmem_ld16(lane_base + (uint32_t)(O_COL + cc * 16), o);
                         tmem_ld_wait();
@@ -385,20 +370,13 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             // P row -> shared memory, the layout tcgen05.mma reads with the 128-byte swizzle:
             // 16-byte chunk index XOR (row mod 8)
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch)
-                *reinterpret_cast<uint4*>(prow + (((uint32_t)(half * 4 + ch) ^ sw) << 4)) =
+            for (int ch = 0; ch < 8; ++ch)
+                *reinterpret_cast<uint4*>(prow + (((uint32_t)ch ^ sw) << 4)) =
                     make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
             fence_async_smem();
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full));
-        }
-        {
-            // whole-row sum: the two halves swap their partial sums
-            float* xb = ctl->xchg[nblocks & 1];
-            xb[half * BQ + row] = l_sum;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-            l_sum += xb[(half ^ 1) * BQ + row];
         }
         if (ok && mbar_wait(smem_u32(&ctl->pv_done), (uint32_t)((nblocks - 1) & 1), abort_flag)) {
             tcgen05_fence_after();
@@ -406,7 +384,6 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             T* orow = reinterpret_cast<T*>(p.out) + (token0 + row) * (int64_t)C + head * D;
 #pragma unroll
             for (int cc = 0; cc < D / 16; ++cc) {
-                if ((cc & 1) != half) continue;
                 uint32_t o[16];
                 tmem_ld16(lane_base + (uint32_t)(O_COL + cc * 16), o);
                 tmem_ld_wait();
@@ -425,7 +402,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
-    if (warp == 9) {
+    if (warp == 5) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS_AT) : "memory");
     }
@@ -435,30 +412,30 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // V of every (unit, head) as [D, keys] (keys contiguous): the K-major B operand of O += P V.
 // Keys are laid out as [H, key_pitch] (key_pitch = W for images; 16 for windows, the columns
 // W..15 zero) and padded with zeros to a multiple of 64.  One CTA transposes 64 key slots x D
-// values through shared memory.
-template <typename T>
+// values through shared memory; both supported types are 16-bit, so only bits move.
 __global__ void __launch_bounds__(256)
-transpose_v_kernel(const T* __restrict__ qkv, int H, int W, int key_pitch, int vt_len, int heads, int D, T* __restrict__ vt)
+transpose_v_kernel(const uint16_t* __restrict__ qkv, int H, int W, int key_pitch, int vt_len, int heads, int D,
+                   uint16_t* __restrict__ vt)
 {
-    __shared__ T tile[128][BKEY + 2];                               // [dv][key slot], padded against bank conflicts
+    __shared__ uint16_t tile[128][BKEY + 2];                        // [dv][key slot], padded against bank conflicts
     const int s0 = blockIdx.x * BKEY;                               // first key slot of this CTA
     const int bh = blockIdx.y;
     const int head = bh % heads, unit = bh / heads;
     const int C = heads * D;
     const int L = H * W;
     const int chunks = D >> 3;                                      // 16-byte chunks per token
-    const T* src = qkv + (int64_t)unit * L * 3 * C + 2 * C + head * D;
+    const uint16_t* src = qkv + (int64_t)unit * L * 3 * C + 2 * C + head * D;
     for (int idx = threadIdx.x; idx < BKEY * chunks; idx += blockDim.x) {
         const int slot = idx / chunks, ch = idx - slot * chunks;
         const int kh = (s0 + slot) / key_pitch, kw = (s0 + slot) - kh * key_pitch;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (kh < H && kw < W) v = *reinterpret_cast<const uint4*>(src + (int64_t)(kh * W + kw) * 3 * C + ch * 8);
-        const T* e = reinterpret_cast<const T*>(&v);
+        const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
 #pragma unroll
         for (int k = 0; k < 8; ++k) tile[ch * 8 + k][slot] = e[k];
     }
     __syncthreads();
-    T* dst = vt + (int64_t)bh * D * vt_len + s0;
+    uint16_t* dst = vt + (int64_t)bh * D * vt_len + s0;
     for (int idx = threadIdx.x; idx < D * (BKEY / 2); idx += blockDim.x) {
         const int dv = idx / (BKEY / 2), pr = idx - dv * (BKEY / 2);
         *reinterpret_cast<uint32_t*>(dst + (int64_t)dv * vt_len + pr * 2) = *reinterpret_cast<const uint32_t*>(&tile[dv][pr * 2]);
@@ -534,9 +511,8 @@ int attn_transpose_v_dispatch(const void* qkv, int dtype, int64_t units, int H, 
     if (units == 0) return SAMQ_OK;
     const int vt_len = padded_keys(H, W);
     dim3 grid((unsigned)(vt_len / BKEY), (unsigned)(units * heads));
-    // both types are 16-bit: the transpose only moves bits
-    transpose_v_kernel<__half><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(qkv), H, W, W == BKEY ? BKEY : 16, vt_len, heads, head_dim, static_cast<__half*>(vt));
+    transpose_v_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(qkv), H, W, W == BKEY ? BKEY : 16, vt_len, heads, head_dim, static_cast<uint16_t*>(vt));
     SAMQ_CUDA_TRY(cudaGetLastError());
     return SAMQ_OK;
 }

@@ -142,6 +142,9 @@ class Attention(nn.Module):
         # kernel (samq_attn_global): scores and the relative-position bias stay on chip instead of going through
         # a [heads, L, L] bias tensor or augmented q / k rows
         self.fused_global_kernel = True
+        # the same kernel for windows: correct, but one short-lived CTA per (window, head, 128 queries) spends most
+        # of its ~10 us on set-up and pipeline fill, so augmented rows + the library attention stay the default
+        self.tc_windows = False
         self._onehot = {}
         if use_rel_pos:
             assert input_size is not None
@@ -204,7 +207,7 @@ class Attention(nn.Module):
             if self.fused_window_kernel and ops.attn_windowed_supported(H, W, d):
                 return ops.attn_windowed(qkv, B, H, W, nh, self.rel_pos_h, self.rel_pos_w, self.scale,
                                          table=self._rel_table(qkv.dtype, qkv.device))
-            if self.fused_global_kernel and ops.attn_global_supported(H, W, d, qkv.dtype):
+            if self.fused_global_kernel and (W == 64 or self.tc_windows) and ops.attn_global_supported(H, W, d, qkv.dtype):
                 return ops.attn_global(qkv, B, H, W, nh, self.rel_pos_h, self.rel_pos_w, self.scale,
                                        table=self._rel_table(qkv.dtype, qkv.device))
             if d + extra <= 128:

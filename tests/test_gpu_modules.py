@@ -308,11 +308,11 @@ def test_global_attention_kernel_against_fp32_reference(cuda_device, dtype, H, W
         attn.rel_pos_w.normal_(0, 0.3)
         qkv = torch.randn(B * H * W, 3 * dim, device=cuda_device, dtype=dtype)
         qkv[:, :dim] *= 2.0                                        # sharper rows: the running maximum must move
-        attn.fused_global_kernel = True
+        attn.fused_global_kernel = attn.tc_windows = True
         a = attn.attend_flat(qkv, B, H, W)
         torch.cuda.synchronize()
         ops.check_status()
-        attn.fused_global_kernel = False
+        attn.fused_global_kernel = attn.tc_windows = False
         b = attn.attend_flat(qkv, B, H, W)
         # fp32 reference from the 16-bit inputs
         q, k, v = qkv.float().view(B, H * W, 3, nh, d).permute(2, 0, 3, 1, 4)
