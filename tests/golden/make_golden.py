@@ -222,7 +222,9 @@ def encoder_case(ptcg):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <checkout of hchautran/SAM_Quantization>")
+    root = sys.argv[1]
     ptcg, Smooth, H = _import_reference(root)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     np.savez_compressed(os.path.join(HERE, "quantizers.npz"), **quantizer_cases(ptcg))
