@@ -326,7 +326,7 @@ __device__ __forceinline__ uint2 codes_of_vector(const uint4& hv, float2 inv2, f
 }
 
 template <bool SRC_BF16, bool LN, int NV>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, (LN && NV <= 5) ? 4 : 1)
 quant_rows_fast_kernel(const uint16_t* __restrict__ x, int64_t M, int K, int64_t ldx, int rows_per_cta,
                        const int32_t* __restrict__ row_map, const __half* __restrict__ gamma,
                        const __half* __restrict__ beta, float ln_eps, float qmax,
