@@ -118,9 +118,8 @@ def bench_window_attention(windows, H, W, heads, head_dim, dtype=torch.bfloat16,
             "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), "tflops": round(flops / ms / 1e9, 1)}
 
 
-def bench_global_attention(images, H, heads, head_dim, dtype=torch.bfloat16, iters=20, warmup=5):
+def bench_global_attention(images, H, heads, head_dim, dtype=torch.bfloat16, iters=20, warmup=5, W=64):
     dev = torch.device("cuda")
-    W = 64
     L, C = H * W, heads * head_dim
     qkv = [torch.randn((images * L, 3 * C), device=dev, dtype=dtype) for _ in range(2)]
     rh = (torch.randn((2 * H - 1, head_dim), device=dev) * 0.02).to(dtype)
@@ -172,6 +171,7 @@ def main():
     ag = sub.add_parser("attn-global")
     ag.add_argument("--images", type=int, default=8)
     ag.add_argument("--H", type=int, default=64)
+    ag.add_argument("--W", type=int, default=64, help="64 for whole images; up to 16 (with H <= 16) for windows, --images is then the window count")
     ag.add_argument("--heads", type=int, default=16)
     ag.add_argument("--head-dim", dest="head_dim", type=int, default=80)
     ag.add_argument("--iters", type=int, default=20)
@@ -188,7 +188,7 @@ def main():
     elif args.cmd == "attn":
         print(json.dumps(bench_window_attention(args.windows, args.H, args.W, args.heads, args.head_dim, iters=args.iters, warmup=args.warmup)))
     elif args.cmd == "attn-global":
-        print(json.dumps(bench_global_attention(args.images, args.H, args.heads, args.head_dim, iters=args.iters, warmup=args.warmup)))
+        print(json.dumps(bench_global_attention(args.images, args.H, args.heads, args.head_dim, iters=args.iters, warmup=args.warmup, W=args.W)))
     elif args.cmd == "quant":
         print(json.dumps(bench_quant(args.M, args.K, getattr(torch, args.dtype), args.ln, args.gather, args.hadamard,
                                      args.granularity, iters=args.iters, warmup=args.warmup)))
