@@ -335,3 +335,36 @@ def test_global_attention_kernel_against_fp32_reference(cuda_device, dtype, H, W
     assert cosine(a, ref) > 0.9999
     # keeping the bias in fp32 on chip must not be less accurate than rounding it to 16 bits in memory
     assert 1.0 - cosine(a, ref) <= 1.25 * (1.0 - cosine(b, ref)) + 1e-6
+
+
+def test_attention_entry_rejects_bad_arguments(cuda_device):
+    """Argument checks of the tensor-core attention entries: status codes, no kernel launch."""
+    import ctypes
+    from sam_quantization_b200 import _lib, ops
+    lib = _lib.load()
+    dev = cuda_device
+    H, W, nh, d = 2, 64, 1, 80
+    qkv = torch.zeros((H * W, 3 * nh * d), dtype=torch.bfloat16, device=dev)
+    vt = torch.zeros((nh * d, H * W), dtype=torch.bfloat16, device=dev)
+    rel = torch.zeros((nh, H * W, 136), dtype=torch.bfloat16, device=dev)
+    out = torch.zeros((H * W, nh * d), dtype=torch.bfloat16, device=dev)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+
+    def call(H_=H, W_=W, d_=d, pitch=136, dtype=_lib.BF16, qkv_=qkv):
+        return lib.samq_attn_global(P(qkv_), P(vt), P(rel), dtype, 1, pitch, H_, W_, nh, d_, 0.1, P(out), None, None)
+
+    assert call(W_=32) != 0                      # neither an image row of 64 nor a window of at most 16
+    assert call(H_=3) != 0                       # 3 * 64 tokens is not a multiple of the 128-query tile
+    assert call(d_=96) != 0                      # head widths 64 and 80 only
+    assert call(pitch=100) != 0                  # rel_all rows shorter than 2H-1 + 2W-1
+    assert call(dtype=_lib.F32) != 0
+    assert lib.samq_attn_global(None, P(vt), P(rel), _lib.BF16, 1, 136, H, W, nh, d, 0.1, P(out), None, None) != 0
+    assert b"" != lib.samq_last_error_string()
+    assert lib.samq_attn_transpose_v(P(qkv), _lib.BF16, 1, H, 40, nh, d, P(vt), None) != 0   # W = 40: unsupported grid
+    assert lib.samq_attn_global(P(qkv), P(vt), P(rel), _lib.BF16, 0, 136, H, W, nh, d, 0.1, P(out), None, None) == 0  # no units
+    assert not ops.attn_global_supported(64, 64, 96, torch.bfloat16)
+    assert ops.attn_global_supported(14, 14, 80, torch.float16)
+    with pytest.raises(ValueError):
+        ops.set_gemm_pair_mode(7)
+    prev = ops.set_gemm_pair_mode(ops.GEMM_PAIR_AUTO)
+    assert ops.set_gemm_pair_mode(prev) == ops.GEMM_PAIR_AUTO
