@@ -15,8 +15,9 @@
 //   warps 0-3  softmax: thread r owns query row r (= TMEM lane r).  Per key block: load the 64
 //              scores from tensor memory, t = s * scale * log2e + bias, row maximum, p = 2^(t - m),
 //              row sum, P as bf16/fp16 into shared memory in the 128-byte-swizzled operand layout.
-//              The maximum m is only raised when a row's new maximum exceeds it by more than 8
-//              (p stays below 2^8); the output accumulator in tensor memory is then rescaled in place.
+//              A block is one pass with the maximum m in use; only when a row exceeds it by more
+//              than 8 (p stays below 2^8 otherwise) is m raised, the pass repeated from the scores
+//              still in tensor memory, and the output accumulator rescaled in place.
 //   warp 4     TMA producer: Q once, then per block the K rows and the matching V^T columns
 //              (two stages).
 //   warp 5     MMA issuer: S = Q K^T (M128 N64 K=D) into one of two score buffers, and
@@ -282,7 +283,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             rwl[j] = j < p.W ? AtOps<T>::up(rel + rows_h + (qw - j + p.W - 1)) * LOG2E : -INFINITY;
         const float c = p.scale * LOG2E;
         const float2 c2 = make_float2(c, c);
-        float m_used = -INFINITY, l_sum = 0.f;
+        float m_used = 0.f, l_sum = 0.f;             // the first block replaces this provisional maximum
         const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
         uint8_t* prow = p_tile + row * 128;
         const uint32_t sw = (uint32_t)(row & 7);
@@ -291,64 +292,69 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             // rel_h term of the key row(s) of block i: one row for images, four for windows
             // (-inf for rows beyond the window)
             constexpr int NRH = WINDOW ? 4 : 1;
-            float2 rh2[NRH];
+            float rhv[NRH];
 #pragma unroll
             for (int r = 0; r < NRH; ++r) {
                 const int kh = NRH * i + r;
-                const float v = kh < p.H ? AtOps<T>::up(rel + (qh - kh + p.H - 1)) * LOG2E : -INFINITY;
-                rh2[r] = make_float2(v, v);
+                rhv[r] = kh < p.H ? AtOps<T>::up(rel + (qh - kh + p.H - 1)) * LOG2E : -INFINITY;
             }
             if (!mbar_wait(smem_u32(&ctl->s_full[i & 1]), (uint32_t)((i >> 1) & 1), abort_flag)) { ok = false; break; }
             tcgen05_fence_after();
-            uint32_t s0[32], s1[32];
-            tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY), s0);
-            tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY + 32), s1);
-            tmem_ld_wait();
+            // One pass over the block's 64 scores with a given reference maximum:
+            //   e = s * scale * log2e + (rel_h + rel_w) * log2e - m_ref,  p = 2^e,
+            // two columns per instruction; returns max e, leaves P packed in pk and the row sum in `sum`.
+            uint32_t pk[BKEY / 2];
+            auto sweep = [&](float m_ref, float& sum) -> float {
+                uint32_t s0[32], s1[32];
+                tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY), s0);
+                tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY + 32), s1);
+                float2 off[NRH];
+#pragma unroll
+                for (int r = 0; r < NRH; ++r) { const float v = rhv[r] - m_ref; off[r] = make_float2(v, v); }
+                tmem_ld_wait();
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // independent chains
+                float2 ls2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    // column j of the first half and column 32 + j of the second
+                    const float2 w0 = make_float2(rwl[j % NRW], rwl[(j + 1) % NRW]);
+                    const float2 w1 = make_float2(rwl[(32 + j) % NRW], rwl[(33 + j) % NRW]);
+                    const float2 b0 = __fadd2_rn(w0, off[WINDOW ? (j >> 4) : 0]);
+                    const float2 b1 = __fadd2_rn(w1, off[WINDOW ? 2 + (j >> 4) : 0]);
+                    const float2 e0 = __ffma2_rn(make_float2(__uint_as_float(s0[j]), __uint_as_float(s0[j + 1])), c2, b0);
+                    const float2 e1 = __ffma2_rn(make_float2(__uint_as_float(s1[j]), __uint_as_float(s1[j + 1])), c2, b1);
+                    const int a = (j >> 1) & 1;
+                    mx[2 * a] = fmaxf(mx[2 * a], fmaxf(e0.x, e0.y));
+                    mx[2 * a + 1] = fmaxf(mx[2 * a + 1], fmaxf(e1.x, e1.y));
+                    const float2 p0 = make_float2(ex2(e0.x), ex2(e0.y));
+                    const float2 p1 = make_float2(ex2(e1.x), ex2(e1.y));
+                    ls2[2 * a] = __fadd2_rn(ls2[2 * a], p0);
+                    ls2[2 * a + 1] = __fadd2_rn(ls2[2 * a + 1], p1);
+                    pk[j >> 1] = AtOps<T>::pack(p0.x, p0.y);
+                    pk[16 + (j >> 1)] = AtOps<T>::pack(p1.x, p1.y);
+                }
+                const float2 a2 = __fadd2_rn(__fadd2_rn(ls2[0], ls2[1]), __fadd2_rn(ls2[2], ls2[3]));
+                sum = a2.x + a2.y;
+                return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            };
+            // Optimistic pass with the maximum in use.  Only when some row of the warp exceeds it by
+            // more than 8 (p would pass 2^8), and on the first block, the maximum is raised and the
+            // pass repeated from the scores still in tensor memory.
+            float bsum;
+            const float e_max = sweep(m_used, bsum);
+            const bool raise = __any_sync(0xffffffffu, i == 0 || e_max > 8.0f);
+            float alpha = 1.0f;
+            if (raise) {                                           // warp-uniform
+                const float m_new = (i == 0) ? m_used + e_max : m_used + fmaxf(e_max, 0.f);
+                alpha = (i == 0) ? 0.f : ex2(m_used - m_new);     // nothing has been accumulated before the first block
+                m_used = m_new;
+                (void)sweep(m_used, bsum);
+                l_sum *= alpha;
+            }
+            l_sum += bsum;
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[i & 1]));   // the score buffer may be overwritten
-
-            // t = s * scale * log2e + (rel_h + rel_w) * log2e, two columns per instruction
-            float t[BKEY];
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // independent chains
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-                // column j of the first half and column 32 + j of the second
-                const float2 w0 = make_float2(rwl[j % NRW], rwl[(j + 1) % NRW]);
-                const float2 w1 = make_float2(rwl[(32 + j) % NRW], rwl[(33 + j) % NRW]);
-                const float2 b0 = __fadd2_rn(w0, rh2[WINDOW ? (j >> 4) : 0]);
-                const float2 b1 = __fadd2_rn(w1, rh2[WINDOW ? 2 + (j >> 4) : 0]);
-                const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(s0[j]), __uint_as_float(s0[j + 1])), c2, b0);
-                const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(s1[j]), __uint_as_float(s1[j + 1])), c2, b1);
-                t[j] = t0.x; t[j + 1] = t0.y; t[32 + j] = t1.x; t[32 + j + 1] = t1.y;
-                const int a = (j >> 1) & 1;
-                mx[2 * a] = fmaxf(mx[2 * a], fmaxf(t0.x, t0.y));
-                mx[2 * a + 1] = fmaxf(mx[2 * a + 1], fmaxf(t1.x, t1.y));
-            }
-            const float mi = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            // raise the running maximum only when some row of the warp needs it
-            const bool raise = __any_sync(0xffffffffu, mi > m_used + 8.0f);
-            float alpha = 1.0f;
-            if (raise) {
-                const float m_new = fmaxf(m_used, mi);
-                alpha = ex2(m_used - m_new);                       // 0 on the first block (m_used = -inf)
-                m_used = m_new;
-                l_sum *= alpha;
-            }
-            const float2 nm2 = make_float2(-m_used, -m_used);
-            uint32_t pk[BKEY / 2];
-            float2 ls2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-            for (int j = 0; j < BKEY; j += 2) {
-                const float2 e = __fadd2_rn(make_float2(t[j], t[j + 1]), nm2);
-                const float2 pv = make_float2(ex2(e.x), ex2(e.y));
-                ls2[(j >> 1) & 3] = __fadd2_rn(ls2[(j >> 1) & 3], pv);
-                pk[j >> 1] = AtOps<T>::pack(pv.x, pv.y);
-            }
-            {
-                const float2 a = __fadd2_rn(__fadd2_rn(ls2[0], ls2[1]), __fadd2_rn(ls2[2], ls2[3]));
-                l_sum += a.x + a.y;
-            }
 
             if (i > 0) {
                 // the previous P V product has left P and has been added into O
