@@ -899,6 +899,103 @@ hadamard_quant_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx,
 }
 
 // ---------------------------------------------------------------------------
+// The 4096-point transform on its own (ViT-L `lin2` input): fp16 arithmetic, codes only.
+// Same arithmetic and stage order as hadamard_quant_kernel, with every address a compile-time
+// constant: 256 threads per row, thread t owns elements [16t, 16t + 16) for the first four
+// stages (registers), elements differing in index bits 4..7 for the next four (their owners sit
+// in the same half-warp: a warp barrier), bits 8..11 for the last four (CTA barrier); the
+// division by sqrt(4096) = 64 is an exact scaling.  Shared-memory slot of element i: i + i / 16.
+// ---------------------------------------------------------------------------
+template <typename SrcT>
+__global__ void __launch_bounds__(256, 6)
+hadamard4096_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, const int32_t* __restrict__ row_map,
+                          const int8_t* __restrict__ signs, float qmax,
+                          int8_t* __restrict__ q_out, float* __restrict__ scale_out)
+{
+    constexpr int K = 4096;
+    __shared__ float sm[K + K / 16 + 8];
+    __shared__ float red[8];
+    const int t = threadIdx.x;
+    const int64_t row = blockIdx.x;
+    const int64_t src = row_map != nullptr ? (int64_t)row_map[row] : row;
+    float v[16];
+    if (src >= 0) {
+        const SrcT* xr = x + src * ldx + 16 * t;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float f[8];
+            unpack<SrcT>(ld_stream(xr + i * 8), f);
+            if (!std::is_same<SrcT, __half>::value) RoundVec<__half, 8>::run(f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[i * 8 + e] = f[e];
+        }
+        if (signs != nullptr) {
+            const uint4 sg = *reinterpret_cast<const uint4*>(signs + 16 * t);
+            const uint32_t w[4] = {sg.x, sg.y, sg.z, sg.w};
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if ((w[j >> 2] >> (8 * (j & 3))) & 0x80u) v[j] = -v[j];
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+    }
+    butterfly16(v);                                        // index bits 0..3
+#pragma unroll
+    for (int j = 0; j < 16; ++j) sm[17 * t + j] = v[j];
+    __syncwarp();
+    {                                                      // index bits 4..7: elements b + 16 j, b = 256 (t / 16) + t % 16
+        float* s = sm + (t >> 4) * 272 + (t & 15);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = s[17 * j];
+        butterfly16(v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) s[17 * j] = v[j];
+    }
+    __syncthreads();
+    float m = 0.f;
+    {                                                      // index bits 8..11: elements t + 256 j
+        float* s = sm + t + (t >> 4);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = s[272 * j];
+        butterfly16(v);
+        // divide by sqrt(4096) (exact), round once to fp16, track the absolute maximum
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+            const __half2 h = __floats2half2_rn(v[j] * 0.015625f, v[j + 1] * 0.015625f);
+            const __half2 a = __habs2(h);
+            m = fmaxf(m, fmaxf(__low2float(a), __high2float(a)));
+            const float2 f = __half22float2(h);
+            s[272 * j] = f.x;
+            s[272 * (j + 1)] = f.y;
+        }
+    }
+    m = warp_max(m);
+    if ((t & 31) == 0) red[t >> 5] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), fmaxf(fmaxf(red[4], red[5]), fmaxf(red[6], red[7])));
+    const float sc = scale_from_absmax<__half>(m, qmax);
+    if (t == 0 && scale_out != nullptr) scale_out[row] = sc;
+    const float inv = __frcp_rn(sc);
+    const float2 inv2 = make_float2(inv, inv), ns2 = make_float2(-sc, -sc);
+    const __half2 hi2 = __float2half2_rn(qmax), lo2 = __float2half2_rn(-qmax), magic = __float2half2_rn(1536.0f);
+    uint32_t hb[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {                          // this thread's 16 consecutive elements again
+        const float2 f = make_float2(sm[17 * t + 2 * j], sm[17 * t + 2 * j + 1]);
+        const float2 y0 = __fmul2_rn(f, inv2);
+        const float2 e = __ffma2_rn(y0, ns2, f);
+        const float2 y = __ffma2_rn(e, inv2, y0);
+        __half2 h = __floats2half2_rn(y.x, y.y);
+        h = __hadd2(__hmin2(__hmax2(h, lo2), hi2), magic);
+        hb[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(q_out + row * K + 16 * t) =
+        make_uint4(__byte_perm(hb[0], hb[1], 0x6420), __byte_perm(hb[2], hb[3], 0x6420),
+                   __byte_perm(hb[4], hb[5], 0x6420), __byte_perm(hb[6], hb[7], 0x6420));
+}
+
+// ---------------------------------------------------------------------------
 // Host launchers
 // ---------------------------------------------------------------------------
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -1062,6 +1159,15 @@ static int quant_typed(const SrcT* x, int64_t M, int K, int64_t ldx, const Prolo
             hadamard_quant_kernel<T, SrcT, HKV><<<(unsigned)M, threads, smem, st>>>(x, M, K, ldx, pro.row_map, divisor, \
                 had->signs, inner, axis, hk, log2_pow, had->hadk, qmax, q, scale, fq, tx, vec);                         \
         } while (0)
+        if constexpr (std::is_same<T, __half>::value) {
+            // the 4096-point transform with codes only has a kernel of its own
+            if (had->mode == SAMQ_HAD_FULL && hk == 1 && K == 4096 && vec && divisor == nullptr && fq == nullptr &&
+                tx == nullptr && q != nullptr) {
+                hadamard4096_quant_kernel<SrcT><<<(unsigned)M, 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, qmax, q, scale);
+                SAMQ_CUDA_TRY(cudaGetLastError());
+                return SAMQ_OK;
+            }
+        }
         if (hk == 1) SAMQ_HAD(1);
         else if (hk == 12) SAMQ_HAD(12);
         else if (hk == 20) SAMQ_HAD(20);

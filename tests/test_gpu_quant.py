@@ -348,3 +348,37 @@ def test_lean_kernel_layernorm(cuda_device, K):
         plain = ops.quantize(ln, 0)
         dq = (out["q"].int() - plain["q"].int()).abs()
         assert int(dq.max()) <= 1 and float((dq > 0).float().mean()) < 2e-3
+
+
+@pytest.mark.parametrize("with_signs", [False, True])
+def test_hadamard_4096_kernel_matches_general_kernel(cuda_device, with_signs):
+    """The kernel specialised for the 4096-point transform (codes only) against the general
+    Hadamard kernel (any extra output selects it) and against the oracle, bit for bit; with a
+    row gather, padding rows and a bf16-stored source."""
+    from sam_quantization_b200 import ops
+    rng = np.random.default_rng(4096 + int(with_signs))
+    x_np = O.rnd(rng.standard_normal((45, 4096)).astype(np.float32) * 3, "f16")
+    x_np[:, rng.permutation(4096)[:40]] *= 20
+    x_np[3] = 0
+    x_np[4] *= 1e-4
+    x = to_dev(x_np, "f16", cuda_device)
+    signs = None
+    if with_signs:
+        signs = torch.from_numpy(rng.choice([-1, 1], size=4096).astype(np.int8)).to(cuda_device)
+    had = ops.Hadamard("full", signs=signs)
+    fast = ops.quantize(x, 0, hadamard=had)
+    general = ops.quantize(x, 0, hadamard=had, transformed=True)
+    assert torch.equal(fast["q"], general["q"]) and torch.equal(fast["scale"], general["scale"])
+    if not with_signs:
+        tx = O.hadamard_full_online(x_np, "f16")
+        q, s, _ = O.quantize(tx, "per_token", "f16")
+        assert np.array_equal(fast["q"].cpu().numpy(), O.saturate_codes(q))
+        assert np.array_equal(f32(fast["scale"]), np.asarray(s, np.float32))
+    rm = torch.tensor([44, -1, 0, 4, 4, 3, -1, 17], dtype=torch.int32, device=cuda_device)
+    a = ops.quantize(x, 0, hadamard=had, row_map=rm)
+    b = ops.quantize(x, 0, hadamard=had, row_map=rm, transformed=True)
+    assert torch.equal(a["q"], b["q"]) and torch.equal(a["scale"], b["scale"]) and int(a["q"][1].abs().max()) == 0
+    xb = x.to(torch.bfloat16)
+    a = ops.quantize(xb, 0, hadamard=had, as_dtype=torch.float16)
+    b = ops.quantize(xb, 0, hadamard=had, as_dtype=torch.float16, transformed=True)
+    assert torch.equal(a["q"], b["q"]) and torch.equal(a["scale"], b["scale"])
