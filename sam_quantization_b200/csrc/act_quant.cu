@@ -996,6 +996,72 @@ hadamard4096_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, co
 }
 
 // ---------------------------------------------------------------------------
+// The transform across 16 heads on its own (`proj` input of the QuaRot configs with 16 heads):
+// fp16 arithmetic, codes only, no shared memory.  A thread owns 8 consecutive positions of the
+// head width for ALL 16 heads: sixteen 16-byte loads in flight, then for every position one
+// 16-point butterfly over the heads in registers (stage order 1, 2, 4, 8 as everywhere), the exact
+// scaling by 1 / sqrt(16), one rounding to fp16.  LPR lanes share a row (8 or 16, the next power of
+// two at or above had_dim / 8), so the row maximum is a few shuffles.
+// ---------------------------------------------------------------------------
+template <typename SrcT, int LPR>
+__global__ void __launch_bounds__(256)
+hadamard_heads16_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, const int32_t* __restrict__ row_map,
+                              int had_dim, float qmax, int8_t* __restrict__ q_out, float* __restrict__ scale_out)
+{
+    constexpr int RPW = 32 / LPR;                              // rows per warp
+    const int lane = threadIdx.x & 31;
+    const int c = lane % LPR;                                  // 16-byte chunk of the head width
+    const int64_t row = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW + lane / LPR;
+    const int K = 16 * had_dim;
+    const bool active = row < M && c * 8 < had_dim;
+    int64_t src = -1;
+    if (active) src = row_map != nullptr ? (int64_t)row_map[row] : row;
+    uint4 raw[16];                                             // [head] -> 8 fp16 values
+#pragma unroll
+    for (int h = 0; h < 16; ++h)
+        raw[h] = src >= 0 ? ld_stream(x + src * ldx + h * had_dim + c * 8) : make_uint4(0, 0, 0, 0);
+    if (!std::is_same<SrcT, __half>::value) {
+#pragma unroll
+        for (int h = 0; h < 16; ++h) {
+            float f[8];
+            unpack<SrcT>(raw[h], f);
+            raw[h] = pack<__half>(f);                          // the cast to fp16 the model applies
+        }
+    }
+    float m = 0.f;
+#pragma unroll
+    for (int pr = 0; pr < 4; ++pr) {                           // two positions at a time
+        float va[16], vb[16];
+#pragma unroll
+        for (int h = 0; h < 16; ++h) {
+            const float2 f = __half22float2(reinterpret_cast<const __half2*>(&raw[h])[pr]);
+            va[h] = f.x; vb[h] = f.y;
+        }
+        butterfly16(va);
+        butterfly16(vb);
+#pragma unroll
+        for (int h = 0; h < 16; ++h) {
+            const __half2 hh = __floats2half2_rn(va[h] * 0.25f, vb[h] * 0.25f);
+            const __half2 a = __habs2(hh);
+            m = fmaxf(m, fmaxf(__low2float(a), __high2float(a)));
+            reinterpret_cast<__half2*>(&raw[h])[pr] = hh;
+        }
+    }
+#pragma unroll
+    for (int o = LPR >> 1; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (!active) return;
+    const float sc = scale_from_absmax<__half>(m, qmax);
+    if (c == 0 && scale_out != nullptr) scale_out[row] = sc;
+    const float inv = __frcp_rn(sc);
+    const float2 inv2 = make_float2(inv, inv), ns2 = make_float2(-sc, -sc);
+    const __half2 hi2 = __float2half2_rn(qmax), lo2 = __float2half2_rn(-qmax);
+    int8_t* qr = q_out + row * K + c * 8;
+#pragma unroll
+    for (int h = 0; h < 16; ++h)
+        *reinterpret_cast<uint2*>(qr + h * had_dim) = codes_of_vector<true>(raw[h], inv2, ns2, lo2, hi2);
+}
+
+// ---------------------------------------------------------------------------
 // Host launchers
 // ---------------------------------------------------------------------------
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -1164,6 +1230,21 @@ static int quant_typed(const SrcT* x, int64_t M, int K, int64_t ldx, const Prolo
             if (had->mode == SAMQ_HAD_FULL && hk == 1 && K == 4096 && vec && divisor == nullptr && fq == nullptr &&
                 tx == nullptr && q != nullptr) {
                 hadamard4096_quant_kernel<SrcT><<<(unsigned)M, 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, qmax, q, scale);
+                SAMQ_CUDA_TRY(cudaGetLastError());
+                return SAMQ_OK;
+            }
+        }
+        if constexpr (std::is_same<T, __half>::value) {
+            // so has the transform across 16 heads
+            if (had->mode == SAMQ_HAD_PARTIAL && hk == 1 && axis == 16 && (inner & 7) == 0 && inner <= 128 && vec &&
+                had->signs == nullptr && divisor == nullptr && fq == nullptr && tx == nullptr && q != nullptr) {
+                if (inner <= 64) {
+                    const unsigned grid = (unsigned)((M + 31) / 32);                 // 8 warps x 4 rows
+                    hadamard_heads16_quant_kernel<SrcT, 8><<<grid, 256, 0, st>>>(x, M, ldx, pro.row_map, inner, qmax, q, scale);
+                } else {
+                    const unsigned grid = (unsigned)((M + 15) / 16);                 // 8 warps x 2 rows
+                    hadamard_heads16_quant_kernel<SrcT, 16><<<grid, 256, 0, st>>>(x, M, ldx, pro.row_map, inner, qmax, q, scale);
+                }
                 SAMQ_CUDA_TRY(cudaGetLastError());
                 return SAMQ_OK;
             }

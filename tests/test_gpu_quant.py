@@ -382,3 +382,33 @@ def test_hadamard_4096_kernel_matches_general_kernel(cuda_device, with_signs):
     a = ops.quantize(xb, 0, hadamard=had, as_dtype=torch.float16)
     b = ops.quantize(xb, 0, hadamard=had, as_dtype=torch.float16, transformed=True)
     assert torch.equal(a["q"], b["q"]) and torch.equal(a["scale"], b["scale"])
+
+
+@pytest.mark.parametrize("had_dim", [64, 80, 8, 128])
+def test_hadamard_across_16_heads_kernel_matches_general_kernel(cuda_device, had_dim):
+    """The register-only kernel for the transform across 16 heads (codes only) against the general
+    Hadamard kernel, bit for bit; ragged row counts, a row gather with padding rows, a bf16 source."""
+    from sam_quantization_b200 import ops
+    K = 16 * had_dim
+    rng = np.random.default_rng(had_dim)
+    x_np = O.rnd(rng.standard_normal((67, K)).astype(np.float32) * 2, "f16")
+    x_np[:, rng.permutation(K)[: max(1, K // 100)]] *= 20
+    x_np[3] = 0
+    x_np[4] *= 1e-4
+    x = to_dev(x_np, "f16", cuda_device)
+    had = ops.Hadamard("partial", had_dim=had_dim)
+    fast = ops.quantize(x, 0, hadamard=had)
+    general = ops.quantize(x, 0, hadamard=had, transformed=True)
+    assert torch.equal(fast["q"], general["q"]) and torch.equal(fast["scale"], general["scale"])
+    tx = O.hadamard_partial_online(x_np, had_dim, "f16")
+    q, s, _ = O.quantize(tx, "per_token", "f16")
+    assert np.array_equal(fast["q"].cpu().numpy(), O.saturate_codes(q))
+    assert np.array_equal(f32(fast["scale"]), np.asarray(s, np.float32))
+    rm = torch.tensor([66, -1, 0, 4, 4, 3, -1, 17, 25], dtype=torch.int32, device=cuda_device)
+    a = ops.quantize(x, 0, hadamard=had, row_map=rm)
+    b = ops.quantize(x, 0, hadamard=had, row_map=rm, transformed=True)
+    assert torch.equal(a["q"], b["q"]) and torch.equal(a["scale"], b["scale"]) and int(a["q"][1].abs().max()) == 0
+    xb = x.to(torch.bfloat16)
+    a = ops.quantize(xb, 0, hadamard=had, as_dtype=torch.float16, row_map=rm)
+    b = ops.quantize(xb, 0, hadamard=had, as_dtype=torch.float16, row_map=rm, transformed=True)
+    assert torch.equal(a["q"], b["q"]) and torch.equal(a["scale"], b["scale"])
