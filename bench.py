@@ -108,12 +108,32 @@ def build_float_encoder(model_type: str, device, dtype, seed: int = 4):
                          attn_dtype=torch.bfloat16 if dtype == torch.float16 else None)
 
 
-def build_quantized_encoder(model_type: str, device, calib_images: int = 8):
-    """ViT encoder, SmoothQuant (alpha 0.5) from `calib_images` synthetic calibration images run
-    through the float model, then W8A8 on every linear (per-channel weights, per-token acts)."""
+RECIPES = {"smoothquant": "SmoothQuant", "rtn": "RTN", "quarot": "QuaRot"}
+
+
+def build_quantized_encoder(model_type: str, device, calib_images: int = 8, recipe: str = "smoothquant"):
+    """ViT encoder with W8A8 on every linear (per-channel weights, per-token activations).
+    smoothquant: SmoothQuant (alpha 0.5) from `calib_images` synthetic calibration images run through
+    the float model first; rtn: nothing first; quarot: `rotate_sam` (residual-stream Hadamard folded
+    into the weights, online Hadamard before lin2 and across the heads before proj)."""
     from sam_quantization_b200.RTN_quantization import (W8A8Linear, get_act_scales_sam,
                                                         replace_linear_with_target_and_quantize, smooth_sam)
     model = build_float_encoder(model_type, device, torch.float16)
+    if recipe == "quarot":
+        import types
+        from sam_quantization_b200.quarot import rotate_sam
+        enc = model.image_encoder
+        dim, heads = enc.blocks[0].attn.qkv.in_features, enc.blocks[0].attn.num_heads
+        rot = types.SimpleNamespace(hidden_size_image_en=dim, num_attention_head_image_en=heads, hidden_size_mask_de=256,
+                                    num_attention_head_mask_de=8, rotate_mode="hadamard", device=str(device), seed=123,
+                                    fp32_had=True)
+        cfg = types.SimpleNamespace(n_bits=8, weight_quant="per_channel", act_quant="per_token", group_size=None,
+                                    quantize_output=False, quantize_input=True)
+        rotate_sam(model, rot, cfg)
+        return model
+    if recipe == "rtn":
+        replace_linear_with_target_and_quantize(model, W8A8Linear, 8, [], weight_quant="per_channel", act_quant="per_token")
+        return model
     calib = (synthetic_images(1, 200 + i).to(device) for i in range(calib_images))
     with torch.no_grad():
         scales = get_act_scales_sam(model, calib, num_samples=calib_images)
@@ -205,7 +225,7 @@ def run_ours(args):
         chunk -= 1
 
     from sam_quantization_b200.engine import EncoderRunner
-    model = build_quantized_encoder(args.model, dev)
+    model = build_quantized_encoder(args.model, dev, recipe=args.recipe)
     enc = EncoderRunner(model, chunk, device=dev, use_graph=not args.no_graph)
 
     # this rank's shard of the global batch: images [rank*local_n, (rank+1)*local_n), seeded per image
@@ -293,7 +313,7 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": f"SAM {args.model} encoder W8A8 SmoothQuant, 1024x1024, global batch {GLOBAL_BATCH}"
+            "config": {"workload": f"SAM {args.model} encoder W8A8 {RECIPES[args.recipe]}, 1024x1024, global batch {GLOBAL_BATCH}"
                                    f" sharded by image, {chunk} images per forward",
                        "l2": "inputs and activations per forward exceed the 126 MB L2", "parallelism": f"dp{world}",
                        "cuda_graph": not args.no_graph},
@@ -328,6 +348,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="vit_h", choices=list(ENC))
+    ap.add_argument("--recipe", default="smoothquant", choices=list(RECIPES),
+                    help="what precedes W8A8 (the headline configuration is vit_h + smoothquant)")
     ap.add_argument("--chunk", type=int, default=8, help="images per encoder forward")
     ap.add_argument("--ref-budget", dest="ref_budget", type=float, default=25.0, help="seconds of CPU work per reference sample")
     ap.add_argument("--no-cpu-baseline", dest="no_cpu_baseline", action="store_true")

@@ -899,25 +899,35 @@ hadamard_quant_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx,
 }
 
 // ---------------------------------------------------------------------------
-// The 4096-point transform on its own (ViT-L `lin2` input): fp16 arithmetic, codes only.
-// Same arithmetic and stage order as hadamard_quant_kernel, with every address a compile-time
-// constant: 256 threads per row, thread t owns elements [16t, 16t + 16) for the first four
-// stages (registers), elements differing in index bits 4..7 for the next four (their owners sit
-// in the same half-warp: a warp barrier), bits 8..11 for the last four (CTA barrier); the
-// division by sqrt(4096) = 64 is an exact scaling.  Shared-memory slot of element i: i + i / 16.
+// The 1024- and 4096-point transforms on their own (ViT-L `qkv` / `lin1` / `lin2` inputs): fp16
+// arithmetic, codes only.  Same arithmetic and stage order as hadamard_quant_kernel, with every
+// address a compile-time constant: K / 16 threads per row (a CTA of 256 threads holds 256 * 16 / K
+// rows), thread t of a row owns elements [16t, 16t + 16) for the first four stages (registers),
+// elements differing in index bits 4..7 for the next four (their owners sit in the same half-warp:
+// a warp barrier), index bits 8 and up for the rest (CTA barrier); the division by sqrt(K) (32 or
+// 64) is an exact scaling.  Shared-memory slot of element i of a row: i + i / 16.
 // ---------------------------------------------------------------------------
-template <typename SrcT>
+template <typename SrcT, int K>
 __global__ void __launch_bounds__(256, 6)
-hadamard4096_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, const int32_t* __restrict__ row_map,
-                          const int8_t* __restrict__ signs, float qmax,
-                          int8_t* __restrict__ q_out, float* __restrict__ scale_out)
+hadamard_pow4_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, const int32_t* __restrict__ row_map,
+                           const int8_t* __restrict__ signs, float qmax,
+                           int8_t* __restrict__ q_out, float* __restrict__ scale_out)
 {
-    constexpr int K = 4096;
-    __shared__ float sm[K + K / 16 + 8];
+    static_assert(K == 1024 || K == 4096, "lengths whose square root is a power of two");
+    constexpr int NT = K / 16;                                 // threads per row
+    constexpr int ROWS = 256 / NT;                             // rows per CTA
+    constexpr int R = K / 256;                                 // points of the last pass: 4 or 16
+    constexpr int PITCH = K + K / 16 + 8;
+    constexpr float INV_ROOT = K == 4096 ? 0.015625f : 0.03125f;
+    __shared__ float sm_all[ROWS * PITCH];
     __shared__ float red[8];
-    const int t = threadIdx.x;
-    const int64_t row = blockIdx.x;
-    const int64_t src = row_map != nullptr ? (int64_t)row_map[row] : row;
+    const int r_in = threadIdx.x / NT;                         // row inside the CTA
+    const int t = threadIdx.x - r_in * NT;                     // thread inside the row
+    float* sm = sm_all + r_in * PITCH;
+    const int64_t row = (int64_t)blockIdx.x * ROWS + r_in;
+    const bool active = row < M;
+    int64_t src = -1;
+    if (active) src = row_map != nullptr ? (int64_t)row_map[row] : row;
     float v[16];
     if (src >= 0) {
         const SrcT* xr = x + src * ldx + 16 * t;
@@ -954,26 +964,47 @@ hadamard4096_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, co
     }
     __syncthreads();
     float m = 0.f;
-    {                                                      // index bits 8..11: elements t + 256 j
-        float* s = sm + t + (t >> 4);
+    {
+        // index bits 8 and up: R-point transforms over elements g + 256 j; a thread takes the 16 / R
+        // groups g = t + NT u.  With v[u R + j] the butterflies act on the low bits of the register index.
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = s[272 * j];
-        butterfly16(v);
-        // divide by sqrt(4096) (exact), round once to fp16, track the absolute maximum
+        for (int u = 0; u < 16 / R; ++u)
 #pragma unroll
-        for (int j = 0; j < 16; j += 2) {
-            const __half2 h = __floats2half2_rn(v[j] * 0.015625f, v[j + 1] * 0.015625f);
+            for (int j = 0; j < R; ++j) v[u * R + j] = sm[t + NT * u + ((t + NT * u) >> 4) + 272 * j];
+        if (R == 16) {
+            butterfly16(v);
+        } else {
+#pragma unroll
+            for (int s = 1; s < R; s <<= 1)
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if ((j & s) == 0) { const float a = v[j], c = v[j | s]; v[j] = a + c; v[j | s] = a - c; }
+        }
+        // divide by sqrt(K) (exact), round once to fp16, track the absolute maximum
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+            const __half2 h = __floats2half2_rn(v[i] * INV_ROOT, v[i + 1] * INV_ROOT);
             const __half2 a = __habs2(h);
             m = fmaxf(m, fmaxf(__low2float(a), __high2float(a)));
             const float2 f = __half22float2(h);
-            s[272 * j] = f.x;
-            s[272 * (j + 1)] = f.y;
+            v[i] = f.x; v[i + 1] = f.y;
         }
+#pragma unroll
+        for (int u = 0; u < 16 / R; ++u)
+#pragma unroll
+            for (int j = 0; j < R; ++j) sm[t + NT * u + ((t + NT * u) >> 4) + 272 * j] = v[u * R + j];
     }
     m = warp_max(m);
-    if ((t & 31) == 0) red[t >> 5] = m;
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
     __syncthreads();
-    m = fmaxf(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), fmaxf(fmaxf(red[4], red[5]), fmaxf(red[6], red[7])));
+    {
+        constexpr int WPR = NT / 32;                           // warps per row
+        float t2 = 0.f;
+#pragma unroll
+        for (int w = 0; w < WPR; ++w) t2 = fmaxf(t2, red[r_in * WPR + w]);
+        m = t2;
+    }
+    if (!active) return;
     const float sc = scale_from_absmax<__half>(m, qmax);
     if (t == 0 && scale_out != nullptr) scale_out[row] = sc;
     const float inv = __frcp_rn(sc);
@@ -1226,10 +1257,13 @@ static int quant_typed(const SrcT* x, int64_t M, int K, int64_t ldx, const Prolo
                 had->signs, inner, axis, hk, log2_pow, had->hadk, qmax, q, scale, fq, tx, vec);                         \
         } while (0)
         if constexpr (std::is_same<T, __half>::value) {
-            // the 4096-point transform with codes only has a kernel of its own
-            if (had->mode == SAMQ_HAD_FULL && hk == 1 && K == 4096 && vec && divisor == nullptr && fq == nullptr &&
+            // the 1024- and 4096-point transforms with codes only have a kernel of their own
+            if (had->mode == SAMQ_HAD_FULL && hk == 1 && (K == 4096 || K == 1024) && vec && divisor == nullptr && fq == nullptr &&
                 tx == nullptr && q != nullptr) {
-                hadamard4096_quant_kernel<SrcT><<<(unsigned)M, 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, qmax, q, scale);
+                if (K == 4096)
+                    hadamard_pow4_quant_kernel<SrcT, 4096><<<(unsigned)M, 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, qmax, q, scale);
+                else
+                    hadamard_pow4_quant_kernel<SrcT, 1024><<<(unsigned)((M + 3) / 4), 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, qmax, q, scale);
                 SAMQ_CUDA_TRY(cudaGetLastError());
                 return SAMQ_OK;
             }

@@ -350,21 +350,22 @@ def test_lean_kernel_layernorm(cuda_device, K):
         assert int(dq.max()) <= 1 and float((dq > 0).float().mean()) < 2e-3
 
 
+@pytest.mark.parametrize("n", [4096, 1024])
 @pytest.mark.parametrize("with_signs", [False, True])
-def test_hadamard_4096_kernel_matches_general_kernel(cuda_device, with_signs):
+def test_hadamard_4096_kernel_matches_general_kernel(cuda_device, with_signs, n):
     """The kernel specialised for the 4096-point transform (codes only) against the general
     Hadamard kernel (any extra output selects it) and against the oracle, bit for bit; with a
     row gather, padding rows and a bf16-stored source."""
     from sam_quantization_b200 import ops
-    rng = np.random.default_rng(4096 + int(with_signs))
-    x_np = O.rnd(rng.standard_normal((45, 4096)).astype(np.float32) * 3, "f16")
-    x_np[:, rng.permutation(4096)[:40]] *= 20
+    rng = np.random.default_rng(n + int(with_signs))
+    x_np = O.rnd(rng.standard_normal((45, n)).astype(np.float32) * 3, "f16")
+    x_np[:, rng.permutation(n)[:n // 100]] *= 20
     x_np[3] = 0
     x_np[4] *= 1e-4
     x = to_dev(x_np, "f16", cuda_device)
     signs = None
     if with_signs:
-        signs = torch.from_numpy(rng.choice([-1, 1], size=4096).astype(np.int8)).to(cuda_device)
+        signs = torch.from_numpy(rng.choice([-1, 1], size=n).astype(np.int8)).to(cuda_device)
     had = ops.Hadamard("full", signs=signs)
     fast = ops.quantize(x, 0, hadamard=had)
     general = ops.quantize(x, 0, hadamard=had, transformed=True)
