@@ -1,7 +1,8 @@
 """Builds libsamq.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
 
 Run as ``python -m sam_quantization_b200.build``.  nvcc cross-compiles, so no GPU is
-needed to build.  The library is rebuilt only when a source is newer than the binary.
+needed to build.  Each source is compiled to its own object (in parallel, and only when it or a
+header changed); the objects are then linked into the shared library.
 """
 from __future__ import annotations
 
@@ -9,17 +10,22 @@ import os
 import shutil
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
+OBJ_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libsamq.so")
-SOURCES = ["abi.cu", "act_quant.cu", "gemm_i8.cu", "gemm_i8_pair.cu", "gemm_i8_grouped.cu", "attn_prep.cu", "attn_window.cu", "attn_global.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-lineinfo", "-std=c++17",
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
 ]
+
+
+def sources() -> list:
+    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
 def _nvcc() -> str:
@@ -29,29 +35,44 @@ def _nvcc() -> str:
     return exe
 
 
-def _stale() -> bool:
-    if not os.path.exists(LIB_PATH):
-        return True
-    t = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
+def _headers_mtime() -> float:
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     deps.append(os.path.join(PKG_DIR, "..", "include", "samq.h"))
-    return any(os.path.getmtime(d) > t for d in deps)
+    return max(os.path.getmtime(d) for d in deps)
+
+
+def _compile(src: str, verbose: bool) -> str:
+    obj = os.path.join(OBJ_DIR, src[:-3] + ".o")
+    cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed on {src}:\n" + res.stdout + res.stderr)
+    return res.stderr
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
     """Compile csrc/*.cu into sam_quantization_b200/libsamq.so and return its path."""
-    if not force and not _stale():
-        return LIB_PATH
-    cmd = [_nvcc(), *NVCC_FLAGS]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(CSRC, s) for s in SOURCES]
-    cmd += ["-o", LIB_PATH]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    if verbose:
-        sys.stderr.write(res.stderr)
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    hdr = _headers_mtime()
+    todo = []
+    for src in sources():
+        obj = os.path.join(OBJ_DIR, src[:-3] + ".o")
+        newest = max(hdr, os.path.getmtime(os.path.join(CSRC, src)))
+        if force or not os.path.exists(obj) or os.path.getmtime(obj) < newest:
+            todo.append(src)
+    if todo:
+        with ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 1)) as pool:
+            for src, log in zip(todo, pool.map(lambda s: _compile(s, verbose), todo)):
+                if verbose:
+                    sys.stderr.write(f"==== {src}\n{log}")
+    objs = [os.path.join(OBJ_DIR, s[:-3] + ".o") for s in sources()]
+    if todo or not os.path.exists(LIB_PATH) or any(os.path.getmtime(o) > os.path.getmtime(LIB_PATH) for o in objs):
+        res = subprocess.run([_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", *objs, "-o", LIB_PATH],
+                             capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("link failed:\n" + res.stdout + res.stderr)
     return LIB_PATH
 
 

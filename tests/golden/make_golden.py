@@ -143,7 +143,7 @@ def hadamard_cases(H):
 
 
 def config1_case(ptcg, Smooth):
-    """BASELINE config 1 (single W8A8 linear, ViT-B fc1 of one image) run through the reference:
+    """The single-linear benchmark configuration (one W8A8 linear, ViT-B fc1 of one image) run through the reference:
     inputs are regenerated from seeds at test time; outputs are kept as digests plus a strided
     sample so the fixture stays small."""
     out = {}

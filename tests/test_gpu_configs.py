@@ -1,4 +1,4 @@
-"""Encoder-level parity at the sizes BASELINE.json names (reduced batch, full architecture):
+"""Encoder-level parity at the full architectures and 1024x1024 inputs of the benchmark configurations:
 the CUDA engine against the float twin that runs the reference's fake-quant arithmetic on the
 same random-init weights.  Final embeddings must reach cosine >= 0.999."""
 import copy

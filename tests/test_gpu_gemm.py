@@ -103,7 +103,7 @@ def test_bad_arguments(cuda_device):
 
 
 def test_config1_against_reference_digests(cuda_device, golden):
-    """BASELINE config 1 end to end through the C ABI: the fake-quant activations and weights
+    """The single-linear benchmark configuration (ViT-B fc1, one image) end to end through the C ABI: the fake-quant activations and weights
     hash to the digests of the reference's outputs; codes, scales and int32 accumulators equal
     the oracle's; the fp16 layer output is within 1e-2 relative max-abs of the reference's."""
     from sam_quantization_b200 import ops

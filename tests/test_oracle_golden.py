@@ -136,7 +136,7 @@ def test_random_hadamard_matrix(golden):
 
 
 def test_config1_reference_digests(golden):
-    """BASELINE config 1 regenerated from its seeds and pushed through the oracle reproduces
+    """The single-linear benchmark configuration (ViT-B fc1, one image) regenerated from its seeds and pushed through the oracle reproduces
     the digests of the reference's outputs (fake-quant activations and weights bit for bit)."""
     import torch
     g = golden("config1")

@@ -4,9 +4,10 @@ Who needs it: a caller that cannot get device memory where the layer runs — fo
 plugin inside a serving process whose memory was carved up at start-up — and so cannot hand
 samq_act_quant_i8 the small workspace its per-tensor mode requires.  This entry point keeps that
 scratch in an array built into the library.  The test drives it through the C ABI with ctypes
-and checks codes, scale and fake-quant output against the workspace-taking entry point, exactly
-(both run the same rounding), on two consecutive calls whose inputs differ, so that anything the
-first call left in the shared scratch would show up in the second.  The file name sorts last so a
+and checks codes, scale and fake-quant output against the workspace-taking entry point and against
+the CPU oracle's per-tensor quantizer, exactly (all three run the same rounding), on two consecutive
+calls whose inputs differ, so that anything the first call left in the shared scratch would show up
+in the second.  The file name sorts last so a
 run that stops at the first failure has already exercised every other test.
 """
 import ctypes
@@ -51,16 +52,25 @@ def test_static_scratch_variant_matches_workspace_variant(cuda_device):
     gen = torch.Generator().manual_seed(77)
     big = (torch.randn(1000, 768, generator=gen) * 9).half().to(cuda_device)      # call 1: large maximum
     small = (torch.randn(130, 768, generator=gen) * 0.1).half().to(cuda_device)   # call 2: smaller, fewer rows
+    from oracle import oracle as O
     for x in (big, small):
         got = _static(lib, x)
         want = _existing(lib, x)
         torch.cuda.synchronize()
         for g, w in zip(got, want):
             assert torch.equal(g, w)
+        q_ref, s_ref, fq_ref = O.quantize_tensor(x.float().cpu().numpy(), "f16")
+        assert np.array_equal(got[0].cpu().numpy(), O.saturate_codes(q_ref))
+        assert np.array_equal(got[1].cpu().numpy(), s_ref)
+        assert np.array_equal(got[2].float().cpu().numpy(), fq_ref)
     for dt in (torch.bfloat16, torch.float32):
         x = torch.randn(257, 100, generator=gen).to(dt).to(cuda_device)           # odd width: scalar path
-        for g, w in zip(_static(lib, x), _existing(lib, x)):
+        got = _static(lib, x)
+        for g, w in zip(got, _existing(lib, x)):
             assert torch.equal(g, w)
+        q_ref, s_ref, _ = O.quantize_tensor(x.float().cpu().numpy(), "bf16" if dt == torch.bfloat16 else "f32")
+        assert np.array_equal(got[0].cpu().numpy(), O.saturate_codes(q_ref))
+        assert np.array_equal(got[1].cpu().numpy(), s_ref)
 
 
 def test_static_scratch_variant_rejects_oversize(cuda_device):
