@@ -33,11 +33,38 @@ STD = (0.229, 0.224, 0.225)
 ENC = {"vit_b": (768, 12, 4), "vit_l": (1024, 24, 4), "vit_h": (1280, 32, 4)}
 
 
+def workload_name(model_type: str, recipe: str) -> str:
+    """``config.workload`` of both arms: the same string, so that the two lines name one workload."""
+    return f"SAM {model_type} encoder W8A8 {RECIPES[recipe]}, 1024x1024 synthetic images, global batch {GLOBAL_BATCH}"
+
+
 def linear_ops_per_image(model_type: str) -> float:
     C, depth, n_global = ENC[model_type]
     windowed = depth - n_global
     mac = windowed * (4900 * 4 * C * C + 4096 * 8 * C * C) + n_global * (4096 * 12 * C * C)
     return 2.0 * mac
+
+
+# DRAM bytes (read + write) of one int8-GEMM launch at M = 32768 rows, from `ncu` captures of
+# `python -m sam_quantization_b200.kernel_bench gemm` on this kernel (profiles/gemm_i8_kernel_*.md), keyed "KxN".
+# W stays in L2, so the traffic of a launch grows in proportion to its rows: it is scaled by rows / 32768.
+GEMM_TRAFFIC_NCU_M32768 = {"1280x3840": 331e6, "1280x5120": 326e6, "5120x1280": 246e6}
+GEMM_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum per launch at M = 32768 (profiles/), scaled by "
+                       "rows / 32768 and averaged over the step's GEMM launches; shapes without a capture count their "
+                       "algorithmic bytes")
+
+
+def gemm_traffic_per_launch(shapes: dict):
+    """Mean DRAM traffic per GEMM launch of one step from the committed captures."""
+    total, launches = 0.0, 0
+    for key, sh in shapes.items():
+        K, N = (int(v) for v in key.split("x"))
+        if key in GEMM_TRAFFIC_NCU_M32768:
+            total += GEMM_TRAFFIC_NCU_M32768[key] * sh["rows"] / 32768.0
+        else:
+            total += sh["rows"] * K + N * K * sh["launches"] + 2.0 * sh["rows"] * N
+        launches += sh["launches"]
+    return total / launches if launches else None
 
 
 def synthetic_images(n: int, seed: int, size: int = 1024) -> torch.Tensor:
@@ -111,35 +138,67 @@ def build_float_encoder(model_type: str, device, dtype, seed: int = 4):
 RECIPES = {"smoothquant": "SmoothQuant", "rtn": "RTN", "quarot": "QuaRot"}
 
 
-def build_quantized_encoder(model_type: str, device, calib_images: int = 8, recipe: str = "smoothquant"):
+def _float_twin(model):
+    """A copy of the float encoder that will run plain torch attention (the checker's side)."""
+    import copy
+    twin = copy.deepcopy(model)
+    for blk in twin.image_encoder.blocks:
+        blk.attn.native_prep = False
+    return twin
+
+
+def build_quantized_encoder(model_type: str, device, calib_images: int = 8, recipe: str = "smoothquant", with_twin: bool = False):
     """ViT encoder with W8A8 on every linear (per-channel weights, per-token activations).
     smoothquant: SmoothQuant (alpha 0.5) from `calib_images` synthetic calibration images run through
     the float model first; rtn: nothing first; quarot: `rotate_sam` (residual-stream Hadamard folded
-    into the weights, online Hadamard before lin2 and across the heads before proj)."""
+    into the weights, online Hadamard before lin2 and across the heads before proj).
+
+    ``with_twin`` also returns the verification twin: the same float weights taken through the
+    reference's fake-quant arithmetic as restated in oracle/torch_twin.py (used only outside the
+    timed regions, to check the embeddings the timed model produced)."""
     from sam_quantization_b200.RTN_quantization import (W8A8Linear, get_act_scales_sam,
                                                         replace_linear_with_target_and_quantize, smooth_sam)
     model = build_float_encoder(model_type, device, torch.float16)
+    twin = _float_twin(model) if with_twin else None
+    if with_twin:
+        from oracle.torch_twin import (RefActQuantWrapper, RefW8A8Linear, random_hadamard_Q, replace_linears,
+                                       rotate_encoder_weights)
     if recipe == "quarot":
         import types
         from sam_quantization_b200.quarot import rotate_sam
         enc = model.image_encoder
         dim, heads = enc.blocks[0].attn.qkv.in_features, enc.blocks[0].attn.num_heads
+        if with_twin:
+            signs, Q = random_hadamard_Q(dim, 123) if dim & (dim - 1) == 0 else (None, None)
+            if Q is None:
+                twin = None                               # the twin's helper covers power-of-two widths
+            else:
+                rotate_encoder_weights(twin, Q.to(device), dim, heads)
+                replace_linears(twin, lambda lin: RefActQuantWrapper(lin))
+                for blk in twin.image_encoder.blocks:
+                    for lin in (blk.attn.qkv, blk.attn.proj, blk.mlp.lin1, blk.mlp.lin2):
+                        lin.quantize_input = True
+                    blk.attn.qkv.pre_signs = blk.mlp.lin1.pre_signs = signs.to(device)
+                    blk.mlp.lin2.online_full_had = True
+                    blk.attn.proj.online_partial_had, blk.attn.proj.had_dim = True, dim // heads
         rot = types.SimpleNamespace(hidden_size_image_en=dim, num_attention_head_image_en=heads, hidden_size_mask_de=256,
                                     num_attention_head_mask_de=8, rotate_mode="hadamard", device=str(device), seed=123,
                                     fp32_had=True)
         cfg = types.SimpleNamespace(n_bits=8, weight_quant="per_channel", act_quant="per_token", group_size=None,
                                     quantize_output=False, quantize_input=True)
         rotate_sam(model, rot, cfg)
-        return model
-    if recipe == "rtn":
-        replace_linear_with_target_and_quantize(model, W8A8Linear, 8, [], weight_quant="per_channel", act_quant="per_token")
-        return model
-    calib = (synthetic_images(1, 200 + i).to(device) for i in range(calib_images))
-    with torch.no_grad():
-        scales = get_act_scales_sam(model, calib, num_samples=calib_images)
-    smooth_sam(model, scales, alpha=0.5)
+        return (model, twin) if with_twin else model
+    if recipe == "smoothquant":
+        calib = (synthetic_images(1, 200 + i).to(device) for i in range(calib_images))
+        with torch.no_grad():
+            scales = get_act_scales_sam(model, calib, num_samples=calib_images)
+        smooth_sam(model, scales, alpha=0.5)
+        if with_twin:
+            smooth_sam(twin, scales, alpha=0.5)
     replace_linear_with_target_and_quantize(model, W8A8Linear, 8, [], weight_quant="per_channel", act_quant="per_token")
-    return model
+    if with_twin:
+        replace_linears(twin, lambda lin: RefW8A8Linear.from_float(lin, 8))
+    return (model, twin) if with_twin else model
 
 
 # ------------------------------------------------------------------------------------------
@@ -171,10 +230,11 @@ def cpu_reference_images_per_s(model_type: str, budget_s: float = 25.0):
         for blk in enc.blocks[1:n]:
             x = blk(x)
         t_rest = time.perf_counter() - t0
-    total = (t_block + t_rest) * depth / n
+    measured = t_block + t_rest
+    total = measured * depth / n
     sample = (f"1 image of 1024x1024, fp32 fake-quant twin of the reference's W8A8Linear path, "
-              f"{n} of {depth} blocks timed ({t_block + t_rest:.1f} s)" + ("" if n == depth else f", scaled by {depth}/{n}"))
-    return 1.0 / total, cores, sample
+              f"{n} of {depth} blocks timed ({measured:.1f} s)" + ("" if n == depth else f", scaled by {depth}/{n}"))
+    return 1.0 / total, cores, sample, measured
 
 
 def run_reference(args):
@@ -186,15 +246,19 @@ def run_reference(args):
     cores = os.cpu_count() or 1
     for _ in range(max(1, min(args.warmup, 1))):
         cpu_reference_images_per_s(args.model, budget_s=4.0)
+    measured = []
     for _ in range(max(1, args.steps)):
-        v, cores, sample = cpu_reference_images_per_s(args.model, budget_s=args.ref_budget)
+        v, cores, sample, t = cpu_reference_images_per_s(args.model, budget_s=args.ref_budget)
         vals.append(v)
+        measured.append(t)
     value = sorted(vals)[len(vals) // 2]
+    # a step of this arm is the bounded sample itself (one image, or its first blocks): ms_per_step is
+    # the time the sample really took, so steps x ms_per_step is what this run spent timing
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * GLOBAL_BATCH / value,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * sum(measured) / len(measured),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"SAM {args.model} encoder W8A8 SmoothQuant, 1024x1024, global batch {GLOBAL_BATCH}"},
+        "config": {"workload": workload_name(args.model, args.recipe), "step": "one bounded CPU sample: " + sample},
         "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -225,7 +289,11 @@ def run_ours(args):
         chunk -= 1
 
     from sam_quantization_b200.engine import EncoderRunner
-    model = build_quantized_encoder(args.model, dev, recipe=args.recipe)
+    twin = None
+    if rank == 0 and not args.no_verify:
+        model, twin = build_quantized_encoder(args.model, dev, recipe=args.recipe, with_twin=True)
+    else:
+        model = build_quantized_encoder(args.model, dev, recipe=args.recipe)
     enc = EncoderRunner(model, chunk, device=dev, use_graph=not args.no_graph)
 
     # this rank's shard of the global batch: images [rank*local_n, (rank+1)*local_n), seeded per image
@@ -266,8 +334,15 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    for _ in range(max(3, args.warmup)):
+    # warm-up: at least the requested steps (never fewer than 3) and at least ~3 s of work, so that the
+    # board has reached its power-capped clock before the timed region whatever the per-rank step length is
+    warm_steps = 0
+    torch.cuda.synchronize()
+    t_warm = time.perf_counter()
+    while warm_steps < max(3, args.warmup) or (time.perf_counter() - t_warm < args.warm_seconds and warm_steps < 400):
         step_resident()
+        torch.cuda.synchronize()
+        warm_steps += 1
     with ClockSampler(local_rank) as clocks:
         total_ms = timed(step_resident, args.steps)
     ops.check_status(dev)
@@ -291,7 +366,24 @@ def run_ours(args):
     prof = ops.kernel_timing_summary()
     ops.enable_kernel_timing(False)
 
-    # verification gather (outside every timed region): embeddings of all ranks to rank 0
+    # verification (outside every timed region): this rank's first forward against the fake-quant twin,
+    # then the embeddings of all ranks gathered to rank 0
+    cos_twin = None
+    if twin is not None:
+        with torch.no_grad():
+            want = torch.cat([twin(resident[i:i + 1]) for i in range(chunk)], 0)
+        got = out_dev[:chunk].double().flatten(1)
+        want = want.double().flatten(1)
+        per_image = (got * want).sum(1) / (got.norm(dim=1) * want.norm(dim=1))
+        cos_twin = {"images": int(chunk), "all": float((got.flatten() @ want.flatten()) / (got.norm() * want.norm())),
+                    "min_per_image": float(per_image.min().item()),
+                    "twin": "float encoder with the reference's fake-quant arithmetic (oracle/torch_twin.py), same weights"}
+        del twin, want, got
+        torch.cuda.empty_cache()
+    lib_int8 = None
+    if rank == 0 and not args.no_library_bar:
+        from sam_quantization_b200.kernel_bench import library_int8_peak
+        lib_int8 = library_int8_peak()
     allv = gather_shards(out_dev, GLOBAL_BATCH, dst=0)
     checksum, finite = None, None
     if rank == 0:
@@ -308,32 +400,49 @@ def run_ours(args):
         # dense int8 tensor peak is twice the dense bf16 peak on this part; the measured bf16
         # figure (sustained: the GEMMs run inside a long step) is doubled accordingly
         int8_peak = 2.0 * float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
+        int8_peak_burst = 2.0 * float(peaks.get("bf16_tflops"))
         achieved = (gemm["ops"] / (gemm["ms"] / 1000.0) / 1e12) if gemm["ms"] > 0 else 0.0
+        clk = clocks.summary()
+        mhz = clk.get("sm_mhz")
         line = {
             "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "warmup": args.warmup, "warmup_steps_run": warm_steps, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": f"SAM {args.model} encoder W8A8 {RECIPES[args.recipe]}, 1024x1024, global batch {GLOBAL_BATCH}"
-                                   f" sharded by image, {chunk} images per forward",
+            "config": {"workload": workload_name(args.model, args.recipe),
+                       "step": f"the global batch sharded by image over {world} rank(s), {chunk} images per forward",
                        "l2": "inputs and activations per forward exceed the 126 MB L2", "parallelism": f"dp{world}",
                        "cuda_graph": not args.no_graph},
             "e2e": {"value": e2e_value, "unit": "images/s",
                     "h2d_bytes_per_step": int(host.numel() * host.element_size()) * world,
                     "d2h_bytes_per_step": int(out_host.numel() * out_host.element_size()) * world},
             "gpu_launches": int(launches),
-            "clocks": clocks.summary(),
+            "clocks": clk,
+            # time x clock: lets points taken at different power-capped clocks (1 vs 8 GPUs) be compared
+            "clock_normalised": {"ms_per_step_x_sm_mhz": (total_ms / args.steps) * mhz if mhz else None,
+                                 "images_per_s_at_sm_max": value * clk["sm_max_mhz"] / mhz if mhz else None},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
-                         "frac": achieved / int8_peak if int8_peak else None, "traffic": None,
-                         "kernel": "gemm_i8_kernel (tcgen05 kind::i8)", "peak_source": f"2 x bf16_tflops_sustained, {peak_kind}",
+                         "frac": achieved / int8_peak if int8_peak else None,
+                         "traffic": gemm_traffic_per_launch(prof.get("gemm_shapes", {})),
+                         "traffic_source": GEMM_TRAFFIC_SOURCE,
+                         "algorithmic_bytes_per_launch": gemm["bytes_alg"] / gemm["launches"] if gemm.get("launches") else None,
+                         "kernel": "gemm_i8_kernel (tcgen05 kind::i8)",
+                         "peak_source": f"2 x bf16_tflops_sustained, {peak_kind} (the GEMMs run inside a long step)",
+                         "frac_of_2x_bf16_burst": achieved / int8_peak_burst if int8_peak_burst else None,
+                         "frac_of_nominal_4500": achieved / 4500.0,
+                         "library_int8_tops": None if lib_int8 is None else {"burst": lib_int8[0], "sustained": lib_int8[1],
+                                                                           "what": "torch._int_mm 8192^3 (cuBLASLt COMPUTE_32I, int32 out), measured in this run"},
+                         "frac_of_library_int8_sustained": None if lib_int8 is None else achieved / lib_int8[1],
                          "gemm_ms_per_step": gemm["ms"], "gemm_launches_per_step": gemm["launches"],
                          "linear_tops_per_image": linear_ops_per_image(args.model) / 1e12},
             "act_quant": {"achieved_gbs": (quant["bytes"] / (quant["ms"] / 1000.0) / 1e9) if quant["ms"] > 0 else 0.0,
-                          "peak_gbs": float(peaks["hbm_gbs"]), "ms_per_step": quant["ms"], "launches_per_step": quant["launches"]},
+                          "peak_gbs": float(peaks["hbm_gbs"]), "ms_per_step": quant["ms"], "launches_per_step": quant["launches"],
+                          "bytes": "rows actually read (padding rows of a window gather read nothing) x element size + codes + scales"},
+            "kernels_ms_per_step": {k: round(v["ms"], 3) for k, v in sorted(prof.items()) if isinstance(v, dict) and "ms" in v},
             "verify": {"finite": finite, "mean_abs_embedding": checksum, "gathered_images": int(allv.shape[0]),
-                       "per_image_mean_abs_every_8th": fingerprint},
+                       "per_image_mean_abs_every_8th": fingerprint, "cosine_vs_twin": cos_twin},
         }
         if not args.no_cpu_baseline and world == 1:
-            v, cores, sample = cpu_reference_images_per_s(args.model, budget_s=args.ref_budget)
+            v, cores, sample, _ = cpu_reference_images_per_s(args.model, budget_s=args.ref_budget)
             line["cpu_baseline"] = {"value": v, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -354,6 +463,9 @@ def main():
     ap.add_argument("--ref-budget", dest="ref_budget", type=float, default=25.0, help="seconds of CPU work per reference sample")
     ap.add_argument("--no-cpu-baseline", dest="no_cpu_baseline", action="store_true")
     ap.add_argument("--no-graph", dest="no_graph", action="store_true", help="run the encoder eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-verify", dest="no_verify", action="store_true", help="skip the comparison of the first forward with the fake-quant twin")
+    ap.add_argument("--no-library-bar", dest="no_library_bar", action="store_true", help="skip measuring the vendor library's int8 GEMM rate")
+    ap.add_argument("--warm-seconds", dest="warm_seconds", type=float, default=3.0, help="minimum untimed warm-up time before the timed region")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -112,7 +112,8 @@ class RefActQuantWrapper(nn.Module):
         # optional: the online x @ Q of quarot/model_utils.py:146-152 evaluated as
         # hadU(x * signs) in fp32 (Q = diag(signs) H / sqrt(n), hadamard_utils.py:86-94) and rounded once
         self.pre_signs, self.pre_hadK, self.pre_K = None, None, 1
-        fake_quant(module.weight.data, weight_quant, group_size, n_bit)
+        if weight_quant is not None:                      # None: transforms only (change-of-basis checks)
+            fake_quant(module.weight.data, weight_quant, group_size, n_bit)
 
     @torch.no_grad()
     def forward(self, x):
@@ -147,3 +148,59 @@ def replace_linears(module, factory, exclude=()):
         else:
             replace_linears(child, factory, exclude)
     return module
+
+
+# ----------------------------------------------------------------------------------------
+# QuaRot weight rotation of the image encoder, restated with the pure-torch transform above
+# ----------------------------------------------------------------------------------------
+
+def exact_had_input_side(lin, hadK=None, K=1):
+    """``apply_exact_had_to_linear(lin, had_dim=-1, output=False)`` (quarot/hadamard_utils.py:112-134):
+    the weight's input side takes the full transform, computed in fp32 and cast back."""
+    W = lin.weight.data
+    lin.weight.data = matmul_hadU(W.float(), hadK, K).to(W.dtype)
+
+
+def exact_had_output_side_per_head(weight, bias, had_dim):
+    """``apply_exact_had_to_linear(v, had_dim=head_dim, output=True)`` (quarot/hadamard_utils.py:135-151):
+    every group of ``had_dim`` consecutive output features takes the power-of-two transform scaled
+    by 1/sqrt(had_dim), weight rows and bias alike; fp32, cast back.  Returns (weight, bias)."""
+    Wt = weight.float().t().contiguous()                                   # [in, out]
+    shape = Wt.shape
+    Wt = matmul_hadU(Wt.reshape(-1, shape[-1] // had_dim, had_dim)).reshape(shape)
+    b = matmul_hadU(bias.float().reshape(-1, had_dim)).reshape(bias.shape)
+    return Wt.t().contiguous().to(weight.dtype), b.to(bias.dtype)
+
+
+@torch.no_grad()
+def rotate_encoder_weights(model, Q, hidden, heads, hadK_of=None):
+    """``rotate_model_sam`` for the image encoder (quarot/rotation_utils.py:137-195): qkv and lin1
+    take ``W @ Q`` in fp64; lin2 and proj take the exact transform on their input side; the V
+    slice of qkv takes the per-head transform on its output side, bias included.
+    ``hadK_of(n) -> (table or None, K)`` supplies the explicit factor for widths that are not a
+    power of two."""
+    hadK_of = hadK_of or (lambda n: (None, 1))
+    Q64 = Q.to(torch.float64)
+    blocks = model.image_encoder.blocks
+    for blk in blocks:
+        for lin in (blk.attn.qkv, blk.mlp.lin1):
+            W = lin.weight.data
+            lin.weight.data = (W.to(torch.float64) @ Q64.to(W.device)).to(W.dtype)
+    for blk in blocks:
+        exact_had_input_side(blk.mlp.lin2, *hadK_of(blk.mlp.lin2.in_features))
+    head_dim = hidden // heads
+    for blk in blocks:
+        qkv = blk.attn.qkv
+        w, b = exact_had_output_side_per_head(qkv.weight.data[2 * hidden:3 * hidden].clone(),
+                                              qkv.bias.data[2 * hidden:3 * hidden].clone(), head_dim)
+        qkv.weight.data[2 * hidden:3 * hidden] = w
+        qkv.bias.data[2 * hidden:3 * hidden] = b
+        exact_had_input_side(blk.attn.proj, *hadK_of(blk.attn.proj.in_features))
+
+
+def random_hadamard_Q(size, seed):
+    """``random_hadamard_matrix`` (quarot/hadamard_utils.py:86-94): (signs, Q) with
+    Q = hadU(diag(signs)) in fp64, so that x @ Q == hadU(x * signs)."""
+    torch.manual_seed(seed)
+    signs = (torch.randint(low=0, high=2, size=(size,)).to(torch.float64) * 2 - 1)
+    return signs, matmul_hadU(torch.diag(signs))

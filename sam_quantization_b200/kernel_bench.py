@@ -5,6 +5,7 @@
     python -m sam_quantization_b200.kernel_bench attn  --windows 200 --H 14 --W 14 --heads 16 --head-dim 80
     python -m sam_quantization_b200.kernel_bench attn-global --images 8 --H 64 --heads 16 --head-dim 80
     python -m sam_quantization_b200.kernel_bench sweep            # the W8A8 GEMM sweep: M x (K, N) x granularity
+    python -m sam_quantization_b200.kernel_bench library --M 32768 --N 5120 --K 1280   # cuBLASLt int8 / fp16 bars
 
 Each line of output is JSON: the shape, the mean CUDA-event time over ``--iters`` launches after
 ``--warmup`` launches, and the achieved rate against the roofline that bounds the kernel
@@ -73,6 +74,61 @@ def bench_gemm(M, N, K, gelu=False, residual=False, w_gran="per_channel", out_dt
             "ms": round(ms, 5), "int8_tops": round(2.0 * M * N * K / ms / 1e9, 1), "buffers": nbuf}
 
 
+def bench_library(M, N, K, iters=50, warmup=10, nbuf=None):
+    """Comparison bars on the same shape, never on the product path: the vendor library's int8
+    GEMM with int32 accumulation (``torch._int_mm`` -> cuBLASLt CUBLAS_COMPUTE_32I, the call
+    quant/qgemm/kernels/matmul_int8.cu:81-137 demonstrates; raw int32 out, no epilogue) and the
+    fp16 ``F.linear`` the reference's model path runs (RTN_quantization/per_tensor_channel_group.py:159)."""
+    dev = torch.device("cuda")
+    per = M * K + M * N * 4
+    nbuf = nbuf or max(1, min(8, (256 << 20) // max(per, 1) + 1))
+    out = {"kernel": "library", "M": M, "N": N, "K": K}
+    w8 = torch.randint(-127, 128, (N, K), device=dev, dtype=torch.int8)
+    if M > 16 and K % 8 == 0 and N % 8 == 0:
+        a8 = [torch.randint(-127, 128, (M, K), device=dev, dtype=torch.int8) for _ in range(nbuf)]
+        try:
+            ms = _time(lambda i: torch._int_mm(a8[i % nbuf], w8.t()), iters, warmup)
+            out["int_mm_ms"], out["int_mm_tops"] = round(ms, 5), round(2.0 * M * N * K / ms / 1e9, 1)
+        except RuntimeError as e:                                  # shape not supported by the library call
+            out["int_mm_error"] = str(e).splitlines()[0][:120]
+        del a8
+    w16 = (torch.randn((N, K), device=dev) * 0.02).half()
+    b16 = (torch.randn(N, device=dev) * 0.01).half()
+    a16 = [torch.randn((M, K), device=dev, dtype=torch.float16) for _ in range(nbuf)]
+    ms = _time(lambda i: torch.nn.functional.linear(a16[i % nbuf], w16, b16), iters, warmup)
+    out["f16_linear_ms"], out["f16_linear_tflops"] = round(ms, 5), round(2.0 * M * N * K / ms / 1e9, 1)
+    return out
+
+
+def library_int8_peak(seconds=1.5):
+    """Measured dense int8 tensor bar of this GPU through the vendor library: ``torch._int_mm`` on
+    8192^3, best single launch of ten (burst) and the mean over ``seconds`` of back-to-back launches
+    (sustained, under the power cap).  Returns (burst TOP/s, sustained TOP/s)."""
+    dev = torch.device("cuda")
+    n = 8192
+    a = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
+    b = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8).t()
+    for _ in range(3):
+        torch._int_mm(a, b)
+    best = 1e9
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        torch._int_mm(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    reps = max(10, int(seconds * 1000.0 / best))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        torch._int_mm(a, b)
+    e1.record()
+    torch.cuda.synchronize()
+    ops_per = 2.0 * n ** 3
+    return ops_per / best / 1e9, ops_per * reps / e0.elapsed_time(e1) / 1e9
+
+
 def bench_quant(M, K, dtype=torch.float16, ln=False, gather=False, hadamard=None, granularity="per_token", group_size=128,
                 iters=50, warmup=10):
     dev = torch.device("cuda")
@@ -136,6 +192,56 @@ def bench_global_attention(images, H, heads, head_dim, dtype=torch.bfloat16, ite
             "head_dim": head_dim, "ms": round(ms, 5), "tflops": round(flops / ms / 1e9, 1)}
 
 
+def _measured_int8_peak():
+    """(dense int8 TOP/s used as the denominator, where it came from): twice the measured dense
+    bf16 burst rate when the pool's peak file is next to the package, else twice 1590."""
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return 2.0 * float(json.load(f)["bf16_tflops"]), "2 x measured bf16 burst"
+    return 2.0 * 1590.0, "2 x 1590 (fallback)"
+
+
+def run_sweep(args):
+    """The W8A8 GEMM sweep: every (K, N) x M x weight granularity, int8 TOP/s and fraction of the
+    dense int8 peak, next to the vendor library's int8 GEMM and fp16 linear on the same shape."""
+    peak, peak_src = (args.peak, "given") if args.peak else _measured_int8_peak()
+    grans = args.granularities.split(",")
+    rows = {}
+    lib_rows = {}
+    for K, N in SWEEP_KN:
+        for M in SWEEP_M:
+            it = args.iters if M <= 32768 else max(10, args.iters // 5)
+            for gran in grans:
+                r = bench_gemm(M, N, K, w_gran=gran, iters=it, warmup=args.warmup)
+                r["frac_of_peak"] = round(r["int8_tops"] / peak, 3)
+                rows[(K, N, M, gran)] = r
+                print(json.dumps(r), flush=True)
+            if not args.no_library:
+                r = bench_library(M, N, K, iters=it, warmup=args.warmup)
+                lib_rows[(K, N, M)] = r
+                print(json.dumps(r), flush=True)
+    if args.markdown:
+        lines = [f"Dense int8 peak used for the fraction: {peak:.0f} TOP/s ({peak_src}).  Each cell: M = "
+                 + " / ".join(str(m) for m in SWEEP_M) + " tokens.", ""]
+        head = "| K -> N | " + " | ".join(f"{g} TOP/s | {g} frac" for g in grans)
+        if lib_rows:
+            head += " | cuBLASLt int8 (int32 out) TOP/s | fp16 F.linear TFLOP/s"
+        lines += [head + " |", "|" + "---|" * (head.count("|"))]
+        for K, N in SWEEP_KN:
+            cells = [f"{K} -> {N}"]
+            for g in grans:
+                cells.append(" / ".join(f"{rows[(K, N, M, g)]['int8_tops']:.0f}" for M in SWEEP_M))
+                cells.append(" / ".join(f"{rows[(K, N, M, g)]['frac_of_peak']:.2f}" for M in SWEEP_M))
+            if lib_rows:
+                cells.append(" / ".join(f"{lib_rows[(K, N, M)].get('int_mm_tops', float('nan')):.0f}" for M in SWEEP_M))
+                cells.append(" / ".join(f"{lib_rows[(K, N, M)]['f16_linear_tflops']:.0f}" for M in SWEEP_M))
+            lines.append("| " + " | ".join(cells) + " |")
+        with open(args.markdown, "w") as f:
+            f.write("\n".join(lines) + "\n")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--pair-mode", dest="pair_mode", type=int, default=None, choices=[0, 1, 2],
@@ -179,7 +285,17 @@ def main():
     s = sub.add_parser("sweep")
     s.add_argument("--iters", type=int, default=100)
     s.add_argument("--warmup", type=int, default=20)
-    s.add_argument("--granularities", default="per_tensor,per_channel")
+    s.add_argument("--granularities", default="per_tensor,per_channel,per_group")
+    s.add_argument("--no-library", dest="no_library", action="store_true", help="skip the cuBLASLt int8 / fp16 comparison bars")
+    s.add_argument("--peak", type=float, default=None, help="dense int8 TOP/s the fraction column divides by (default: "
+                   "twice the measured bf16 burst figure of MEASURED_PEAKS.json, else 2 x 1590)")
+    s.add_argument("--markdown", default=None, help="also write the sweep as a markdown table to this path")
+    lb = sub.add_parser("library")
+    lb.add_argument("--M", type=int, default=32768)
+    lb.add_argument("--N", type=int, default=5120)
+    lb.add_argument("--K", type=int, default=1280)
+    lb.add_argument("--iters", type=int, default=50)
+    lb.add_argument("--warmup", type=int, default=10)
     args = ap.parse_args()
     if args.pair_mode is not None:
         ops.set_gemm_pair_mode(args.pair_mode)
@@ -192,12 +308,10 @@ def main():
     elif args.cmd == "quant":
         print(json.dumps(bench_quant(args.M, args.K, getattr(torch, args.dtype), args.ln, args.gather, args.hadamard,
                                      args.granularity, iters=args.iters, warmup=args.warmup)))
+    elif args.cmd == "library":
+        print(json.dumps(bench_library(args.M, args.N, args.K, iters=args.iters, warmup=args.warmup)))
     else:
-        for gran in args.granularities.split(","):
-            for K, N in SWEEP_KN:
-                for M in SWEEP_M:
-                    it = args.iters if M <= 32768 else max(10, args.iters // 5)
-                    print(json.dumps(bench_gemm(M, N, K, w_gran=gran, iters=it, warmup=args.warmup)), flush=True)
+        run_sweep(args)
 
 
 if __name__ == "__main__":

@@ -59,7 +59,8 @@ _status_words = {}
 # ---- launch accounting and optional per-kernel timing (used by bench.py) -----------------------
 _launches = 0
 _timing_on = False
-_timing_records = []          # (kind, start_event, end_event, work)
+_timing_records = []          # (kind, start_event, end_event, work, detail)
+_valid_rows = {}              # (data_ptr, numel) of a row map -> rows that are not padding
 
 
 def reset_counters() -> None:
@@ -81,20 +82,34 @@ def enable_kernel_timing(on: bool) -> None:
 
 def kernel_timing_summary() -> dict:
     """{kind: {"ms", "launches", "ops" | "bytes"}} summed over the bracketed launches
-    (synchronises).  ``ops`` = 2*M*N*K per GEMM, ``bytes`` = the algorithmic M*(in+1)*K+4M of K1."""
+    (synchronises).  ``ops`` = 2*M*N*K per GEMM, ``bytes`` = the algorithmic bytes of K1 (source rows
+    actually read x element size + codes + scales).  The GEMM entry also carries ``bytes_alg`` (the
+    algorithmic M*K + N*K + out_bytes*M*N) and ``"gemm_shapes"`` maps "KxN" to launches and total rows."""
     torch.cuda.synchronize()
     out = {}
-    for kind, e0, e1, work in _timing_records:
+    shapes = {}
+    for kind, e0, e1, work, detail in _timing_records:
         d = out.setdefault(kind, {"ms": 0.0, "launches": 0, "ops": 0.0, "bytes": 0.0})
-        d["ms"] += e0.elapsed_time(e1)
+        ms = e0.elapsed_time(e1)
+        d["ms"] += ms
         d["launches"] += 1
         d["ops" if kind == "gemm_i8" else "bytes"] += work
+        if kind == "gemm_i8" and detail is not None:
+            M, N, K, out_bytes = detail
+            d["bytes_alg"] = d.get("bytes_alg", 0.0) + M * K + N * K + out_bytes * M * N
+            sh = shapes.setdefault(f"{K}x{N}", {"launches": 0, "rows": 0, "ms": 0.0, "ops": 0.0})
+            sh["launches"] += 1
+            sh["rows"] += M
+            sh["ms"] += ms
+            sh["ops"] += work
+    if shapes:
+        out["gemm_shapes"] = shapes
     return out
 
 
 class _Timed:
-    def __init__(self, kind, work, kernels=1):
-        self.kind, self.work, self.kernels = kind, work, kernels
+    def __init__(self, kind, work, kernels=1, detail=None):
+        self.kind, self.work, self.kernels, self.detail = kind, work, kernels, detail
 
     def __enter__(self):
         global _launches
@@ -108,7 +123,7 @@ class _Timed:
     def __exit__(self, *exc):
         if _timing_on:
             self.e1.record()
-            _timing_records.append((self.kind, self.e0, self.e1, self.work))
+            _timing_records.append((self.kind, self.e0, self.e1, self.work, self.detail))
         return False
 
 
@@ -229,8 +244,14 @@ def quantize(x: torch.Tensor, granularity: int = GRAN_ROW, group_size: Optional[
         if divisor.numel() != K:
             raise ValueError("divisor must have K elements")
     spec = _spec(hadamard, keep)
-    nbytes = M * (K * x.element_size() + (K if codes else 0) + (K * x.element_size() if fake_quant else 0)
-                  + (K * x.element_size() if transformed else 0)) + scale.numel() * 4
+    rows_read = M
+    if _timing_on and row_map is not None:                # padding rows (negative map entries) read nothing
+        key = (row_map.data_ptr(), row_map.numel())
+        if key not in _valid_rows:
+            _valid_rows[key] = int((row_map >= 0).sum().item())
+        rows_read = _valid_rows[key]
+    nbytes = rows_read * K * x.element_size() + M * ((K if codes else 0) + (K * x.element_size() if fake_quant else 0)
+                                                     + (K * x.element_size() if transformed else 0)) + scale.numel() * 4
     with torch.cuda.device(dev), _Timed("act_quant", nbytes, 3 if granularity == GRAN_TENSOR else 1):
         _lib.check(lib.samq_act_quant_i8_ex(
             _ptr(x2), _DTYPE_CODE[tdtype], M, K, ldx,
@@ -345,7 +366,7 @@ def gemm_i8(a_q: torch.Tensor, w_q: torch.Tensor,
         a_scale = a_scale.to(device=dev, dtype=torch.float32).contiguous()
     if w_scale is not None:
         w_scale = w_scale.to(device=dev, dtype=torch.float32).contiguous()
-    with torch.cuda.device(dev), _Timed("gemm_i8", 2.0 * M * N * K):
+    with torch.cuda.device(dev), _Timed("gemm_i8", 2.0 * M * N * K, detail=(M, N, K, out.element_size())):
         _lib.check(lib.samq_gemm_i8(
             _ptr(a2), lda, _ptr(w2), ldw, M, N, K,
             _ptr(a_scale), a_gran, _ptr(w_scale), w_gran, int(group_size or 0),

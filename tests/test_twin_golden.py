@@ -37,3 +37,45 @@ def test_twin_encoder_equals_reference_encoder(golden):
             emb = model(tiny_images()).numpy()
         want = g[f"{tag}/embedding"]
         assert np.abs(emb - want).max() <= 1e-4 * np.abs(want).max()
+
+
+def test_twin_random_hadamard_equals_reference(golden):
+    """The twin's Q = hadU(diag(signs)) is the reference's ``random_hadamard_matrix(seed=123)``
+    byte for byte (digest recorded from the reference's function)."""
+    import hashlib
+    from oracle.torch_twin import random_hadamard_Q
+    g = golden("hadamard")
+    sizes = sorted(int(k.split("/")[1]) for k in g.files if k.startswith("randhad/") and k.endswith("/sha256"))
+    assert sizes
+    for n in sizes:
+        if n & (n - 1):
+            continue                                      # the twin's helper covers powers of two
+        signs, Q = random_hadamard_Q(n, 123)
+        assert hashlib.sha256(Q.numpy().tobytes()).hexdigest() == str(g[f"randhad/{n}/sha256"])
+        assert torch.equal((Q * signs.view(-1, 1))[0], torch.full((n,), 1.0 / n ** 0.5, dtype=torch.float64))   # Q = diag(signs) H / sqrt(n)
+
+
+def test_twin_rotation_is_an_exact_change_of_basis():
+    """Weights rotated by the twin's restatement of ``rotate_model_sam`` plus the online
+    transforms of ``ActQuantWrapper`` (sign flip + transform before qkv / lin1, full transform
+    before lin2, across-heads transform before proj) reproduce the unrotated float encoder."""
+    import copy
+    from oracle.torch_twin import RefActQuantWrapper, random_hadamard_Q, rotate_encoder_weights
+    from sam_quantization_b200.sam_encoder import build_encoder
+    kw = dict(TINY)
+    kw.update(embed_dim=32, num_heads=4)
+    model = build_encoder(seed=9, dtype=torch.float32, attn_dtype=None, **kw)
+    rot = copy.deepcopy(model)
+    signs, Q = random_hadamard_Q(32, 123)
+    rotate_encoder_weights(rot, Q, 32, 4)
+    replace_linears(rot, lambda lin: RefActQuantWrapper(lin, weight_quant=None))
+    for blk in rot.image_encoder.blocks:
+        blk.attn.qkv.pre_signs = blk.mlp.lin1.pre_signs = signs
+        blk.mlp.lin2.online_full_had = True
+        blk.attn.proj.online_partial_had, blk.attn.proj.had_dim = True, 8
+    x = tiny_images()
+    with torch.no_grad():
+        a, b = model(x), rot(x)
+    assert (a - b).abs().max() <= 2e-4 * a.abs().max()
+    # and the rotation did change the weights
+    assert not torch.allclose(model.image_encoder.blocks[0].attn.qkv.weight, rot.image_encoder.blocks[0].attn.qkv.module.weight)
