@@ -208,7 +208,9 @@ int samq_act_quant_per_tensor_static(const void* x, int dtype, int64_t M, int64_
  *
  * computed with tcgen05.mma kind::i8 into tensor memory.  With grouped scales
  * (either operand) the int32 partial sum of each group of `group_size`
- * columns of K is scaled on its own and the products are summed in fp32.
+ * columns of K is scaled on its own and the products are summed in fp32;
+ * group_size must then be a multiple of 32 that divides K, with at most 160
+ * groups per row (SAMQ_ERR_UNSUPPORTED / SAMQ_ERR_TOO_LARGE otherwise).
  *
  * A        : [M, K] int8, row stride lda bytes (lda % 16 == 0, base 16-byte aligned)
  * W        : [N, K] int8, row stride ldw bytes (same alignment rule)

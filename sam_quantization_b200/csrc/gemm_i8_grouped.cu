@@ -10,7 +10,10 @@
 // every wait bounded), with a 128 x 128 tile and four 128-column TMEM accumulators: the MMA warp
 // accumulates the k-blocks of one group into the next free accumulator and publishes it; the
 // epilogue warps drain it into fp32 registers (64 per thread) scaled by that group's scales while
-// the MMAs of the following groups run.  group_size must be a multiple of 128.
+// the MMAs of the following groups run.  group_size must be a multiple of 32 (one tcgen05.mma
+// covers 32 columns of K; a 128-column stage may hold up to four groups, each accumulated into its
+// own buffer).  The drain is two instructions per element when only the weights are grouped (the
+// per-token scale is applied once at the end of the tile) and packed fp32x2 throughout.
 #include "gemm_common.cuh"
 
 namespace samq {
@@ -23,7 +26,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BN = 128;
 constexpr int UK = 32;
-constexpr int STAGES = 5;
+constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK;               // 16 KiB
 constexpr int B_BYTES = BN * BK;               // 16 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -31,7 +34,7 @@ constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + EPI_WARPS * 32;
 constexpr int ACC_BUFS = 4;
 constexpr int TMEM_COLS = ACC_BUFS * BN;       // 512
-constexpr int MAX_GROUPS = 64;                 // w-scale staging: MAX_GROUPS x BN floats
+constexpr int MAX_GROUPS = 160;                // w-scale staging: MAX_GROUPS x BN floats (K = 5120 in groups of 32)
 constexpr int STAGING_BYTES = 32 * 64;
 
 struct __align__(8) Control {
@@ -51,7 +54,8 @@ constexpr uint32_t kInstrDesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)
 struct GroupedParams {
     int M, N, K;
     int groups;                 // K / group_size
-    int kb_per_group;           // group_size / 128
+    int units_per_group;        // group_size / 32: tcgen05.mma instructions per group
+    int a_grouped;              // the activation scale changes with the group
     const float* a_scale; int a_row_stride, a_group_stride;    // a_scale[m * a_row_stride + g * a_group_stride]
     const float* w_scale; int w_row_stride, w_group_stride;
     const void* bias;
@@ -102,7 +106,8 @@ gemm_i8_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
-    const int k_blocks = p.groups * p.kb_per_group;
+    const int total_units = p.groups * p.units_per_group;          // K / 32
+    const int k_blocks = (total_units + BK / UK - 1) / (BK / UK);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -132,22 +137,27 @@ gemm_i8_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int unit = 0;                                   // 32-column steps of K issued for this tile
+                uint64_t adesc = 0, bdesc = 0;
                 for (int g = 0; g < p.groups && ok; ++g) {
                     if (!mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-                    for (int kb = 0; kb < p.kb_per_group; ++kb) {
-                        if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag)) { ok = false; break; }
-                        tcgen05_fence_after();
-                        const uint32_t sa = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
-                        const uint64_t adesc = make_smem_desc(sa);
-                        const uint64_t bdesc = make_smem_desc(sa + A_BYTES);
-#pragma unroll
-                        for (int k = 0; k < BK / UK; ++k)
-                            mma_i8(tmem_d, adesc + (uint64_t)(k * (UK >> 4)), bdesc + (uint64_t)(k * (UK >> 4)),
-                                   kInstrDesc, (kb | k) != 0 ? 1u : 0u);
-                        tcgen05_commit(smem_u32(&ctl->empty[stage]));
-                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    for (int u = 0; u < p.units_per_group; ++u) {
+                        const int k = unit & (BK / UK - 1);
+                        if (k == 0) {                            // first step of a stage: its operands must have landed
+                            if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag)) { ok = false; break; }
+                            tcgen05_fence_after();
+                            const uint32_t sa = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
+                            adesc = make_smem_desc(sa);
+                            bdesc = make_smem_desc(sa + A_BYTES);
+                        }
+                        mma_i8(tmem_d, adesc + (uint64_t)(k * (UK >> 4)), bdesc + (uint64_t)(k * (UK >> 4)), kInstrDesc, u != 0 ? 1u : 0u);
+                        ++unit;
+                        if ((unit & (BK / UK - 1)) == 0 || unit == total_units) {   // last step that reads this stage
+                            tcgen05_commit(smem_u32(&ctl->empty[stage]));
+                            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                        }
                     }
                     if (!ok) break;
                     tcgen05_commit(smem_u32(&ctl->acc_full[acc]));       // this group's partial sums are complete
@@ -185,35 +195,43 @@ gemm_i8_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
             const int row = m0 + quad * 32 + lane;
             const bool row_ok = row < p.M;
-            float y[64];
+            float2 y2[32];
 #pragma unroll
-            for (int j = 0; j < 64; ++j) y[j] = 0.f;
+            for (int j = 0; j < 32; ++j) y2[j] = make_float2(0.f, 0.f);
+            // a per-token (or per-tensor) activation scale is the same for every group: it multiplies the sum once
+            float a_row = 1.0f;
+            if (!p.a_grouped && p.a_scale != nullptr && row_ok) a_row = p.a_scale[(int64_t)row * p.a_row_stride];
             for (int g = 0; g < p.groups; ++g) {
                 if (ok && !mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag)) ok = false;
                 if (!ok) break;
                 tcgen05_fence_after();
                 float a_s = 1.0f;
-                if (p.a_scale != nullptr && row_ok) a_s = p.a_scale[(int64_t)row * p.a_row_stride + (int64_t)g * p.a_group_stride];
+                if (p.a_grouped && p.a_scale != nullptr && row_ok) a_s = p.a_scale[(int64_t)row * p.a_row_stride + (int64_t)g * p.a_group_stride];
+                const float2 a2 = make_float2(a_s, a_s);
                 const uint32_t tmem_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + half_n * 64);
                 const float* ws = wscales + g * BN + half_n * 64;
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_row + (uint32_t)(c * 32), r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const float4 w4 = *reinterpret_cast<const float4*>(ws + c * 32 + j);
-                        y[c * 32 + j + 0] = fmaf(__int2float_rn((int)r[j + 0]), a_s * w4.x, y[c * 32 + j + 0]);
-                        y[c * 32 + j + 1] = fmaf(__int2float_rn((int)r[j + 1]), a_s * w4.y, y[c * 32 + j + 1]);
-                        y[c * 32 + j + 2] = fmaf(__int2float_rn((int)r[j + 2]), a_s * w4.z, y[c * 32 + j + 2]);
-                        y[c * 32 + j + 3] = fmaf(__int2float_rn((int)r[j + 3]), a_s * w4.w, y[c * 32 + j + 3]);
-                    }
-                }
+                uint32_t r0[32], r1[32];
+                tmem_ld32(tmem_row, r0);
+                tmem_ld32(tmem_row + 32u, r1);
+                tmem_ld_wait();
+                // the accumulator is in registers: hand the buffer back before doing the arithmetic
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
                 if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const uint32_t* r = c == 0 ? r0 : r1;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 w4 = *reinterpret_cast<const float4*>(ws + c * 32 + j);
+                        float2 wlo = make_float2(w4.x, w4.y), whi = make_float2(w4.z, w4.w);
+                        if (p.a_grouped) { wlo = __fmul2_rn(wlo, a2); whi = __fmul2_rn(whi, a2); }
+                        const int q = (c * 32 + j) >> 1;
+                        y2[q] = __ffma2_rn(make_float2(__int2float_rn((int)r[j + 0]), __int2float_rn((int)r[j + 1])), wlo, y2[q]);
+                        y2[q + 1] = __ffma2_rn(make_float2(__int2float_rn((int)r[j + 2]), __int2float_rn((int)r[j + 3])), whi, y2[q + 1]);
+                    }
+                }
             }
             if (!ok) continue;                       // keep visiting the named barriers
 
@@ -228,7 +246,11 @@ gemm_i8_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 constexpr int NVEC = 32 / PER16;
                 float v[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = y[c * 32 + j] + biases[col0 + j];
+                for (int j = 0; j < 32; j += 2) {
+                    const float2 t = y2[(c * 32 + j) >> 1];
+                    v[j] = fmaf(t.x, a_row, biases[col0 + j]);
+                    v[j + 1] = fmaf(t.y, a_row, biases[col0 + j + 1]);
+                }
                 if (p.activation == SAMQ_ACT_GELU) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
@@ -305,8 +327,8 @@ int gemm_i8_grouped_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int6
     if (M == 0) return SAMQ_OK;
     if (A == nullptr || W == nullptr || out == nullptr) return fail(SAMQ_ERR_BAD_ARG, "A, W and out must not be null");
     if (group_size <= 0 || K % group_size != 0) return fail(SAMQ_ERR_BAD_ARG, "group_size %d must divide K=%lld", group_size, (long long)K);
-    if (group_size % BK != 0)
-        return fail(SAMQ_ERR_UNSUPPORTED, "the grouped GEMM needs group_size to be a multiple of %d (got %d)", BK, group_size);
+    if (group_size % UK != 0)
+        return fail(SAMQ_ERR_UNSUPPORTED, "the grouped GEMM needs group_size to be a multiple of %d (got %d)", UK, group_size);
     const int64_t groups = K / group_size;
     if (groups > MAX_GROUPS) return fail(SAMQ_ERR_TOO_LARGE, "K / group_size = %lld exceeds %d groups", (long long)groups, MAX_GROUPS);
     if (M > 2147483647LL - BM || N > 2147483647LL - BN) return fail(SAMQ_ERR_TOO_LARGE, "GEMM dimension exceeds 2^31");
@@ -326,7 +348,8 @@ int gemm_i8_grouped_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int6
 
     GroupedParams p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
-    p.groups = (int)groups; p.kb_per_group = group_size / BK;
+    p.groups = (int)groups; p.units_per_group = group_size / UK;
+    p.a_grouped = (a_gran == SAMQ_GRAN_GROUP) ? 1 : 0;
     p.a_scale = a_scale; p.w_scale = w_scale;
     p.a_row_stride = (a_gran == SAMQ_GRAN_GROUP) ? (int)groups : (a_gran == SAMQ_GRAN_ROW ? 1 : 0);
     p.a_group_stride = (a_gran == SAMQ_GRAN_GROUP) ? 1 : 0;

@@ -143,7 +143,9 @@ def test_config1_against_reference_digests(cuda_device, golden):
 
 
 @pytest.mark.parametrize("wq,aq,g", [("per_group", "per_token", 128), ("per_group", "per_group_token", 128),
-                                     ("per_channel", "per_group_token", 256), ("per_group", "per_tensor", 384)])
+                                     ("per_channel", "per_group_token", 256), ("per_group", "per_tensor", 384),
+                                     ("per_group", "per_group_token", 64), ("per_group", "per_token", 32),
+                                     ("per_group", "per_group_token", 96)])
 def test_grouped_scales_against_oracle(cuda_device, wq, aq, g):
     """Grouped weights and / or activations: per-group int32 partial sums scaled in fp32."""
     from sam_quantization_b200 import ops
@@ -176,7 +178,23 @@ def test_grouped_gemm_rejects_small_groups(cuda_device):
     a = torch.zeros((8, 256), dtype=torch.int8, device=dev)
     w = torch.zeros((8, 256), dtype=torch.int8, device=dev)
     with pytest.raises(SamqError):
-        ops.gemm_i8(a, w, torch.ones(8, device=dev), torch.ones((8, 8), device=dev), 0, 2, 32, out_dtype=torch.float16)
+        ops.gemm_i8(a, w, torch.ones(8, device=dev), torch.ones((8, 16), device=dev), 0, 2, 16, out_dtype=torch.float16)
+
+
+def test_group_size_64_linear_as_in_the_quarot_yaml(cuda_device):
+    """group_size 64 (the only group size the reference's configurations use, quant/config/hq44k/quarot.yaml)
+    through the module: ViT-H lin2's width, 80 groups per row."""
+    from oracle.torch_twin import RefW8A8Linear
+    from sam_quantization_b200.RTN_quantization import W8A8Linear
+    g = torch.Generator().manual_seed(3)
+    lin = torch.nn.Linear(5120, 256).half().to(cuda_device)
+    x = torch.randn(300, 5120, generator=g).half().to(cuda_device)
+    import copy
+    src = copy.deepcopy(lin)
+    mine = W8A8Linear.from_float(lin, 8, "per_group", "per_group_token", False, 64)
+    twin = RefW8A8Linear.from_float(src, 8, "per_group", "per_group_token", False, 64)
+    a, b = mine(x).float(), twin(x).float()
+    assert (a - b).abs().max() <= 1e-2 * b.abs().max()
 
 
 # ---- CTA-pair implementation (tcgen05 cta_group::2) --------------------------------------------
