@@ -112,6 +112,9 @@ class RefActQuantWrapper(nn.Module):
         # optional: the online x @ Q of quarot/model_utils.py:146-152 evaluated as
         # hadU(x * signs) in fp32 (Q = diag(signs) H / sqrt(n), hadamard_utils.py:86-94) and rounded once
         self.pre_signs, self.pre_hadK, self.pre_K = None, None, 1
+        # optional: evaluate the float linear in another dtype (fp64) and round once to the tensor dtype: the same
+        # arithmetic as the reference up to the summation order / accumulator width of its float GEMM
+        self.linear_dtype = None
         if weight_quant is not None:                      # None: transforms only (change-of-basis checks)
             fake_quant(module.weight.data, weight_quant, group_size, n_bit)
 
@@ -133,7 +136,12 @@ class RefActQuantWrapper(nn.Module):
             x = v.transpose(1, 2).reshape(shape).to(dt)
         if self.quantize_input:
             x = fake_quant(x.contiguous().clone(), self.act_quant_name, self.group_size, self.n_bits)
-        x = self.module(x).to(dt)
+        if self.linear_dtype is None:
+            x = self.module(x).to(dt)
+        else:
+            ld = self.linear_dtype
+            x = torch.nn.functional.linear(x.to(ld), self.module.weight.to(ld),
+                                           None if self.module.bias is None else self.module.bias.to(ld)).to(dt)
         if self.quantize_output:
             x = fake_quant(x, self.act_quant_name, self.group_size, self.n_bits)
         return x

