@@ -219,19 +219,32 @@ gemm_i8_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
                 if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    const uint32_t* r = c == 0 ? r0 : r1;
+                // int32 -> fp32 without the conversion instruction: a group of up to 256 columns keeps
+                // |acc| <= 127^2 * 256 < 2^22, so 1.5 * 2^23 + acc is exact in fp32 and its bit pattern is
+                // 0x4B400000 + acc; an integer add and a packed float subtract recover float(acc) exactly.
+                auto drain = [&](const uint32_t (&r)[32], int c, auto magic) {
+                    constexpr bool MAGIC = decltype(magic)::value;
+                    const float2 k2 = make_float2(-12582912.0f, -12582912.0f);
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
                         const float4 w4 = *reinterpret_cast<const float4*>(ws + c * 32 + j);
                         float2 wlo = make_float2(w4.x, w4.y), whi = make_float2(w4.z, w4.w);
                         if (p.a_grouped) { wlo = __fmul2_rn(wlo, a2); whi = __fmul2_rn(whi, a2); }
+                        float2 flo, fhi;
+                        if (MAGIC) {
+                            flo = __fadd2_rn(make_float2(__uint_as_float(r[j + 0] + 0x4B400000u), __uint_as_float(r[j + 1] + 0x4B400000u)), k2);
+                            fhi = __fadd2_rn(make_float2(__uint_as_float(r[j + 2] + 0x4B400000u), __uint_as_float(r[j + 3] + 0x4B400000u)), k2);
+                        } else {
+                            flo = make_float2(__int2float_rn((int)r[j + 0]), __int2float_rn((int)r[j + 1]));
+                            fhi = make_float2(__int2float_rn((int)r[j + 2]), __int2float_rn((int)r[j + 3]));
+                        }
                         const int q = (c * 32 + j) >> 1;
-                        y2[q] = __ffma2_rn(make_float2(__int2float_rn((int)r[j + 0]), __int2float_rn((int)r[j + 1])), wlo, y2[q]);
-                        y2[q + 1] = __ffma2_rn(make_float2(__int2float_rn((int)r[j + 2]), __int2float_rn((int)r[j + 3])), whi, y2[q + 1]);
+                        y2[q] = __ffma2_rn(flo, wlo, y2[q]);
+                        y2[q + 1] = __ffma2_rn(fhi, whi, y2[q + 1]);
                     }
-                }
+                };
+                if (p.units_per_group <= 8) { drain(r0, 0, std::true_type{}); drain(r1, 1, std::true_type{}); }
+                else { drain(r0, 0, std::false_type{}); drain(r1, 1, std::false_type{}); }
             }
             if (!ok) continue;                       // keep visiting the named barriers
 
