@@ -141,6 +141,57 @@ class W8A8Linear(nn.Module):
         g = self.group_size
         return (q.view(self.out_features, -1, g) * s.view(self.out_features, -1, 1)).view(self.out_features, -1)
 
+    @weight.setter
+    def weight(self, value: torch.Tensor) -> None:
+        """Assigning a float weight (what reference-style code does with ``module.weight = ...``)
+        re-quantizes it with this layer's weight granularity."""
+        out = ops.quantize_weight(value.detach().to(self.qweight.device if self.qweight.is_cuda else value.device),
+                                  ops.WEIGHT_GRANULARITY[self.weight_quant_name], self.group_size, n_bits=self.n_bits)
+        self.qweight, self.w_scale = out["q"], out["scale"]
+        self.compute_dtype = value.dtype
+
+    # -- checkpoints ---------------------------------------------------------------------------
+    def get_extra_state(self):
+        """What a checkpoint needs besides the tensors (int8 codes ``qweight``, fp32 ``w_scale``,
+        ``bias``) to rebuild the layer."""
+        return {"kind": "W8A8Linear", "in_features": self.in_features, "out_features": self.out_features,
+                "act_quant": self.act_quant_name, "weight_quant": self.weight_quant_name,
+                "quantize_output": self.quantize_output, "group_size": self.group_size, "n_bits": self.n_bits,
+                "compute_dtype": str(self.compute_dtype).split(".")[-1]}
+
+    def set_extra_state(self, state):
+        self.act_quant_name, self.weight_quant_name = state["act_quant"], state["weight_quant"]
+        self.quantize_output = bool(state["quantize_output"])
+        self.output_quant_name = self.act_quant_name if self.quantize_output else "None"
+        self.group_size, self.n_bits = state["group_size"], state["n_bits"]
+        self.compute_dtype = getattr(torch, state["compute_dtype"])
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        """Accepts this module's own format and the reference's (RTN_quantization/per_tensor_channel_group.py:111-128:
+        a float ``weight`` [N, K], already fake-quantized or not, and a ``bias`` of shape [1, N] or [N]): a float
+        weight is quantized on the way in."""
+        wkey, bkey = prefix + "weight", prefix + "bias"
+        if wkey in state_dict and prefix + "qweight" not in state_dict:
+            w = state_dict.pop(wkey)
+            dev = self.qweight.device if self.qweight.is_cuda else w.device
+            if dev.type != "cuda":
+                raise RuntimeError("loading a float weight into W8A8Linear quantizes it on the GPU: move the module to a CUDA device first")
+            out = ops.quantize_weight(w.detach().to(dev), ops.WEIGHT_GRANULARITY[self.weight_quant_name], self.group_size,
+                                      n_bits=self.n_bits)
+            state_dict[prefix + "qweight"], state_dict[prefix + "w_scale"] = out["q"], out["scale"]
+            self.compute_dtype = w.dtype
+            if prefix + "_extra_state" not in state_dict:
+                state_dict[prefix + "_extra_state"] = self.get_extra_state()
+        if bkey in state_dict and state_dict[bkey] is not None and self._buffers.get("bias") is not None:
+            b = state_dict[bkey].reshape(-1)
+            state_dict[bkey] = b
+            if self.bias.dtype != b.dtype:                          # the bias keeps the checkpoint's dtype
+                self._buffers["bias"] = torch.empty_like(self.bias, dtype=b.dtype)
+        skey = prefix + "w_scale"
+        if skey in state_dict and state_dict[skey].shape != self.w_scale.shape:   # [N] | [1] | [N, K/g] by granularity
+            self._buffers["w_scale"] = torch.empty(state_dict[skey].shape, dtype=torch.float32, device=self.w_scale.device)
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
+
     def act_quant(self, x):
         """Fake-quantize like the reference's ``self.act_quant`` partial (:130-140)."""
         out = ops.quantize(x, ops.ACT_GRANULARITY[self.act_quant_name], self.group_size, codes=False,
@@ -205,10 +256,8 @@ class W8A8Linear(nn.Module):
                                 act_quant=act_quant, quantize_output=quantize_output,
                                 group_size=group_size, n_bit=n_bits)
         w = module.weight.data
-        if weight_quant == "per_group":
-            assert type(group_size) == int, "group_size must be an integer"
-            assert module.in_features % group_size == 0, \
-                f"in_features ({module.in_features}) must be divisible by group_size ({group_size})"
+        if weight_quant == "per_group" or act_quant == "per_group_token":
+            ops.check_gemm_group_size(module.in_features, group_size)
         out = ops.quantize_weight(w, ops.WEIGHT_GRANULARITY[weight_quant], group_size, codes=True,
                                   fake_quant=True, n_bits=n_bits)
         w.copy_(out["fq"])                               # the reference quantizes the source in place

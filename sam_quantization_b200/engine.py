@@ -18,10 +18,16 @@ class EncoderRunner:
 
     ``images`` may live on the host (pinned memory makes the copy asynchronous) or on the device;
     they are copied into the graph's static input.  The returned tensor is the graph's static
-    output: it is overwritten by the next call, so copy it if it must outlive that call."""
+    output: it is overwritten by the next call, so copy it if it must outlive that call.
+
+    The GEMM and attention kernels give up on a stalled pipeline after a bounded wait and raise a
+    device status word instead of hanging; their output is then incomplete.  ``check_status=True``
+    makes every call synchronise and raise ``RuntimeError`` in that case; otherwise call
+    ``runner.check()`` (or ``ops.check_status``) wherever the caller synchronises anyway."""
 
     def __init__(self, model: torch.nn.Module, batch: int, img_size: int = 1024, dtype: torch.dtype = torch.float16,
-                 device: Optional[torch.device] = None, use_graph: bool = True, warmup: int = 3):
+                 device: Optional[torch.device] = None, use_graph: bool = True, warmup: int = 3, check_status: bool = False):
+        self.check_status = bool(check_status)
         self.encoder = getattr(model, "image_encoder", model)
         self.device = torch.device(device) if device is not None else next(self.encoder.parameters()).device
         if self.device.type != "cuda":
@@ -52,4 +58,11 @@ class EncoderRunner:
             self.graph.replay()
         else:
             self.static_out = self.encoder(self.static_in)
+        if self.check_status:
+            self.check()
         return self.static_out
+
+    def check(self) -> None:
+        """Synchronise and raise if a kernel of this device reported a timed-out wait."""
+        from . import ops
+        ops.check_status(self.device)

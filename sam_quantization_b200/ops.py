@@ -309,6 +309,21 @@ def quantize_weight(w: torch.Tensor, granularity: int = GRAN_ROW, group_size: Op
     return out
 
 
+GEMM_GROUP_MULTIPLE = 32        # one tcgen05.mma covers 32 columns of K
+GEMM_MAX_GROUPS = 160
+
+
+def check_gemm_group_size(in_features: int, group_size) -> None:
+    """Raise early (at module construction) for a group size the grouped int8 GEMM cannot run: the
+    reference's float path accepts any divisor of the width; the tensor-core path needs groups of a
+    multiple of 32 columns and at most 160 groups per row."""
+    assert type(group_size) == int, "group_size must be an integer"
+    assert in_features % group_size == 0, f"in_features ({in_features}) must be divisible by group_size ({group_size})"
+    if group_size % GEMM_GROUP_MULTIPLE != 0 or in_features // group_size > GEMM_MAX_GROUPS:
+        raise ValueError(f"group_size={group_size} with in_features={in_features}: the int8 GEMM needs group sizes that are "
+                         f"multiples of {GEMM_GROUP_MULTIPLE} and at most {GEMM_MAX_GROUPS} groups per row")
+
+
 GEMM_PAIR_NEVER, GEMM_PAIR_AUTO, GEMM_PAIR_ALWAYS = 0, 1, 2
 
 

@@ -86,6 +86,13 @@ class ActQuantWrapper(torch.nn.Module):
     ``fp32_had``, ``quantize_input``, ``quantize_output``; ``pre_signs`` (not in the reference)
     folds the online ``x @ Q`` of a randomized-Hadamard Q into the same kernel.
 
+    ``fp32_had``: the kernel always computes the transform in fp32 and rounds once to the tensor
+    dtype.  For power-of-two lengths (``K == 1``) that is also what the reference's library call
+    does internally for half inputs, so both settings run the same code; for lengths with an
+    explicit factor (``K > 1``: 768, 1280, 3072, 5120, 12 heads) ``fp32_had=False`` raises
+    ``NotImplementedError`` at the first forward instead of returning values rounded differently
+    from the reference's two-rounding half path.
+
     forward: [full | partial Hadamard] -> [int8 activation quantization] -> Linear ->
     [output fake-quant].  With ``quantize_input`` the Linear is the int8 GEMM on the stored weight
     codes; without it the transformed fp16 activation meets the fake-quantized float weight in a
@@ -98,6 +105,8 @@ class ActQuantWrapper(torch.nn.Module):
         assert isinstance(module, torch.nn.Linear)
         if act_quant not in ops.ACT_GRANULARITY:
             raise ValueError(f"Invalid act_quant: {act_quant}")
+        if act_quant == "per_group_token" or weight_quant == "per_group":
+            ops.check_gemm_group_size(module.in_features, group_size)
         self.module = module
         self.bias = module.bias
         self.group_size = group_size
@@ -114,13 +123,45 @@ class ActQuantWrapper(torch.nn.Module):
         self.quantize_output = False
         self.quantize_input = False
         self.pre_signs = None
-        self.qweight, self.w_scale = None, None
+        self._pre_k, self._pre_hadk = 1, None
+        self.register_buffer("qweight", None)            # int8 codes and fp32 scales of the weight: saved in checkpoints
+        self.register_buffer("w_scale", None)
         if weight_quant in ops.WEIGHT_GRANULARITY:
             out = ops.quantize_weight(module.weight.data, ops.WEIGHT_GRANULARITY[weight_quant], group_size,
                                       codes=True, fake_quant=True, n_bits=n_bit)
             module.weight.data.copy_(out["fq"])          # the wrapped Linear keeps the fake-quantized weight
             self.qweight, self.w_scale = out["q"], out["scale"]
         self.weight = module.weight
+
+    # -- checkpoints ---------------------------------------------------------------------------
+    _FLAGS = ("K", "online_full_had", "online_partial_had", "had_dim", "fp32_had", "quantize_output", "quantize_input",
+              "group_size", "n_bits", "act_quant_name", "weight_quant_name", "_pre_k")
+
+    def get_extra_state(self):
+        """The rotation flags a checkpoint must carry next to the tensors (weight codes and scales,
+        the wrapped Linear, ``had_K``): which online transform runs, its factor order and head width,
+        and the sign vector / factor of a folded ``x @ Q``."""
+        state = {"kind": "ActQuantWrapper"}
+        state.update({k: getattr(self, k) for k in self._FLAGS})
+        state["pre_signs"] = None if self.pre_signs is None else self.pre_signs.detach().cpu()
+        state["pre_hadk"] = None if self._pre_hadk is None else self._pre_hadk.detach().cpu()
+        return state
+
+    def set_extra_state(self, state):
+        for k in self._FLAGS:
+            setattr(self, k, state[k])
+        dev = self.module.weight.device
+        self.pre_signs = None if state["pre_signs"] is None else state["pre_signs"].to(dev)
+        self._pre_hadk = None if state["pre_hadk"] is None else state["pre_hadk"].to(dev)
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        dev = self.module.weight.device
+        for name, dtype in (("qweight", torch.int8), ("w_scale", torch.float32), ("had_K", None)):
+            t = state_dict.get(prefix + name)
+            cur = self._buffers.get(name)
+            if t is not None and (cur is None or cur.shape != t.shape or cur.dtype != t.dtype):
+                self._buffers[name] = torch.empty(t.shape, dtype=t.dtype if dtype is None else dtype, device=dev)
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
 
     def extra_repr(self) -> str:
         return f"Activation Quantization: {self.act_quant_name}"
@@ -130,6 +171,14 @@ class ActQuantWrapper(torch.nn.Module):
 
     def _hadamard_spec(self, x):
         signs = self.pre_signs
+        if (self.online_full_had or self.online_partial_had) and not self.fp32_had and int(self.K) > 1:
+            # quarot/utils.py:260-261,280-288: without fp32_had the reference runs the power-of-two part in the
+            # fast_hadamard_transform library, rounds to the tensor dtype, and mixes the K chunks with a matmul in
+            # that dtype (a second rounding).  The kernel here evaluates the whole transform in fp32 and rounds
+            # once; rather than silently returning differently rounded values it asks for the mode it implements.
+            raise NotImplementedError(
+                f"online Hadamard with an explicit order-{int(self.K)} factor is implemented in fp32 with one rounding: "
+                "construct the rotation with fp32_had=True")
         if self.online_full_had or signs is not None:
             hk = None if self.K == 1 or self.had_K is None else self.had_K.to(x.device)
             if not self.online_full_had:

@@ -368,3 +368,88 @@ def test_attention_entry_rejects_bad_arguments(cuda_device):
         ops.set_gemm_pair_mode(7)
     prev = ops.set_gemm_pair_mode(ops.GEMM_PAIR_AUTO)
     assert ops.set_gemm_pair_mode(prev) == ops.GEMM_PAIR_AUTO
+
+
+# ---- packed checkpoints (quant/e2e_quant.py:10-14, RTN_quantization/Smooth_sam.py:126-142) -------
+
+def test_packed_checkpoint_round_trip_w8a8(cuda_device, tmp_path):
+    """save -> load into a float skeleton with other weights -> identical embeddings; the file
+    holds int8 codes and scales for the linears, not float weights."""
+    from sam_quantization_b200.RTN_quantization import (W8A8Linear, get_act_scales_sam,
+                                                        replace_linear_with_target_and_quantize, smooth_sam)
+    from sam_quantization_b200.checkpoint import load_quantized, save_quantized
+    from sam_quantization_b200.sam_encoder import build_encoder
+    dev = cuda_device
+    mine, _ = _tiny_pair(dev, torch.float16, torch.bfloat16)
+    scales = get_act_scales_sam(mine, [tiny_images(seed=200).to(dev, torch.float16)])
+    smooth_sam(mine, scales, alpha=0.5)
+    replace_linear_with_target_and_quantize(mine, W8A8Linear, 8, ["proj"], weight_quant="per_group", act_quant="per_token",
+                                            quantize_output=True, group_size=32)
+    img = tiny_images().to(dev, torch.float16)
+    with torch.no_grad():
+        want = mine(img)
+    path = str(tmp_path / "w8a8.pt")
+    save_quantized(mine, path)
+    blob = torch.load(path, map_location="cpu")
+    sd = blob["state_dict"]
+    assert sd["image_encoder.blocks.0.attn.qkv.qweight"].dtype == torch.int8
+    assert sd["image_encoder.blocks.0.attn.qkv.w_scale"].shape == (3 * 64, 2)          # [N, K / group]
+    assert "image_encoder.blocks.0.attn.qkv.weight" not in sd
+    assert "image_encoder.blocks.0.attn.proj.weight" in sd                             # excluded by name: still a Linear
+    fresh = build_encoder(seed=99, dtype=torch.float16, attn_dtype=torch.bfloat16, device=dev, **TINY)
+    load_quantized(fresh, path)
+    lin = fresh.image_encoder.blocks[1].mlp.lin1
+    assert isinstance(lin, W8A8Linear) and lin.weight_quant_name == "per_group" and lin.quantize_output and lin.group_size == 32
+    assert isinstance(fresh.image_encoder.blocks[1].attn.proj, torch.nn.Linear)
+    with torch.no_grad():
+        assert torch.equal(fresh(img), want)
+
+
+def test_packed_checkpoint_round_trip_quarot(cuda_device, tmp_path):
+    """The rotation flags (which online transform, head width, the folded sign vector) travel with
+    the checkpoint: a float skeleton loaded from it reproduces the rotated model bit for bit."""
+    from sam_quantization_b200.checkpoint import load_quantized, save_quantized
+    from sam_quantization_b200.quarot import rotate_sam, utils as qutils
+    from sam_quantization_b200.sam_encoder import build_encoder
+    dev = cuda_device
+    mine, _ = _tiny_pair(dev, torch.float16, torch.bfloat16)
+    args = types.SimpleNamespace(hidden_size_image_en=64, num_attention_head_image_en=4, hidden_size_mask_de=256,
+                                 num_attention_head_mask_de=8, rotate_mode="hadamard", device=str(dev), seed=123, fp32_had=True)
+    cfg = types.SimpleNamespace(n_bits=8, weight_quant="per_channel", act_quant="per_token", group_size=None,
+                                quantize_output=False, quantize_input=True)
+    rotate_sam(mine, args, cfg)
+    img = tiny_images().to(dev, torch.float16)
+    with torch.no_grad():
+        want = mine(img)
+    path = str(tmp_path / "quarot.pt")
+    save_quantized(mine, path)
+    fresh = build_encoder(seed=98, dtype=torch.float16, attn_dtype=torch.bfloat16, device=dev, **TINY)
+    load_quantized(fresh, path)
+    proj = fresh.image_encoder.blocks[0].attn.proj
+    assert isinstance(proj, qutils.ActQuantWrapper) and proj.online_partial_had and proj.had_dim == 16 and proj.quantize_input
+    assert fresh.image_encoder.blocks[0].mlp.lin2.online_full_had
+    assert fresh.image_encoder.blocks[0].attn.qkv.pre_signs is not None
+    with torch.no_grad():
+        assert torch.equal(fresh(img), want)
+
+
+def test_reference_format_state_dict_loads_into_w8a8linear(cuda_device):
+    """A state dict written by the reference's class (a float ``weight`` [N, K] and a ``bias`` of
+    shape [1, N], RTN_quantization/per_tensor_channel_group.py:111-128) loads: the weight is
+    quantized on the way in, and assigning ``module.weight`` re-quantizes."""
+    from sam_quantization_b200.RTN_quantization import W8A8Linear
+    g = torch.Generator().manual_seed(8)
+    w = (torch.randn(72, 256, generator=g) * 0.02).half()
+    b = (torch.randn(72, generator=g) * 0.01).half()
+    x = torch.randn(50, 256, generator=g).half().to(cuda_device)
+    lin = torch.nn.Linear(256, 72).half().to(cuda_device)
+    lin.weight.data, lin.bias.data = w.clone().to(cuda_device), b.clone().to(cuda_device)
+    want = W8A8Linear.from_float(lin, 8)(x)
+    mod = W8A8Linear(256, 72).to(cuda_device)
+    mod.load_state_dict({"weight": w.clone(), "bias": b.clone().view(1, -1)})
+    assert torch.equal(mod(x), want)
+    mod2 = W8A8Linear(256, 72).to(cuda_device)
+    mod2.bias = b.clone().to(cuda_device)
+    mod2.weight = w.clone().to(cuda_device)
+    assert torch.equal(mod2(x), want)
+    assert torch.equal(mod2.weight, mod.weight)

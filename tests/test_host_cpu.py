@@ -138,3 +138,39 @@ def test_monkeypatch_behaves_like_the_reference_module():
     spec.loader.exec_module(ref)
     from sam_quantization_b200.quarot import monkeypatch as mine
     assert _exercise(mine) == _exercise(ref)
+
+
+# ---- argument checks that run before any kernel --------------------------------------------------
+
+def test_group_sizes_the_int8_gemm_cannot_run_are_rejected_at_construction():
+    """The reference's float path takes any group size that divides the width; the int8 GEMM needs
+    multiples of 32 and at most 160 groups, and says so when the module is built, not at the
+    first forward."""
+    from sam_quantization_b200.RTN_quantization import W8A8Linear
+    from sam_quantization_b200.quarot.utils import ActQuantWrapper
+    lin = nn.Linear(96, 8)
+    with pytest.raises(ValueError, match="multiples of 32"):
+        W8A8Linear.from_float(lin, 8, weight_quant="per_group", act_quant="per_token", group_size=24)
+    with pytest.raises(ValueError, match="multiples of 32"):
+        W8A8Linear.from_float(lin, 8, weight_quant="per_channel", act_quant="per_group_token", group_size=48)
+    with pytest.raises(ValueError, match="multiples of 32"):
+        ActQuantWrapper(lin, act_quant="per_group_token", weight_quant="per_group", group_size=16)
+    with pytest.raises(AssertionError):
+        W8A8Linear.from_float(lin, 8, weight_quant="per_group", group_size=64)       # does not divide 96
+    with pytest.raises(ValueError, match="160 groups"):
+        W8A8Linear.from_float(nn.Linear(32 * 161, 8), 8, weight_quant="per_group", group_size=32)
+
+
+def test_half_precision_hadamard_with_an_explicit_factor_is_refused():
+    """``fp32_had=False`` with a non-power-of-two transform length raises instead of returning the
+    one-rounding fp32 result under the name of the reference's two-rounding half path."""
+    from sam_quantization_b200.quarot.utils import ActQuantWrapper
+    w = ActQuantWrapper(nn.Linear(96, 8), weight_quant=None)
+    w.online_full_had, w.K, w.fp32_had = True, 12, False
+    with pytest.raises(NotImplementedError, match="fp32_had=True"):
+        w._hadamard_spec(torch.zeros(2, 96))
+    w.fp32_had = True
+    w.had_K = torch.ones(12, 12)
+    assert w._hadamard_spec(torch.zeros(2, 96)).had_k == 12
+    w.K, w.fp32_had, w.had_K = 1, False, None           # powers of two: both settings run the same kernel
+    assert w._hadamard_spec(torch.zeros(2, 96)).had_k == 1
