@@ -306,6 +306,19 @@ int samq_attn_global(const void* qkv, const void* vt, const void* rel_all, int d
 int samq_attn_windowed(const void* qkv, int dtype, int64_t windows, int H, int W, int num_heads, int head_dim,
                        const void* rel_table, int table_rows, float scale, void* out, void* stream);
 
+/* The same attention for SAM's 14 x 14 windows on the tensor cores, the default for windowed
+ * blocks (replaces quarot/model_utils.py:158-170 on the windows of quarot/model_utils.py:15-36):
+ * a persistent tcgen05 kernel walks (window, head) items; Q, K, V are read in place from
+ * `qkv` [windows * 196, 3C] by TMA; the products of each query with the two relative-position
+ * tables come out of the same MMA as its scores; softmax is exact two-pass in fp32; nothing but
+ * `out` [windows * 196, C] is written.
+ * rel_table : [56, head_dim] of the qkv dtype: the 27 rows of rel_pos_h, the 27 rows of rel_pos_w,
+ *             two zero rows (table_rows must be 56).
+ * head_dim 64 or 80; dtype SAMQ_F16 or SAMQ_BF16; qkv, rel_table and out 16-byte aligned.
+ * status : optional device int32, set non-zero if a bounded wait inside the kernel ran out. */
+int samq_attn_window14(const void* qkv, const void* rel_table, int table_rows, int dtype, int64_t windows,
+                       int num_heads, int head_dim, float scale, void* out, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

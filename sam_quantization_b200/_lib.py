@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = (
     "samq_attn_windowed",
     "samq_attn_transpose_v",
     "samq_attn_global",
+    "samq_attn_window14",
 )
 
 
@@ -151,6 +152,11 @@ def load() -> ctypes.CDLL:
     lib.samq_attn_windowed.argtypes = [
         c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int,   # qkv, dtype, windows, H, W, heads, head_dim
         c_void_p, c_int, c_float, c_void_p, c_void_p,           # rel_table, table_rows, scale, out, stream
+    ]
+    lib.samq_attn_window14.restype = c_int
+    lib.samq_attn_window14.argtypes = [
+        c_void_p, c_void_p, c_int, c_int, c_int64,              # qkv, rel_table, table_rows, dtype, windows
+        c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,    # heads, head_dim, scale, out, status, stream
     ]
     _lib = lib
     return lib

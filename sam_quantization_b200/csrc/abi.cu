@@ -56,6 +56,8 @@ int attn_transpose_v_dispatch(const void* qkv, int dtype, int64_t units, int H, 
 int attn_global_dispatch(const void* qkv, const void* vt, const void* rel_all, int dtype, int64_t images, int rel_pitch,
                          int H, int W, int heads, int head_dim, float scale, void* out, int32_t* status, void* stream);
 
+int attn_window14_dispatch(const void* qkv, const void* table, int table_rows, int dtype, int64_t windows, int heads, int head_dim,
+                           float scale, void* out, int32_t* status, void* stream);
 int attn_window_dispatch(const void* qkv, int dtype, int64_t windows, int H, int W, int nh, int d,
                          const void* table, int table_rows, float scale, void* out, void* stream);
 
@@ -123,6 +125,12 @@ int samq_attn_windowed(const void* qkv, int dtype, int64_t windows, int H, int W
                        const void* rel_table, int table_rows, float scale, void* out, void* stream)
 {
     return samq::attn_window_dispatch(qkv, dtype, windows, H, W, num_heads, head_dim, rel_table, table_rows, scale, out, stream);
+}
+
+int samq_attn_window14(const void* qkv, const void* rel_table, int table_rows, int dtype, int64_t windows,
+                       int num_heads, int head_dim, float scale, void* out, int32_t* status, void* stream)
+{
+    return samq::attn_window14_dispatch(qkv, rel_table, table_rows, dtype, windows, num_heads, head_dim, scale, out, status, stream);
 }
 
 int samq_attn_rel_bias(const void* rel_all, int dtype, int64_t images, int rel_pitch, int H, int W, int num_heads,

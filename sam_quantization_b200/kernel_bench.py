@@ -4,6 +4,7 @@
     python -m sam_quantization_b200.kernel_bench quant --M 65536 --K 1280 [--ln] [--gather] [--hadamard full]
     python -m sam_quantization_b200.kernel_bench attn  --windows 200 --H 14 --W 14 --heads 16 --head-dim 80
     python -m sam_quantization_b200.kernel_bench attn-global --images 8 --H 64 --heads 16 --head-dim 80
+    python -m sam_quantization_b200.kernel_bench attn-window14 --windows 200 --heads 16 --head-dim 80
     python -m sam_quantization_b200.kernel_bench sweep            # the W8A8 GEMM sweep: M x (K, N) x granularity
     python -m sam_quantization_b200.kernel_bench library --M 32768 --N 5120 --K 1280   # cuBLASLt int8 / fp16 bars
 
@@ -174,6 +175,27 @@ def bench_window_attention(windows, H, W, heads, head_dim, dtype=torch.bfloat16,
             "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), "tflops": round(flops / ms / 1e9, 1)}
 
 
+def bench_window14(windows, heads, head_dim, dtype=torch.bfloat16, iters=50, warmup=10):
+    """samq_attn_window14 on [windows*196, 3C]; GB/s over the algorithmic bytes (q, k, v read, out written)."""
+    dev = torch.device("cuda")
+    C = heads * head_dim
+    nbuf = 3
+    qkv = [torch.randn((windows * 196, 3 * C), device=dev, dtype=dtype) for _ in range(nbuf)]
+    rh = (torch.randn((27, head_dim), device=dev) * 0.02).to(dtype)
+    rw = (torch.randn((27, head_dim), device=dev) * 0.02).to(dtype)
+    table = ops.rel_pos_table(rh, rw, dtype, dev)
+
+    def run(i):
+        ops.attn_window14(qkv[i % nbuf], windows, heads, rh, rw, head_dim ** -0.5, table=table)
+
+    ms = _time(run, iters, warmup)
+    ops.check_status()
+    nbytes = windows * 196 * 4 * C * qkv[0].element_size()
+    flops = 4.0 * windows * heads * 196 * 196 * head_dim
+    return {"kernel": "attn_window14", "windows": windows, "heads": heads, "head_dim": head_dim, "ms": round(ms, 5),
+            "gbs": round(nbytes / ms / 1e6, 1), "tflops": round(flops / ms / 1e9, 1)}
+
+
 def bench_global_attention(images, H, heads, head_dim, dtype=torch.bfloat16, iters=20, warmup=5, W=64):
     dev = torch.device("cuda")
     L, C = H * W, heads * head_dim
@@ -274,6 +296,12 @@ def main():
     a.add_argument("--head-dim", dest="head_dim", type=int, default=80)
     a.add_argument("--iters", type=int, default=50)
     a.add_argument("--warmup", type=int, default=10)
+    aw = sub.add_parser("attn-window14")
+    aw.add_argument("--windows", type=int, default=200)
+    aw.add_argument("--heads", type=int, default=16)
+    aw.add_argument("--head-dim", dest="head_dim", type=int, default=80)
+    aw.add_argument("--iters", type=int, default=50)
+    aw.add_argument("--warmup", type=int, default=10)
     ag = sub.add_parser("attn-global")
     ag.add_argument("--images", type=int, default=8)
     ag.add_argument("--H", type=int, default=64)
@@ -303,6 +331,8 @@ def main():
         print(json.dumps(bench_gemm(args.M, args.N, args.K, args.gelu, args.residual, args.w_gran, iters=args.iters, warmup=args.warmup)))
     elif args.cmd == "attn":
         print(json.dumps(bench_window_attention(args.windows, args.H, args.W, args.heads, args.head_dim, iters=args.iters, warmup=args.warmup)))
+    elif args.cmd == "attn-window14":
+        print(json.dumps(bench_window14(args.windows, args.heads, args.head_dim, iters=args.iters, warmup=args.warmup)))
     elif args.cmd == "attn-global":
         print(json.dumps(bench_global_attention(args.images, args.H, args.heads, args.head_dim, iters=args.iters, warmup=args.warmup, W=args.W)))
     elif args.cmd == "quant":

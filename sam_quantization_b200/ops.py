@@ -497,6 +497,35 @@ def attn_global(qkv: torch.Tensor, units: int, H: int, W: int, num_heads: int, r
     return out
 
 
+def attn_window14_supported(H: int, W: int, head_dim: int, dtype) -> bool:
+    """Shapes ``samq_attn_window14`` is built for: SAM's 14 x 14 windows, head width 64 or 80."""
+    return H == 14 and W == 14 and head_dim in (64, 80) and dtype in (torch.float16, torch.bfloat16)
+
+
+def attn_window14(qkv: torch.Tensor, windows: int, num_heads: int, rel_pos_h: torch.Tensor, rel_pos_w: torch.Tensor,
+                  scale: float, table: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of 14 x 14 windows with the decomposed relative-position bias in one tensor-core
+    kernel (``samq_attn_window14``): ``qkv`` [windows*196, 3C] -> [windows*196, C], same dtype.
+    ``table`` is an optional cached ``rel_pos_table`` of the two [27, d] tables (56 rows)."""
+    _require_cuda(qkv, "qkv")
+    lib = _lib.load()
+    tokens, three_c = qkv.shape
+    C = three_c // 3
+    d = C // num_heads
+    if tokens != windows * 196 or not qkv.is_contiguous():
+        raise ValueError("qkv must be a contiguous [windows*196, 3C] tensor")
+    if rel_pos_h.shape != (27, d) or rel_pos_w.shape != (27, d):
+        raise ValueError("relative position tables must be [27, d]")
+    if table is None:
+        table = rel_pos_table(rel_pos_h, rel_pos_w, qkv.dtype, qkv.device)
+    out = torch.empty((tokens, C), dtype=qkv.dtype, device=qkv.device)
+    esz = qkv.element_size()
+    with torch.cuda.device(qkv.device), _Timed("attn_window14", 4 * tokens * C * esz):
+        _lib.check(lib.samq_attn_window14(_ptr(qkv), _ptr(table), table.shape[0], _DTYPE_CODE[qkv.dtype], windows, num_heads, d,
+                                          float(scale), _ptr(out), _ptr(status_word(qkv.device)), _stream()))
+    return out
+
+
 def attn_windowed_supported(H: int, W: int, head_dim: int) -> bool:
     """Shapes ``samq_attn_windowed`` has a variant for."""
     L, J = H * W, 2 * H - 1 + 2 * W - 1

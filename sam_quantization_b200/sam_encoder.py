@@ -142,9 +142,12 @@ class Attention(nn.Module):
         # kernel (samq_attn_global): scores and the relative-position bias stay on chip instead of going through
         # a [heads, L, L] bias tensor or augmented q / k rows
         self.fused_global_kernel = True
-        # the same kernel for windows: correct, but one short-lived CTA per (window, head, 128 queries) spends most
-        # of its ~10 us on set-up and pipeline fill, so augmented rows + the library attention stay the default
+        # the same kernel for windows other than 14 x 14: correct, but one short-lived CTA per (window, head,
+        # 128 queries) spends most of its ~10 us on set-up and pipeline fill; off by default
         self.tc_windows = False
+        # 14 x 14 windows (every windowed block of SAM) in the persistent tensor-core kernel samq_attn_window14:
+        # q, k, v read in place, the table products computed by the same MMA as the scores
+        self.window14_kernel = True
         self._onehot = {}
         if use_rel_pos:
             assert input_size is not None
@@ -204,6 +207,9 @@ class Attention(nn.Module):
         extra = H + W
         if self._native(qkv, d, H, W):
             from . import ops
+            if self.window14_kernel and ops.attn_window14_supported(H, W, d, qkv.dtype):
+                return ops.attn_window14(qkv, B, nh, self.rel_pos_h, self.rel_pos_w, self.scale,
+                                         table=self._rel_table(qkv.dtype, qkv.device))
             if self.fused_window_kernel and ops.attn_windowed_supported(H, W, d):
                 return ops.attn_windowed(qkv, B, H, W, nh, self.rel_pos_h, self.rel_pos_w, self.scale,
                                          table=self._rel_table(qkv.dtype, qkv.device))

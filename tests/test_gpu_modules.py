@@ -258,6 +258,7 @@ def test_attention_prep_kernels_against_torch_path(cuda_device, dtype, H, W, dim
         B = 3
         qkv = torch.randn(B * H * W, 3 * dim, device=cuda_device, dtype=dtype)
         attn.native_prep = True
+        attn.window14_kernel = False                  # this test is about the input-building kernels
         a = attn.attend_flat(qkv, B, H, W)
         attn.native_prep = False
         b = attn.attend_flat(qkv, B, H, W)
@@ -281,6 +282,7 @@ def test_windowed_attention_kernel_variants_agree(cuda_device, dtype, H, W, dim,
         attn.rel_pos_w.normal_(0, 0.3)
         B = 5
         qkv = torch.randn(B * H * W, 3 * dim, device=cuda_device, dtype=dtype)
+        attn.window14_kernel = False
         outs = []
         for native, fused in ((True, True), (True, False), (False, False)):
             attn.native_prep, attn.fused_window_kernel = native, fused
@@ -308,6 +310,7 @@ def test_global_attention_kernel_against_fp32_reference(cuda_device, dtype, H, W
         attn.rel_pos_w.normal_(0, 0.3)
         qkv = torch.randn(B * H * W, 3 * dim, device=cuda_device, dtype=dtype)
         qkv[:, :dim] *= 2.0                                        # sharper rows: the running maximum must move
+        attn.window14_kernel = False
         attn.fused_global_kernel = attn.tc_windows = True
         a = attn.attend_flat(qkv, B, H, W)
         torch.cuda.synchronize()
@@ -335,6 +338,78 @@ def test_global_attention_kernel_against_fp32_reference(cuda_device, dtype, H, W
     assert cosine(a, ref) > 0.9999
     # keeping the bias in fp32 on chip must not be less accurate than rounding it to 16 bits in memory
     assert 1.0 - cosine(a, ref) <= 1.25 * (1.0 - cosine(b, ref)) + 1e-6
+
+
+def _fp32_window_attention(qkv, attn, B, H, W, nh, d):
+    dim = nh * d
+    dev = qkv.device
+    q, k, v = qkv.float().view(B, H * W, 3, nh, d).permute(2, 0, 3, 1, 4)
+    s = (q * attn.scale) @ k.transpose(-1, -2)
+    rq = q.view(B, nh, H, W, d)
+    Rh = attn.rel_pos_h.float()[(torch.arange(H)[:, None] - torch.arange(H)[None, :] + H - 1).to(dev)]
+    Rw = attn.rel_pos_w.float()[(torch.arange(W)[:, None] - torch.arange(W)[None, :] + W - 1).to(dev)]
+    rel_h = torch.einsum("bnhwc,hkc->bnhwk", rq, Rh)
+    rel_w = torch.einsum("bnhwc,wkc->bnhwk", rq, Rw)
+    s = (s.view(B, nh, H, W, H, W) + rel_h[..., :, None] + rel_w[..., None, :]).view(B, nh, H * W, H * W)
+    return (s.softmax(-1) @ v).permute(0, 2, 1, 3).reshape(B * H * W, dim)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("dim,nh,B", [(160, 2, 1), (160, 2, 7), (128, 2, 3), (1280, 16, 25), (768, 12, 40), (80, 1, 401)])
+def test_window14_attention_kernel_against_fp32_reference(cuda_device, dtype, dim, nh, B):
+    """The persistent tensor-core kernel for 14 x 14 windows (q, k, v read in place, the table
+    products from the same MMA as the scores, exact two-pass softmax) against the same attention in
+    fp32 torch ops and against the augmented-row route through the library attention.  The larger
+    cases give every CTA several (window, head) items, so buffers and barrier phases wrap."""
+    from sam_quantization_b200 import ops
+    from sam_quantization_b200.sam_encoder import Attention
+    H = W = 14
+    torch.manual_seed(dim + B)
+    attn = Attention(dim, nh, use_rel_pos=True, input_size=(H, W)).to(cuda_device, dtype)
+    d = dim // nh
+    with torch.no_grad():
+        attn.rel_pos_h.normal_(0, 0.3)
+        attn.rel_pos_w.normal_(0, 0.3)
+        qkv = torch.randn(B * H * W, 3 * dim, device=cuda_device, dtype=dtype)
+        qkv[:, :dim] *= 2.0
+        assert ops.attn_window14_supported(H, W, d, dtype)
+        a = attn.attend_flat(qkv, B, H, W)
+        torch.cuda.synchronize()
+        ops.check_status()
+        a2 = attn.attend_flat(qkv, B, H, W)                        # a second launch reproduces the first bit for bit
+        attn.window14_kernel = False
+        b = attn.attend_flat(qkv, B, H, W)
+        ref = _fp32_window_attention(qkv, attn, B, H, W, nh, d)
+    assert a.shape == (B * H * W, dim) and a.dtype == dtype
+    assert torch.isfinite(a.float()).all()
+    assert torch.equal(a, a2)
+    tol = 3e-2 if dtype == torch.bfloat16 else 4e-3
+    assert rel_err(a.float(), ref) < tol
+    assert cosine(a, ref) > 0.9999
+    # the table products stay in fp32 on chip: not less accurate than the route that rounds them to 16 bits
+    assert 1.0 - cosine(a, ref) <= 1.25 * (1.0 - cosine(b, ref)) + 1e-6
+    # every window separately (a wrong window / head mapping would hide in a global norm)
+    per_window = (a.float() - ref).view(B, -1).norm(dim=1) / ref.view(B, -1).norm(dim=1)
+    assert float(per_window.max()) < 2 * tol
+
+
+def test_window14_entry_rejects_bad_arguments(cuda_device):
+    import ctypes
+    from sam_quantization_b200 import _lib
+    lib = _lib.load()
+    dev = cuda_device
+    qkv = torch.zeros((196, 3 * 80), dtype=torch.bfloat16, device=dev)
+    tab = torch.zeros((56, 80), dtype=torch.bfloat16, device=dev)
+    out = torch.zeros((196, 80), dtype=torch.bfloat16, device=dev)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    assert lib.samq_attn_window14(P(qkv), P(tab), 56, _lib.BF16, 1, 1, 80, 0.1, P(out), None, None) == 0
+    assert lib.samq_attn_window14(P(qkv), P(tab), 54, _lib.BF16, 1, 1, 80, 0.1, P(out), None, None) != 0      # table not padded to 56 rows
+    assert b"56" in lib.samq_last_error_string()
+    assert lib.samq_attn_window14(P(qkv), P(tab), 56, _lib.BF16, 1, 1, 96, 0.1, P(out), None, None) != 0      # head widths 64 and 80 only
+    assert lib.samq_attn_window14(P(qkv), P(tab), 56, _lib.F32, 1, 1, 80, 0.1, P(out), None, None) != 0
+    assert lib.samq_attn_window14(None, P(tab), 56, _lib.BF16, 1, 1, 80, 0.1, P(out), None, None) != 0
+    assert lib.samq_attn_window14(P(qkv), P(tab), 56, _lib.BF16, 0, 1, 80, 0.1, P(out), None, None) == 0       # no windows: nothing to do
+    torch.cuda.synchronize()
 
 
 def test_attention_entry_rejects_bad_arguments(cuda_device):
