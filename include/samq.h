@@ -232,6 +232,19 @@ int samq_gemm_i8(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
                  int activation, void* out, int out_dtype, int64_t ldo,
                  int32_t* status, void* stream);
 
+/* Self-test of the GEMM kernel's failure path.  The reference reports a failed native call by
+ * throwing from `ensure()` (quant/qgemm/include/common.h:16-23) after the fact; a persistent
+ * tensor-core pipeline can instead stall (a load that never lands), so every wait inside these
+ * kernels is bounded and a kernel that gives up raises `status` and returns on its own.  This
+ * entry runs the raw-int32 GEMM (A [M,K], W [N,K] -> out [M,N], M*N <= 2^22) with a stall made
+ * on the host side of the launch: the producer warp never loads k-block `skip_kblock` of each
+ * CTA's first tile, and waits give up after `wait_limit_cycles` SM cycles (1e5 .. 4e9).  No
+ * fault, trap or endless loop is involved: the kernel drains its roles, frees its tensor memory,
+ * sets *status = 1 and returns; `out` is then incomplete.  The next samq_gemm_i8 call is unaffected. */
+int samq_gemm_i8_stall_selftest(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
+                                int64_t M, int64_t N, int64_t K, int32_t* out, int64_t ldo,
+                                int skip_kblock, long long wait_limit_cycles, int32_t* status, void* stream);
+
 /* Process-wide choice between the two implementations of samq_gemm_i8 for row / tensor scales
  * (no reference counterpart: the reference has a single cuBLAS-style path):
  *   NEVER  - one CTA per 128 x 256 output tile;

@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "samq_act_quant_per_tensor_static",
     "samq_gemm_i8",
     "samq_gemm_set_pair_mode",
+    "samq_gemm_i8_stall_selftest",
     "samq_attn_window_prep",
     "samq_attn_rel_bias",
     "samq_attn_windowed",
@@ -126,6 +127,11 @@ def load() -> ctypes.CDLL:
         c_void_p, c_void_p, c_int64,                     # bias, residual, ldr
         c_int, c_void_p, c_int, c_int64,                 # activation, out, out_dtype, ldo
         c_void_p, c_void_p,                              # status, stream
+    ]
+    lib.samq_gemm_i8_stall_selftest.restype = c_int
+    lib.samq_gemm_i8_stall_selftest.argtypes = [
+        c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64,   # A, lda, W, ldw, M, N, K
+        c_void_p, c_int64, c_int, ctypes.c_longlong, c_void_p, c_void_p,   # out, ldo, skip_kblock, wait_limit_cycles, status, stream
     ]
     lib.samq_gemm_set_pair_mode.restype = c_int
     lib.samq_gemm_set_pair_mode.argtypes = [c_int]

@@ -56,6 +56,9 @@ int attn_transpose_v_dispatch(const void* qkv, int dtype, int64_t units, int H, 
 int attn_global_dispatch(const void* qkv, const void* vt, const void* rel_all, int dtype, int64_t images, int rel_pitch,
                          int H, int W, int heads, int head_dim, float scale, void* out, int32_t* status, void* stream);
 
+int gemm_i8_stall_selftest_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int64_t M, int64_t N, int64_t K,
+                                    int32_t* out, int64_t ldo, int skip_kblock, long long wait_limit_cycles,
+                                    int32_t* status, void* stream);
 int attn_window14_dispatch(const void* qkv, const void* table, int table_rows, int dtype, int64_t windows, int heads, int head_dim,
                            float scale, void* out, int32_t* status, void* stream);
 int attn_window_dispatch(const void* qkv, int dtype, int64_t windows, int H, int W, int nh, int d,
@@ -173,6 +176,13 @@ int samq_gemm_i8(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
                                            bias, residual, ldr, activation, out, out_dtype, ldo, status, stream);
     return samq::gemm_i8_dispatch(A, lda, W, ldw, M, N, K, a_scale, a_gran, w_scale, w_gran, group_size,
                                   bias, residual, ldr, activation, out, out_dtype, ldo, status, stream);
+}
+
+int samq_gemm_i8_stall_selftest(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int64_t M, int64_t N, int64_t K,
+                                int32_t* out, int64_t ldo, int skip_kblock, long long wait_limit_cycles,
+                                int32_t* status, void* stream)
+{
+    return samq::gemm_i8_stall_selftest_dispatch(A, lda, W, ldw, M, N, K, out, ldo, skip_kblock, wait_limit_cycles, status, stream);
 }
 
 int samq_gemm_set_pair_mode(int mode)

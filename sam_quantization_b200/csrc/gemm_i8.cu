@@ -70,6 +70,8 @@ struct GemmParams {
     int vec_ok;                                // rows of out/residual are 16-byte aligned
     int tma_store;                             // out is described by map_out: store through shared memory + TMA
     int32_t* status;
+    long long wait_limit;                      // cycles a pipeline wait may take before the kernel gives up
+    int skip_kblock;                           // self-test only: the producer never loads this k-block of its first tile (-1: none)
 };
 
 // OutT = __half | __nv_bfloat16 | float | int32_t (raw accumulators); GELU / RES compile the
@@ -123,12 +125,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int m0 = (tile / n_blocks) * BM;
                 const int n0 = (tile % n_blocks) * BN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, p.wait_limit)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&ctl->full[stage]);
                     const uint32_t sa = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
-                    mbar_expect_tx(bar, STAGE_BYTES);
-                    tma_load_2d(sa, &map_a, bar, kb * BK, m0);
-                    tma_load_2d(sa + A_BYTES, &map_w, bar, kb * BK, n0);
+                    if (!(kb == p.skip_kblock && tile == (int)blockIdx.x)) {      // the self-test leaves one stage unfilled
+                        mbar_expect_tx(bar, STAGE_BYTES);
+                        tma_load_2d(sa, &map_a, bar, kb * BK, m0);
+                        tma_load_2d(sa + A_BYTES, &map_w, bar, kb * BK, n0);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -145,11 +149,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                if (!mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort_flag, p.wait_limit)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag, p.wait_limit)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t sa = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
                     const uint64_t adesc = make_smem_desc(sa);
@@ -203,7 +207,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
             // after a failed wait keep visiting the named barrier above so no warp is left behind
-            if (ok && !mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag)) ok = false;
+            if (ok && !mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag, p.wait_limit)) ok = false;
             if (!ok) continue;
             tcgen05_fence_after();
             const int row = m0 + quad * 32 + lane;
@@ -375,11 +379,44 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap&
 
 }  // namespace
 
+// skip_kblock / wait_limit_cycles: see samq_gemm_i8_stall_selftest; the product entry passes -1 / 0.
+static int gemm_i8_run(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
+                       int64_t M, int64_t N, int64_t K,
+                       const float* a_scale, int a_gran, const float* w_scale, int w_gran, int group_size,
+                       const void* bias, const void* residual, int64_t ldr, int activation,
+                       void* out, int out_dtype, int64_t ldo, int32_t* status, void* stream,
+                       int skip_kblock, long long wait_limit_cycles);
+
 int gemm_i8_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
                      int64_t M, int64_t N, int64_t K,
                      const float* a_scale, int a_gran, const float* w_scale, int w_gran, int group_size,
                      const void* bias, const void* residual, int64_t ldr, int activation,
                      void* out, int out_dtype, int64_t ldo, int32_t* status, void* stream)
+{
+    return gemm_i8_run(A, lda, W, ldw, M, N, K, a_scale, a_gran, w_scale, w_gran, group_size, bias, residual, ldr, activation,
+                       out, out_dtype, ldo, status, stream, -1, 0);
+}
+
+int gemm_i8_stall_selftest_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int64_t M, int64_t N, int64_t K,
+                                    int32_t* out, int64_t ldo, int skip_kblock, long long wait_limit_cycles,
+                                    int32_t* status, void* stream)
+{
+    if (status == nullptr) return fail(SAMQ_ERR_BAD_ARG, "the stall self-test reports through the status word: it must not be null");
+    if (skip_kblock < 0 || skip_kblock >= (K + BK - 1) / BK)
+        return fail(SAMQ_ERR_BAD_ARG, "skip_kblock %d is not a k-block of K=%lld", skip_kblock, (long long)K);
+    if (wait_limit_cycles < 100000 || wait_limit_cycles > WAIT_LIMIT_CYCLES)
+        return fail(SAMQ_ERR_BAD_ARG, "wait_limit_cycles must lie between 1e5 and %lld", WAIT_LIMIT_CYCLES);
+    if (M * N > (int64_t)1 << 22) return fail(SAMQ_ERR_TOO_LARGE, "the stall self-test is meant for a small GEMM");
+    return gemm_i8_run(A, lda, W, ldw, M, N, K, nullptr, SAMQ_GRAN_ROW, nullptr, SAMQ_GRAN_ROW, 0, nullptr, nullptr, 0,
+                       SAMQ_ACT_NONE, out, SAMQ_I32, ldo, status, stream, skip_kblock, wait_limit_cycles);
+}
+
+static int gemm_i8_run(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
+                       int64_t M, int64_t N, int64_t K,
+                       const float* a_scale, int a_gran, const float* w_scale, int w_gran, int group_size,
+                       const void* bias, const void* residual, int64_t ldr, int activation,
+                       void* out, int out_dtype, int64_t ldo, int32_t* status, void* stream,
+                       int skip_kblock, long long wait_limit_cycles)
 {
     if (M < 0 || N <= 0 || K <= 0) return fail(SAMQ_ERR_BAD_ARG, "bad GEMM shape M=%lld N=%lld K=%lld",
                                                (long long)M, (long long)N, (long long)K);
@@ -412,6 +449,8 @@ int gemm_i8_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw,
     p.w_scale = w_scale; p.w_stride = (w_gran == SAMQ_GRAN_ROW) ? 1 : 0;
     p.bias = bias; p.residual = residual; p.ldr = ldr;
     p.out = out; p.ldo = ldo; p.activation = activation; p.status = status;
+    p.skip_kblock = skip_kblock;
+    p.wait_limit = wait_limit_cycles > 0 ? wait_limit_cycles : WAIT_LIMIT_CYCLES;
     const size_t esz = (out_dtype == SAMQ_F16 || out_dtype == SAMQ_BF16) ? 2 : 4;
     p.vec_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((ldo * esz) % 16 == 0) &&
                (residual == nullptr || (((reinterpret_cast<uintptr_t>(residual) & 15) == 0) && ((ldr * esz) % 16 == 0)));

@@ -31,14 +31,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait. Returns false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          long long limit_cycles = WAIT_LIMIT_CYCLES) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 255u) == 0) {
             if (*abort_flag != 0) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; return false; }
+            if (clock64() - t0 > limit_cycles) { *abort_flag = 1; return false; }
         }
     }
     return true;

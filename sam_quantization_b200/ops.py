@@ -390,6 +390,22 @@ def gemm_i8(a_q: torch.Tensor, w_q: torch.Tensor,
     return out.view(*lead, N)
 
 
+def gemm_stall_selftest(a_q: torch.Tensor, w_q: torch.Tensor, skip_kblock: int = 0, wait_limit_cycles: int = 2_000_000) -> torch.Tensor:
+    """Run ``samq_gemm_i8_stall_selftest``: the raw-int32 GEMM with one operand stage that the
+    producer never fills, so that a bounded wait inside the kernel runs out.  The kernel returns on
+    its own and raises the device status word (``check_status`` then raises); the returned tensor
+    is incomplete."""
+    _require_cuda(a_q, "a_q")
+    lib = _lib.load()
+    M, K = a_q.shape
+    N = w_q.shape[0]
+    out = torch.zeros((M, N), dtype=torch.int32, device=a_q.device)
+    with torch.cuda.device(a_q.device):
+        _lib.check(lib.samq_gemm_i8_stall_selftest(_ptr(a_q), a_q.stride(0), _ptr(w_q), w_q.stride(0), M, N, K, _ptr(out), N,
+                                                   int(skip_kblock), int(wait_limit_cycles), _ptr(status_word(a_q.device)), _stream()))
+    return out
+
+
 def rel_pos_table(rel_pos_h: torch.Tensor, rel_pos_w: torch.Tensor, dtype, device) -> torch.Tensor:
     """The rows of ``rel_pos_h`` followed by those of ``rel_pos_w`` as one [J, d] matrix of
     ``dtype`` (J rounded up to a multiple of 8, zero rows at the end)."""

@@ -260,3 +260,39 @@ def test_pair_unaligned_output_takes_direct_stores(cuda_device, pair_mode):
     ops.check_status()
     want = O.dequant_epilogue(O.int32_accumulators(a, w), sa, sw, None, None, None, "f16")
     assert np.all(np.abs(f32(y) - want) <= 2.0 ** -10 * np.maximum(np.abs(want), 1e-2) + 1e-6)
+
+
+# ---- the failure path: a bounded wait that runs out -----------------------------------------------
+
+def test_stalled_pipeline_gives_up_and_reports(cuda_device):
+    """A GEMM whose producer never fills one operand stage (a stall made on the host side of the
+    launch, no fault involved): the kernel's bounded waits run out after ~1 ms, it returns on its
+    own with the status word raised, ``check_status`` raises, and the next GEMM is exact."""
+    from sam_quantization_b200 import ops
+    from sam_quantization_b200._lib import SamqError
+    dev = cuda_device
+    g = torch.Generator().manual_seed(12)
+    a = torch.randint(-127, 128, (256, 1024), generator=g, dtype=torch.int8).to(dev)
+    w = torch.randint(-127, 128, (512, 1024), generator=g, dtype=torch.int8).to(dev)
+    want = (a.double() @ w.double().t()).to(torch.int32)
+    assert torch.equal(ops.gemm_i8(a, w, out_dtype=torch.int32), want)
+    ops.check_status()
+    for skip in (1, 6):                                    # a stage of the first trip round the ring, and of the second
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        out = ops.gemm_stall_selftest(a, w, skip_kblock=skip, wait_limit_cycles=2_000_000)
+        t1.record()
+        torch.cuda.synchronize()                           # the kernel came back by itself
+        assert t0.elapsed_time(t1) < 200.0                 # ~1 ms of waiting, nowhere near the 2 s default
+        assert int(ops.status_word(dev).item()) == 1
+        assert not torch.equal(out, want)                  # the tiles were never completed
+        with pytest.raises(RuntimeError, match="bounded wait"):
+            ops.check_status()
+        ops.check_status()                                 # reading the status cleared it
+        assert torch.equal(ops.gemm_i8(a, w, out_dtype=torch.int32), want)
+        ops.check_status()
+    with pytest.raises(SamqError):
+        ops.gemm_stall_selftest(a, w, skip_kblock=99)      # not a k-block of this GEMM
+    with pytest.raises(SamqError):
+        ops.gemm_stall_selftest(a, w, skip_kblock=0, wait_limit_cycles=10)
