@@ -46,9 +46,9 @@ def linear_ops_per_image(model_type: str) -> float:
 
 
 # DRAM bytes (read + write) of one int8-GEMM launch at M = 32768 rows, from `ncu` captures of
-# `python -m sam_quantization_b200.kernel_bench gemm` on this kernel (profiles/gemm_i8_kernel_*.md), keyed "KxN".
+# `python -m sam_quantization_b200.kernel_bench gemm` on this kernel (profiles/gemm_i8_kernel_vit_h_dram_traffic.md), keyed "KxN".
 # W stays in L2, so the traffic of a launch grows in proportion to its rows: it is scaled by rows / 32768.
-GEMM_TRAFFIC_NCU_M32768 = {"1280x3840": 331e6, "1280x5120": 326e6, "5120x1280": 246e6}
+GEMM_TRAFFIC_NCU_M32768 = {"1280x3840": 243e6, "1280x1280": 177e6, "1280x5120": 329e6, "5120x1280": 324e6}
 GEMM_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum per launch at M = 32768 (profiles/), scaled by "
                        "rows / 32768 and averaged over the step's GEMM launches; shapes without a capture count their "
                        "algorithmic bytes")
