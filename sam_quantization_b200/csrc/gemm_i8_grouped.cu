@@ -7,13 +7,18 @@
 //   acc_g[m,n] = sum over the K columns of group g of A[m,k] * W[n,k]            (int32, exact)
 //
 // Same pipeline as gemm_i8_kernel (TMA producer warp, tcgen05.mma issuer warp, 8 epilogue warps,
-// every wait bounded), with a 128 x 128 tile and four 128-column TMEM accumulators: the MMA warp
-// accumulates the k-blocks of one group into the next free accumulator and publishes it; the
-// epilogue warps drain it into fp32 registers (64 per thread) scaled by that group's scales while
-// the MMAs of the following groups run.  group_size must be a multiple of 32 (one tcgen05.mma
-// covers 32 columns of K; a 128-column stage may hold up to four groups, each accumulated into its
-// own buffer).  The drain is two instructions per element when only the weights are grouped (the
-// per-token scale is applied once at the end of the tile) and packed fp32x2 throughout.
+// every wait bounded).  Tile 128 x 128 with four 128-column TMEM accumulators and six operand stages:
+// the MMA warp accumulates one group into the next free accumulator and publishes it; the epilogue
+// warps drain it into fp32 registers (64 running sums per thread), scaled by that group's scales,
+// while the MMAs of the following groups run.  group_size must be a multiple of 32 (one tcgen05.mma
+// covers 32 columns of K; a 128-column stage may hold up to four groups), at most 160 groups per row.
+// The weight scales of the next group are fetched into a small per-warp ring in shared memory while the
+// current group drains; the int32 -> fp32 conversion is an integer add (exact for groups of up to 256
+// columns); a per-token activation scale multiplies the sum once at the end of the tile.
+// SAMQ_GROUPED_BN = 256 builds the 128 x 256-tile variant (two accumulators, four stages, 128 running
+// sums per thread): it needs a third less operand traffic but measured no faster (0.80 against
+// 0.82-0.94 POP/s at group 128), the drain being bound by the latency of the tensor-memory loads, which
+// more registers per thread leave less room to overlap.
 #include "gemm_common.cuh"
 
 namespace samq {
@@ -23,19 +28,24 @@ using namespace gemm;
 
 namespace {
 
+#ifndef SAMQ_GROUPED_BN
+#define SAMQ_GROUPED_BN 128
+#endif
 constexpr int BM = 128;
-constexpr int BN = 128;
+constexpr int BN = SAMQ_GROUPED_BN;            // 128: four accumulators, six stages; 256: two accumulators, four stages
 constexpr int UK = 32;
-constexpr int STAGES = 4;
+constexpr int STAGES = BN == 128 ? 6 : 4;
 constexpr int A_BYTES = BM * BK;               // 16 KiB
-constexpr int B_BYTES = BN * BK;               // 16 KiB
+constexpr int B_BYTES = BN * BK;               // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int EPI_WARPS = 8;
+constexpr int EPI_WARPS = 8;                   // two per TMEM lane quadrant, BN / 2 columns each
+constexpr int CPW = BN / 2;                    // accumulator columns per epilogue warp
 constexpr int THREADS = 64 + EPI_WARPS * 32;
-constexpr int ACC_BUFS = 4;
+constexpr int ACC_BUFS = 512 / BN;
 constexpr int TMEM_COLS = ACC_BUFS * BN;       // 512
-constexpr int MAX_GROUPS = 160;                // w-scale staging: MAX_GROUPS x BN floats (K = 5120 in groups of 32)
+constexpr int MAX_GROUPS = 160;                // K = 5120 in groups of 32
 constexpr int STAGING_BYTES = 32 * 64;
+constexpr int RING_FLOATS = 2 * CPW;           // per epilogue warp: the weight scales of two consecutive groups
 
 struct __align__(8) Control {
     uint64_t full[STAGES];
@@ -47,9 +57,20 @@ struct __align__(8) Control {
 };
 
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)EPI_WARPS * STAGING_BYTES +
-                              (size_t)(MAX_GROUPS + 1) * BN * sizeof(float) + sizeof(Control);
+                              (size_t)EPI_WARPS * RING_FLOATS * sizeof(float) + (size_t)BN * sizeof(float) + sizeof(Control);
 
 constexpr uint32_t kInstrDesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void tmem_ld16x(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16x(taddr, r); }
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
 
 struct GroupedParams {
     int M, N, K;
@@ -77,8 +98,8 @@ gemm_i8_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
     uint8_t* tiles = smem_raw + pad;
     uint8_t* staging = tiles + (size_t)STAGES * STAGE_BYTES;
-    float* wscales = reinterpret_cast<float*>(staging + (size_t)EPI_WARPS * STAGING_BYTES);   // [groups][BN]
-    float* biases = wscales + MAX_GROUPS * BN;                                                 // [BN]
+    float* rings = reinterpret_cast<float*>(staging + (size_t)EPI_WARPS * STAGING_BYTES);     // [EPI_WARPS][2][CPW]
+    float* biases = rings + EPI_WARPS * RING_FLOATS;                                           // [BN]
     Control* ctl = reinterpret_cast<Control*>(biases + BN);
     volatile uint32_t* abort_flag = &ctl->abort_flag;
 
@@ -136,7 +157,36 @@ gemm_i8_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             int stage = 0; uint32_t phase = 0;
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
+            // The issuing thread must hand the tensor core an MMA every few tens of clocks, so the common
+            // case (groups that are whole 128-column stages) keeps the four MMAs of a stage unrolled and free of
+            // bookkeeping; groups of 32, 64 or 96 columns take the step-by-step loop below.
+            const bool whole_stages = (p.units_per_group & (BK / UK - 1)) == 0;
+            const int kb_per_group = p.units_per_group / (BK / UK);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                if (whole_stages) {
+                    for (int g = 0; g < p.groups && ok; ++g) {
+                        if (!mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                        tcgen05_fence_after();
+                        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                        for (int kb = 0; kb < kb_per_group; ++kb) {
+                            if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag)) { ok = false; break; }
+                            tcgen05_fence_after();
+                            const uint32_t sa = smem_u32(tiles + (size_t)stage * STAGE_BYTES);
+                            const uint64_t adesc = make_smem_desc(sa);
+                            const uint64_t bdesc = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+                            for (int k = 0; k < BK / UK; ++k)
+                                mma_i8(tmem_d, adesc + (uint64_t)(k * (UK >> 4)), bdesc + (uint64_t)(k * (UK >> 4)),
+                                       kInstrDesc, (kb | k) != 0 ? 1u : 0u);
+                            tcgen05_commit(smem_u32(&ctl->empty[stage]));
+                            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                        }
+                        if (!ok) break;
+                        tcgen05_commit(smem_u32(&ctl->acc_full[acc]));       // this group's partial sums are complete
+                        if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
+                    }
+                    continue;
+                }
                 int unit = 0;                                   // 32-column steps of K issued for this tile
                 uint64_t adesc = 0, bdesc = 0;
                 for (int g = 0; g < p.groups && ok; ++g) {
@@ -168,25 +218,20 @@ gemm_i8_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     } else {
         const int ew = warp - 2;
         const int quad = warp & 3;
-        const int half_n = ew >> 2;               // which 64 columns of the 128
+        const int half_n = ew >> 2;               // which half of the tile's columns
         const int epi_tid = threadIdx.x - 64;
         int acc = 0; uint32_t acc_phase = 0;
         bool ok = true;
         const uint32_t stage_addr = smem_u32(staging + (size_t)ew * STAGING_BYTES);
         uint8_t* stage_ptr = staging + (size_t)ew * STAGING_BYTES;
+        float* ring = rings + ew * RING_FLOATS;
         const uint32_t swz = (uint32_t)((lane >> 1) & 3);
+        const bool magic_ok = p.units_per_group <= 8;     // |acc| < 2^22: the integer-add conversion is exact
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             const int m0 = (tile / n_blocks) * BM;
             const int n0 = (tile % n_blocks) * BN;
-            // stage this tile's weight scales (all groups) and bias; the first barrier keeps slow
-            // warps of the previous tile from seeing them change under their feet
+            // the bias of this tile; the first barrier keeps slow warps of the previous tile from seeing it change
             asm volatile("bar.sync 1, %0;" ::"r"(EPI_WARPS * 32) : "memory");
-            for (int i = epi_tid; i < p.groups * BN; i += EPI_WARPS * 32) {
-                const int g = i / BN, c = i - g * BN, n = n0 + c;
-                float wv = 1.0f;
-                if (n < p.N && p.w_scale != nullptr) wv = p.w_scale[(int64_t)n * p.w_row_stride + (int64_t)g * p.w_group_stride];
-                wscales[i] = wv;
-            }
             if (epi_tid < BN) {
                 const int n = n0 + epi_tid;
                 biases[epi_tid] = (n < p.N && p.bias != nullptr) ? OutOps<OutT>::up(reinterpret_cast<const OutT*>(p.bias)[n]) : 0.f;
@@ -195,63 +240,92 @@ gemm_i8_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
             const int row = m0 + quad * 32 + lane;
             const bool row_ok = row < p.M;
-            float2 y2[32];
+            // weight scales of group g for this warp's columns: lane l fetches columns l, l+32, ...
+            auto fetch_w = [&](int g, float (&w)[CPW / 32]) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y2[j] = make_float2(0.f, 0.f);
+                for (int i = 0; i < CPW / 32; ++i) {
+                    const int n = n0 + half_n * CPW + i * 32 + lane;
+                    w[i] = (n < p.N && p.w_scale != nullptr) ? p.w_scale[(int64_t)n * p.w_row_stride + (int64_t)g * p.w_group_stride] : 1.0f;
+                }
+            };
+            {
+                float w0[CPW / 32];
+                fetch_w(0, w0);
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < CPW / 32; ++i) ring[i * 32 + lane] = w0[i];
+                __syncwarp();
+            }
+            float2 y2[CPW / 2];
+#pragma unroll
+            for (int j = 0; j < CPW / 2; ++j) y2[j] = make_float2(0.f, 0.f);
             // a per-token (or per-tensor) activation scale is the same for every group: it multiplies the sum once
             float a_row = 1.0f;
             if (!p.a_grouped && p.a_scale != nullptr && row_ok) a_row = p.a_scale[(int64_t)row * p.a_row_stride];
+            float a_s = 1.0f;
+            if (p.a_grouped && p.a_scale != nullptr && row_ok) a_s = p.a_scale[(int64_t)row * p.a_row_stride];
             for (int g = 0; g < p.groups; ++g) {
+                // next group's scales travel while this group drains
+                float wn[CPW / 32];
+#pragma unroll
+                for (int i = 0; i < CPW / 32; ++i) wn[i] = 1.f;
+                float a_next = 1.0f;
+                if (g + 1 < p.groups) {
+                    fetch_w(g + 1, wn);
+                    if (p.a_grouped && p.a_scale != nullptr && row_ok) a_next = p.a_scale[(int64_t)row * p.a_row_stride + (int64_t)(g + 1) * p.a_group_stride];
+                }
                 if (ok && !mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag)) ok = false;
                 if (!ok) break;
                 tcgen05_fence_after();
-                float a_s = 1.0f;
-                if (p.a_grouped && p.a_scale != nullptr && row_ok) a_s = p.a_scale[(int64_t)row * p.a_row_stride + (int64_t)g * p.a_group_stride];
                 const float2 a2 = make_float2(a_s, a_s);
-                const uint32_t tmem_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + half_n * 64);
-                const float* ws = wscales + g * BN + half_n * 64;
-                uint32_t r0[32], r1[32];
-                tmem_ld32(tmem_row, r0);
-                tmem_ld32(tmem_row + 32u, r1);
-                tmem_ld_wait();
-                // the accumulator is in registers: hand the buffer back before doing the arithmetic
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
-                if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
-                // int32 -> fp32 without the conversion instruction: a group of up to 256 columns keeps
-                // |acc| <= 127^2 * 256 < 2^22, so 1.5 * 2^23 + acc is exact in fp32 and its bit pattern is
-                // 0x4B400000 + acc; an integer add and a packed float subtract recover float(acc) exactly.
-                auto drain = [&](const uint32_t (&r)[32], int c, auto magic) {
-                    constexpr bool MAGIC = decltype(magic)::value;
-                    const float2 k2 = make_float2(-12582912.0f, -12582912.0f);
+                const uint32_t tmem_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + half_n * CPW);
+                const float* ws = ring + (g & 1) * CPW;
+                const float2 k2 = make_float2(-12582912.0f, -12582912.0f);
+                // 64 columns per warp: two 32-column loads; 128 columns per warp: eight 16-column loads (register budget)
+                constexpr int CH = CPW == 64 ? 32 : 16;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const float4 w4 = *reinterpret_cast<const float4*>(ws + c * 32 + j);
+                for (int c = 0; c < CPW / CH; ++c) {
+                    uint32_t r[CH];
+                    tmem_ld_chunk(tmem_row + (uint32_t)(c * CH), r);
+                    tmem_ld_wait();
+                    if (c == CPW / CH - 1) {                    // the accumulator is in registers: hand the buffer back
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
+                    }
+#pragma unroll
+                    for (int j = 0; j < CH; j += 4) {
+                        const float4 w4 = *reinterpret_cast<const float4*>(ws + c * CH + j);
                         float2 wlo = make_float2(w4.x, w4.y), whi = make_float2(w4.z, w4.w);
                         if (p.a_grouped) { wlo = __fmul2_rn(wlo, a2); whi = __fmul2_rn(whi, a2); }
                         float2 flo, fhi;
-                        if (MAGIC) {
+                        if (magic_ok) {
+                            // 1.5 * 2^23 + acc is exact in fp32 and its bit pattern is 0x4B400000 + acc
                             flo = __fadd2_rn(make_float2(__uint_as_float(r[j + 0] + 0x4B400000u), __uint_as_float(r[j + 1] + 0x4B400000u)), k2);
                             fhi = __fadd2_rn(make_float2(__uint_as_float(r[j + 2] + 0x4B400000u), __uint_as_float(r[j + 3] + 0x4B400000u)), k2);
                         } else {
                             flo = make_float2(__int2float_rn((int)r[j + 0]), __int2float_rn((int)r[j + 1]));
                             fhi = make_float2(__int2float_rn((int)r[j + 2]), __int2float_rn((int)r[j + 3]));
                         }
-                        const int q = (c * 32 + j) >> 1;
+                        const int q = (c * CH + j) >> 1;
                         y2[q] = __ffma2_rn(flo, wlo, y2[q]);
                         y2[q + 1] = __ffma2_rn(fhi, whi, y2[q + 1]);
                     }
-                };
-                if (p.units_per_group <= 8) { drain(r0, 0, std::true_type{}); drain(r1, 1, std::true_type{}); }
-                else { drain(r0, 0, std::false_type{}); drain(r1, 1, std::false_type{}); }
+                }
+                if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
+                // publish the next group's weight scales (every lane has finished reading this group's)
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < CPW / 32; ++i) ring[((g + 1) & 1) * CPW + i * 32 + lane] = wn[i];
+                __syncwarp();
+                a_s = a_next;
             }
             if (!ok) continue;                       // keep visiting the named barriers
 
             // ---- finish the tile: bias, activation, residual, store ----
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const int col0 = half_n * 64 + c * 32;
+            for (int c = 0; c < CPW / 32; ++c) {
+                const int col0 = half_n * CPW + c * 32;
                 const int n_first = n0 + col0;
                 if (n_first >= p.N) continue;
                 const int n_valid = min(32, p.N - n_first);
@@ -264,23 +338,24 @@ gemm_i8_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     v[j] = fmaf(t.x, a_row, biases[col0 + j]);
                     v[j + 1] = fmaf(t.y, a_row, biases[col0 + j + 1]);
                 }
-                if (p.activation == SAMQ_ACT_GELU) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
-                }
+                if (p.activation == SAMQ_ACT_GELU) gelu32(v);
                 if (p.residual != nullptr && row_ok) {
                     const OutT* res = reinterpret_cast<const OutT*>(p.residual) + (int64_t)row * p.ldr + n_first;
+                    if (p.vec_ok && n_valid == 32) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) if (j < n_valid) v[j] += OutOps<OutT>::up(res[j]);
+                        for (int j = 0; j < NVEC; ++j) {
+                            OutT tmp[PER16];
+                            *reinterpret_cast<uint4*>(tmp) = *reinterpret_cast<const uint4*>(res + j * PER16);
+#pragma unroll
+                            for (int e = 0; e < PER16; ++e) v[j * PER16 + e] += OutOps<OutT>::up(tmp[e]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (j < n_valid) v[j] += OutOps<OutT>::up(res[j]);
+                    }
                 }
                 uint4 packed[NVEC];
-#pragma unroll
-                for (int j = 0; j < NVEC; ++j) {
-                    OutT tmp[PER16];
-#pragma unroll
-                    for (int e = 0; e < PER16; ++e) tmp[e] = OutOps<OutT>::down(v[j * PER16 + e]);
-                    packed[j] = *reinterpret_cast<const uint4*>(tmp);
-                }
+                OutOps<OutT>::pack32(v, packed);
                 if (p.tma_store) {
 #pragma unroll
                     for (int part = 0; part < NVEC / 4; ++part) {
@@ -371,7 +446,8 @@ int gemm_i8_grouped_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int6
     p.bias = bias; p.residual = residual; p.ldr = ldr;
     p.out = out; p.ldo = ldo; p.activation = activation; p.status = status;
     const size_t esz = (out_dtype == SAMQ_F16 || out_dtype == SAMQ_BF16) ? 2 : 4;
-    p.vec_ok = 0;
+    p.vec_ok = (((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((ldo * esz) % 16 == 0) &&
+                (residual == nullptr || (((reinterpret_cast<uintptr_t>(residual) & 15) == 0) && ((ldr * esz) % 16 == 0)))) ? 1 : 0;
     memset(&mo, 0, sizeof(mo));
     p.tma_store = 0;
     if (((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((ldo * esz) % 16 == 0)) {
