@@ -245,6 +245,32 @@ int samq_gemm_i8_stall_selftest(const int8_t* A, int64_t lda, const int8_t* W, i
                                 int64_t M, int64_t N, int64_t K, int32_t* out, int64_t ldo,
                                 int skip_kblock, long long wait_limit_cycles, int32_t* status, void* stream);
 
+/* ---- the packed int4 format of the reference's native extension -------------------------------
+ *
+ * Replace `qgemm.sym_quant`, `qgemm.matmul` and `qgemm.sym_dequant`
+ * (quant/qgemm/kernels/bindings.cpp:7-91; quant.cu:11-97; gemm.cu:6-45) with the same data formats:
+ * two 4-bit two's-complement codes per byte, element 2j in the low nibble of byte j.
+ *
+ * samq_sym_quant_i4    : x fp16 [rows, cols] (row stride ldx elements), scale fp16 [rows] ->
+ *                        q_packed uint8 [rows, (cols + 1) / 2]:
+ *                        q = clamp(round_half_even(half(x / scale[row])), -8, 7)      (quant.cu:11-46)
+ * samq_pack_i4 / samq_unpack_i4 : int8 codes in [-8, 7] <-> the packed form (what a weight quantized
+ *                        with n_bits = 4 is stored as; widened to int8 on the way into the GEMM)
+ * samq_matmul_i4       : C int32 [M, N] = A [M, K] x B [N, K]^T from packed operands [M, K/2], [N, K/2]
+ *                        (bindings.cpp:7-26).  The tensor cores have no 4-bit integer kind: the codes are
+ *                        widened into `workspace` ((M + N) * round_up(K, 16) bytes, 16-byte aligned) and
+ *                        multiplied by the int8 tcgen05 GEMM; the result is exact.
+ * samq_sym_dequant_i32 : out fp16 [rows, cols] = (scale_row[m] * scale_col[n]) * half(q[m, n]), every
+ *                        product rounded to fp16 as quant.cu:64-80 does (|q| beyond 65504 overflows there
+ *                        too; the fused epilogue of samq_gemm_i8 dequantises in fp32 instead). */
+int samq_sym_quant_i4(const void* x, const void* scale, int64_t rows, int64_t cols, int64_t ldx, uint8_t* q_packed, void* stream);
+int samq_pack_i4(const int8_t* codes, int64_t rows, int64_t cols, int64_t ldc, uint8_t* q_packed, int64_t ldq, void* stream);
+int samq_unpack_i4(const uint8_t* q_packed, int64_t rows, int64_t cols, int64_t ldq, int8_t* codes, int64_t ldc, void* stream);
+int samq_matmul_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, void* workspace, size_t workspace_bytes,
+                   int32_t* C, int32_t* status, void* stream);
+int samq_sym_dequant_i32(const int32_t* q, const void* scale_row, const void* scale_col, int64_t rows, int64_t cols,
+                         void* out, void* stream);
+
 /* Process-wide choice between the two implementations of samq_gemm_i8 for row / tensor scales
  * (no reference counterpart: the reference has a single cuBLAS-style path):
  *   NEVER  - one CTA per 128 x 256 output tile;

@@ -360,3 +360,50 @@ def random_hadamard_matrix(size, seed, signs=None):
     """Q = hadU(diag(signs)) in fp64 (hadamard_utils.py:86-94)."""
     s = random_hadamard_signs(size, seed) if signs is None else np.asarray(signs, np.float64)
     return matmul_hadU(np.diag(s), np_dtype=np.float64)
+
+
+# ----------------------------------------------------------------------------------------
+# The packed int4 path of the native extension: quant/qgemm/kernels/quant.cu, bindings.cpp
+# ----------------------------------------------------------------------------------------
+
+def sym_quant_int4(x, scale):
+    """``sym_quant`` (quant.cu:11-46): codes = clamp(round_half_even(fp16(x / scale[row])), -8, 7)
+    from fp16 ``x`` [rows, cols] and fp16 ``scale`` [rows]; returns (codes int8 [rows, cols],
+    packed uint8 [rows, ceil(cols / 2)]) with element 2j in the low nibble of byte j.  The fp16
+    quotient formed in fp32 and rounded once equals the correctly rounded half division."""
+    x = rnd(x, "f16")
+    s = rnd(np.asarray(scale, np.float32).reshape(-1, 1), "f16")
+    q = np.clip(np.rint(_div(x, s, "f16")), -8, 7).astype(np.int8)
+    return q, pack_int4(q)
+
+
+def pack_int4(codes):
+    codes = np.asarray(codes, np.int8)
+    rows, cols = codes.shape
+    padded = np.zeros((rows, (cols + 1) // 2 * 2), np.uint8)
+    padded[:, :cols] = codes.astype(np.uint8) & 0xF
+    return (padded[:, 0::2] | (padded[:, 1::2] << 4)).astype(np.uint8)
+
+
+def unpack_int4(packed, cols):
+    packed = np.asarray(packed, np.uint8)
+    out = np.empty((packed.shape[0], packed.shape[1] * 2), np.int8)
+    out[:, 0::2] = ((packed & 0xF).astype(np.int8) ^ 8) - 8
+    out[:, 1::2] = ((packed >> 4).astype(np.int8) ^ 8) - 8
+    return out[:, :cols]
+
+
+def matmul_int4(a_packed, b_packed):
+    """``matmul`` (bindings.cpp:7-26): int32 [M, N] = A [M, K] x B [N, K]^T from the packed operands."""
+    K = 2 * np.asarray(a_packed).shape[1]
+    return int32_accumulators(unpack_int4(a_packed, K), unpack_int4(b_packed, K))
+
+
+def sym_dequant_int32(q, scale_row, scale_col):
+    """``sym_dequant`` (quant.cu:64-80): (scale_row[m] * scale_col[n]) * half(q[m, n]), each product
+    rounded to fp16; int -> half rounds to nearest even and overflows to inf beyond 65504."""
+    sr = rnd(np.asarray(scale_row, np.float32).reshape(-1, 1), "f16")
+    sc = rnd(np.asarray(scale_col, np.float32).reshape(1, -1), "f16")
+    with np.errstate(over="ignore"):
+        xe = np.asarray(q, np.float64).astype(np.float16).astype(np.float32)
+        return rnd(rnd(sr * sc, "f16") * xe, "f16")

@@ -29,6 +29,11 @@ EXPORTED_SYMBOLS = (
     "samq_gemm_i8",
     "samq_gemm_set_pair_mode",
     "samq_gemm_i8_stall_selftest",
+    "samq_sym_quant_i4",
+    "samq_pack_i4",
+    "samq_unpack_i4",
+    "samq_matmul_i4",
+    "samq_sym_dequant_i32",
     "samq_attn_window_prep",
     "samq_attn_rel_bias",
     "samq_attn_windowed",
@@ -133,6 +138,16 @@ def load() -> ctypes.CDLL:
         c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64,   # A, lda, W, ldw, M, N, K
         c_void_p, c_int64, c_int, ctypes.c_longlong, c_void_p, c_void_p,   # out, ldo, skip_kblock, wait_limit_cycles, status, stream
     ]
+    lib.samq_sym_quant_i4.restype = c_int
+    lib.samq_sym_quant_i4.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]
+    lib.samq_pack_i4.restype = c_int
+    lib.samq_pack_i4.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p]
+    lib.samq_unpack_i4.restype = c_int
+    lib.samq_unpack_i4.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p]
+    lib.samq_matmul_i4.restype = c_int
+    lib.samq_matmul_i4.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]
+    lib.samq_sym_dequant_i32.restype = c_int
+    lib.samq_sym_dequant_i32.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]
     lib.samq_gemm_set_pair_mode.restype = c_int
     lib.samq_gemm_set_pair_mode.argtypes = [c_int]
     lib.samq_attn_transpose_v.restype = c_int

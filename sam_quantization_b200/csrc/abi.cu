@@ -59,6 +59,10 @@ int attn_global_dispatch(const void* qkv, const void* vt, const void* rel_all, i
 int gemm_i8_stall_selftest_dispatch(const int8_t* A, int64_t lda, const int8_t* W, int64_t ldw, int64_t M, int64_t N, int64_t K,
                                     int32_t* out, int64_t ldo, int skip_kblock, long long wait_limit_cycles,
                                     int32_t* status, void* stream);
+int sym_quant_i4_dispatch(const void* x, const void* scale, int64_t rows, int64_t cols, int64_t ldx, uint8_t* q, void* stream);
+int unpack_i4_dispatch(const uint8_t* q, int64_t rows, int64_t cols, int64_t ldq, int8_t* out, int64_t ldo, void* stream);
+int pack_i4_dispatch(const int8_t* codes, int64_t rows, int64_t cols, int64_t ldc, uint8_t* q, int64_t ldq, void* stream);
+int sym_dequant_i32_dispatch(const int32_t* q, const void* scale_row, const void* scale_col, int64_t rows, int64_t cols, void* out, void* stream);
 int attn_window14_dispatch(const void* qkv, const void* table, int table_rows, int dtype, int64_t windows, int heads, int head_dim,
                            float scale, void* out, int32_t* status, void* stream);
 int attn_window_dispatch(const void* qkv, int dtype, int64_t windows, int H, int W, int nh, int d,
@@ -183,6 +187,46 @@ int samq_gemm_i8_stall_selftest(const int8_t* A, int64_t lda, const int8_t* W, i
                                 int32_t* status, void* stream)
 {
     return samq::gemm_i8_stall_selftest_dispatch(A, lda, W, ldw, M, N, K, out, ldo, skip_kblock, wait_limit_cycles, status, stream);
+}
+
+int samq_sym_quant_i4(const void* x, const void* scale, int64_t rows, int64_t cols, int64_t ldx, uint8_t* q_packed, void* stream)
+{
+    return samq::sym_quant_i4_dispatch(x, scale, rows, cols, ldx, q_packed, stream);
+}
+
+int samq_unpack_i4(const uint8_t* q_packed, int64_t rows, int64_t cols, int64_t ldq, int8_t* codes, int64_t ldc, void* stream)
+{
+    return samq::unpack_i4_dispatch(q_packed, rows, cols, ldq, codes, ldc, stream);
+}
+
+int samq_pack_i4(const int8_t* codes, int64_t rows, int64_t cols, int64_t ldc, uint8_t* q_packed, int64_t ldq, void* stream)
+{
+    return samq::pack_i4_dispatch(codes, rows, cols, ldc, q_packed, ldq, stream);
+}
+
+int samq_matmul_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, void* workspace, size_t workspace_bytes,
+                   int32_t* C, int32_t* status, void* stream)
+{
+    if (K <= 0 || (K & 1)) return samq::fail(SAMQ_ERR_BAD_ARG, "K=%lld must be positive and even (two codes per byte)", (long long)K);
+    if (M < 0 || N <= 0) return samq::fail(SAMQ_ERR_BAD_ARG, "bad shape M=%lld N=%lld", (long long)M, (long long)N);
+    const int64_t Kp = (K + 15) / 16 * 16;                       // rows of the widened operands stay 16-byte aligned
+    const size_t need = (size_t)(M + N) * (size_t)Kp;
+    if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
+        return samq::fail(SAMQ_ERR_WORKSPACE, "the int4 matmul needs %zu bytes of 16-byte aligned workspace ((M + N) * K rounded up to 16)", need);
+    int8_t* a8 = static_cast<int8_t*>(workspace);
+    int8_t* b8 = a8 + (size_t)M * Kp;
+    int rc = samq::unpack_i4_dispatch(A, M, K, K / 2, a8, Kp, stream);
+    if (rc != SAMQ_OK) return rc;
+    rc = samq::unpack_i4_dispatch(B, N, K, K / 2, b8, Kp, stream);
+    if (rc != SAMQ_OK) return rc;
+    return samq_gemm_i8(a8, Kp, b8, Kp, M, N, K, nullptr, SAMQ_GRAN_ROW, nullptr, SAMQ_GRAN_ROW, 0, nullptr, nullptr, 0,
+                        SAMQ_ACT_NONE, C, SAMQ_I32, N, status, stream);
+}
+
+int samq_sym_dequant_i32(const int32_t* q, const void* scale_row, const void* scale_col, int64_t rows, int64_t cols,
+                         void* out, void* stream)
+{
+    return samq::sym_dequant_i32_dispatch(q, scale_row, scale_col, rows, cols, out, stream);
 }
 
 int samq_gemm_set_pair_mode(int mode)
