@@ -33,6 +33,7 @@ class EncoderRunner:
         if self.device.type != "cuda":
             raise RuntimeError("EncoderRunner needs a CUDA device")
         self.batch = batch
+        self._copy_stream = None
         self.static_in = torch.zeros((batch, 3, img_size, img_size), dtype=dtype, device=self.device)
         self.graph = None
         with torch.no_grad(), torch.cuda.device(self.device):
@@ -61,6 +62,63 @@ class EncoderRunner:
         if self.check_status:
             self.check()
         return self.static_out
+
+    @torch.no_grad()
+    def encode(self, images: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """Encode ``images`` [n * batch, 3, S, S] into ``out`` [n * batch, C, h, w], ``batch`` images per
+        forward.  With host tensors (pinned memory) the copy of chunk i + 1 to the device runs on a
+        second stream while chunk i is being encoded, and the embeddings of chunk i leave for the host
+        while chunk i + 1 is encoded; device tensors are encoded in place.  Returns ``out``; the work is
+        ordered on the current stream (synchronise it before reading a host ``out``)."""
+        n, b = images.shape[0], self.batch
+        if n % b or out.shape[0] != n:
+            raise ValueError(f"images and out must hold a multiple of {b} images")
+        cur = torch.cuda.current_stream(self.device)
+        if images.is_cuda:
+            for i in range(0, n, b):
+                out[i:i + b].copy_(self(images[i:i + b]), non_blocking=True)
+            return out
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+            self._stage = [torch.empty_like(self.static_in) for _ in range(2)]
+            self._stage_free = [torch.cuda.Event() for _ in range(2)]
+            self._out_stage = [torch.empty_like(self.static_out) for _ in range(2)]
+            self._out_free = [torch.cuda.Event() for _ in range(2)]
+        side = self._copy_stream
+        side.wait_stream(cur)                                   # earlier users of the staging buffers
+        ready = []
+        with torch.cuda.stream(side):                           # first chunk
+            self._stage[0].copy_(images[0:b], non_blocking=True)
+            ev = torch.cuda.Event(); ev.record(side); ready.append(ev)
+        for k, i in enumerate(range(0, n, b)):
+            slot = k & 1
+            if i + b < n:                                       # prefetch the next chunk while this one runs
+                with torch.cuda.stream(side):
+                    side.wait_event(self._stage_free[slot ^ 1]) if k >= 1 else None
+                    self._stage[slot ^ 1].copy_(images[i + b:i + 2 * b], non_blocking=True)
+                    ev = torch.cuda.Event(); ev.record(side); ready.append(ev)
+            cur.wait_event(ready[k])
+            self.static_in.copy_(self._stage[slot], non_blocking=True)
+            self._stage_free[slot].record(cur)
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self.static_out = self.encoder(self.static_in)
+            if out.is_cuda:
+                out[i:i + b].copy_(self.static_out, non_blocking=True)
+            else:
+                if k >= 2:
+                    cur.wait_event(self._out_free[slot])        # the copy that last read this slot has finished
+                self._out_stage[slot].copy_(self.static_out, non_blocking=True)
+                done = torch.cuda.Event(); done.record(cur)
+                with torch.cuda.stream(side):
+                    side.wait_event(done)
+                    out[i:i + b].copy_(self._out_stage[slot], non_blocking=True)
+                    self._out_free[slot].record(side)
+        cur.wait_stream(side)
+        if self.check_status:
+            self.check()
+        return out
 
     def check(self) -> None:
         """Synchronise and raise if a kernel of this device reported a timed-out wait."""

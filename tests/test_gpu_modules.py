@@ -528,3 +528,34 @@ def test_reference_format_state_dict_loads_into_w8a8linear(cuda_device):
     mod2.weight = w.clone().to(cuda_device)
     assert torch.equal(mod2(x), want)
     assert torch.equal(mod2.weight, mod.weight)
+
+
+def test_encoder_runner_encode_overlaps_copies_and_matches_direct_calls(cuda_device):
+    """``EncoderRunner.encode``: pinned host images in, host (or device) embeddings out, the copies of
+    the neighbouring chunks overlapping the current forward; same embeddings as calling the model."""
+    from sam_quantization_b200.RTN_quantization import W8A8Linear, replace_linear_with_target_and_quantize
+    from sam_quantization_b200.engine import EncoderRunner
+    dev = cuda_device
+    mine, _ = _tiny_pair(dev, torch.float16, torch.bfloat16)
+    replace_linear_with_target_and_quantize(mine, W8A8Linear, 8, [])
+    size = TINY["img_size"]
+    imgs = torch.cat([tiny_images(seed=300 + i) for i in range(5)], 0)[:10].half()       # 10 images
+    with torch.no_grad():
+        want = torch.cat([mine(imgs[i:i + 2].to(dev)) for i in range(0, 10, 2)], 0)
+    runner = EncoderRunner(mine, 2, img_size=size, device=dev, check_status=True)
+    host_in = imgs.pin_memory()
+    host_out = torch.empty(want.shape, dtype=want.dtype).pin_memory()
+    for _ in range(2):                                           # the second call reuses the staging buffers
+        host_out.zero_()
+        runner.encode(host_in, host_out)
+        torch.cuda.synchronize()
+        assert torch.equal(host_out, want.cpu())
+    dev_out = torch.empty_like(want)
+    runner.encode(imgs.to(dev), dev_out)
+    torch.cuda.synchronize()
+    assert torch.equal(dev_out, want)
+    runner.encode(host_in, dev_out.zero_())
+    torch.cuda.synchronize()
+    assert torch.equal(dev_out, want)
+    with pytest.raises(ValueError):
+        runner.encode(host_in[:3], host_out[:3])
