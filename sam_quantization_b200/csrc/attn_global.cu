@@ -233,16 +233,28 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         uint8_t* prow = p_tile + row * 128;
         const uint32_t sw = (uint32_t)(row & 7);
         bool ok = true;
+        // rel_h term of the key row(s) of a block: one row for images, four for windows.  The values of
+        // block i + 1 are fetched (16-bit, from L2) while block i is processed: a warp issues in order, so a
+        // load consumed in the iteration that issues it would stall the whole softmax for its latency.
+        constexpr int NRH = WINDOW ? 4 : 1;
+        T rh_next[NRH];
+        auto fetch_rh = [&](int blk) {
+#pragma unroll
+            for (int r = 0; r < NRH; ++r) {
+                const int kh = NRH * blk + r;
+                rh_next[r] = rel[kh < p.H ? (qh - kh + p.H - 1) : 0];
+            }
+        };
+        fetch_rh(0);
         for (int i = 0; i < nblocks; ++i) {
-            // rel_h term of the key row(s) of block i: one row for images, four for windows
             // (-inf for rows beyond the window)
-            constexpr int NRH = WINDOW ? 4 : 1;
             float rhv[NRH];
 #pragma unroll
             for (int r = 0; r < NRH; ++r) {
                 const int kh = NRH * i + r;
-                rhv[r] = kh < p.H ? AtOps<T>::up(rel + (qh - kh + p.H - 1)) * LOG2E : -INFINITY;
+                rhv[r] = kh < p.H ? AtOps<T>::up(&rh_next[r]) * LOG2E : -INFINITY;
             }
+            if (i + 1 < nblocks) fetch_rh(i + 1);
             if (!mbar_wait(smem_u32(&ctl->s_full[i & 1]), (uint32_t)((i >> 1) & 1), abort_flag)) { ok = false; break; }
             tcgen05_fence_after();
             // One pass over the block's 64 scores with a given reference maximum:
