@@ -206,16 +206,18 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + b));
                 }
             }
-            // after a failed wait keep visiting the named barrier above so no warp is left behind
-            if (ok && !mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag, p.wait_limit)) ok = false;
-            if (!ok) continue;
-            tcgen05_fence_after();
+            // the row's activation scale does not depend on the accumulator: fetch it before waiting for the
+            // MMAs, so that its latency is not added to the epilogue (a warp issues in order)
             const int row = m0 + quad * 32 + lane;
             const bool row_ok = row < p.M;
             float a_s = 1.0f;
             if constexpr (!std::is_same<OutT, int32_t>::value) {
                 if (p.a_scale != nullptr && row_ok) a_s = p.a_scale[(int64_t)row * p.a_stride];
             }
+            // after a failed wait keep visiting the named barrier above so no warp is left behind
+            if (ok && !mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag, p.wait_limit)) ok = false;
+            if (!ok) continue;
+            tcgen05_fence_after();
             const uint32_t stage_addr = smem_u32(staging + (size_t)ew * STAGING_BYTES);
             uint8_t* stage_ptr = staging + (size_t)ew * STAGING_BYTES;
             const int rr = quad * 32 + lane;                       // row inside the tile
