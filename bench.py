@@ -354,12 +354,17 @@ def run_ours(args):
     e2e_value = GLOBAL_BATCH * args.steps / (e2e_ms / 1000.0)
 
     # per-kernel timing of the dominant kernel (the int8 GEMM): one more step, run eagerly (not
-    # through the graph) with CUDA events around every launch on the launching stream
+    # through the graph) with CUDA events around every launch on the launching stream.
+    # Each forward is enqueued behind a spin kernel that keeps the GPU busy while the host runs ahead, so that
+    # the launches execute back to back and an event pair brackets only its kernel (on an idle stream the start
+    # event would be reached when it is enqueued, microseconds before the launch that follows it).
     torch.cuda.synchronize()
     ops.enable_kernel_timing(True)
     ops.reset_counters()
+    spin_cycles = int(0.04 * 1e3 * torch.cuda.get_device_properties(dev).clock_rate) if hasattr(torch.cuda.get_device_properties(dev), "clock_rate") else 60_000_000
     with torch.no_grad():
         for i in range(0, local_n, chunk):
+            torch.cuda._sleep(spin_cycles)
             out_dev[i:i + chunk].copy_(model.image_encoder(resident[i:i + chunk]))
     torch.cuda.synchronize()
     launches = ops.launch_count() * args.steps

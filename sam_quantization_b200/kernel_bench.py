@@ -28,11 +28,17 @@ SWEEP_M = (196, 4096, 32768, 262144)
 SWEEP_KN = ((768, 2304), (768, 3072), (3072, 768), (1024, 4096), (4096, 1024), (1280, 3840), (1280, 5120), (5120, 1280))
 
 
-def _time(fn, iters, warmup):
+def _time(fn, iters, warmup, head_start_ms=20.0):
+    """Mean CUDA-event time of ``fn`` over ``iters`` back-to-back launches.  The loop is enqueued behind a spin
+    kernel of ``head_start_ms`` so that the host (tens of microseconds of Python per call) stays ahead of the
+    GPU: otherwise a kernel shorter than the host's per-call cost would be timed at the host's pace."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if head_start_ms > 0:
+        khz = getattr(torch.cuda.get_device_properties(torch.cuda.current_device()), "clock_rate", 1_900_000)
+        torch.cuda._sleep(int(head_start_ms * khz))
     e0.record()
     for i in range(iters):
         fn(i)
