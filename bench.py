@@ -168,6 +168,10 @@ def build_quantized_encoder(model_type: str, device, calib_images: int = 8, reci
         from sam_quantization_b200.quarot import rotate_sam
         enc = model.image_encoder
         dim, heads = enc.blocks[0].attn.qkv.in_features, enc.blocks[0].attn.num_heads
+        if (dim // heads) & (dim // heads - 1):
+            # quarot/hadamard_utils.py:117-118 asserts a power-of-two head width for the V-side transform
+            raise SystemExit(f"QuaRot needs a power-of-two head width; {model_type} has {dim // heads} (the reference's "
+                             "apply_exact_had_to_linear asserts the same): use vit_b or vit_l")
         if with_twin:
             signs, Q = random_hadamard_Q(dim, 123) if dim & (dim - 1) == 0 else (None, None)
             if Q is None:
