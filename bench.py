@@ -285,6 +285,11 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     from sam_quantization_b200.dist import gather_shards, init_process_group, shard_range
+    # libraries may write to file descriptor 1 on their own (NCCL prints its version there when it starts):
+    # keep stdout for the one JSON line by pointing fd 1 at stderr until that line is printed
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
     init_process_group("nccl", device=dev)
     first, last = shard_range(rank, world, GLOBAL_BATCH)          # this rank's images [first, last)
     local_n = last - first
@@ -453,10 +458,16 @@ def run_ours(args):
         if not args.no_cpu_baseline and world == 1:
             v, cores, sample, _ = cpu_reference_images_per_s(args.model, budget_s=args.ref_budget)
             line["cpu_baseline"] = {"value": v, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample}
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
         print(json.dumps(line), flush=True)
+        os.dup2(2, 1)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    sys.stdout.flush()
+    os.dup2(saved_stdout, 1)
+    os.close(saved_stdout)
 
 
 def main():
