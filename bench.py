@@ -479,7 +479,7 @@ def main():
     ap.add_argument("--model", default="vit_h", choices=list(ENC))
     ap.add_argument("--recipe", default="smoothquant", choices=list(RECIPES),
                     help="what precedes W8A8 (the headline configuration is vit_h + smoothquant)")
-    ap.add_argument("--chunk", type=int, default=8, help="images per encoder forward")
+    ap.add_argument("--chunk", type=int, default=32, help="images per encoder forward (capped by the rank's share of the batch)")
     ap.add_argument("--ref-budget", dest="ref_budget", type=float, default=25.0, help="seconds of CPU work per reference sample")
     ap.add_argument("--no-cpu-baseline", dest="no_cpu_baseline", action="store_true")
     ap.add_argument("--no-graph", dest="no_graph", action="store_true", help="run the encoder eagerly instead of replaying a CUDA graph")

@@ -338,6 +338,25 @@ def set_gemm_pair_mode(mode: int) -> int:
     return prev
 
 
+_bias_cache = {}
+
+
+def _bias_as(bias: torch.Tensor, dtype: torch.dtype, dev) -> torch.Tensor:
+    """``bias`` flattened in the epilogue's parameter dtype.  A layer whose output dtype differs from its
+    bias dtype (qkv storing bf16 for the attention) would otherwise launch a conversion kernel on every
+    call; the converted copy is cached until the bias changes (new storage or an in-place update)."""
+    if bias.dtype == dtype and bias.device == dev and bias.dim() == 1 and bias.is_contiguous():
+        return bias
+    key = (bias.data_ptr(), bias._version, bias.numel(), bias.dtype, dtype, str(dev))
+    hit = _bias_cache.get(key)
+    if hit is None:
+        if len(_bias_cache) > 4096:
+            _bias_cache.clear()
+        hit = bias.detach().reshape(-1).to(device=dev, dtype=dtype).contiguous()
+        _bias_cache[key] = hit
+    return hit
+
+
 def gemm_i8(a_q: torch.Tensor, w_q: torch.Tensor,
             a_scale: Optional[torch.Tensor] = None, w_scale: Optional[torch.Tensor] = None,
             a_gran: int = GRAN_ROW, w_gran: int = GRAN_ROW, group_size: int = 0,
@@ -366,7 +385,7 @@ def gemm_i8(a_q: torch.Tensor, w_q: torch.Tensor,
             raise ValueError("out has the wrong dtype, shape or layout")
     param_dtype = torch.float32 if out_dtype in (torch.float32, torch.int32) else out_dtype
     if bias is not None:
-        bias = bias.reshape(-1).to(device=dev, dtype=param_dtype).contiguous()
+        bias = _bias_as(bias, param_dtype, dev)
         if bias.numel() != N:
             raise ValueError("bias must have N elements")
     ldr = 0
