@@ -7,6 +7,7 @@ outputs.  CPU tensors are rejected: this package has no CPU compute path.
 from __future__ import annotations
 
 import ctypes
+import weakref
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -347,14 +348,14 @@ def _bias_as(bias: torch.Tensor, dtype: torch.dtype, dev) -> torch.Tensor:
     call; the converted copy is cached until the bias changes (new storage or an in-place update)."""
     if bias.dtype == dtype and bias.device == dev and bias.dim() == 1 and bias.is_contiguous():
         return bias
-    key = (bias.data_ptr(), bias._version, bias.numel(), bias.dtype, dtype, str(dev))
+    key = (id(bias), bias.data_ptr(), bias._version, dtype, str(dev))
     hit = _bias_cache.get(key)
-    if hit is None:
+    if hit is None or hit[0]() is not bias:              # the weak reference guards against a recycled id / address
         if len(_bias_cache) > 4096:
             _bias_cache.clear()
-        hit = bias.detach().reshape(-1).to(device=dev, dtype=dtype).contiguous()
+        hit = (weakref.ref(bias), bias.detach().reshape(-1).to(device=dev, dtype=dtype).contiguous())
         _bias_cache[key] = hit
-    return hit
+    return hit[1]
 
 
 def gemm_i8(a_q: torch.Tensor, w_q: torch.Tensor,
