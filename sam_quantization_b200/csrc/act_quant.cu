@@ -905,12 +905,15 @@ hadamard_quant_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx,
 // rows), thread t of a row owns elements [16t, 16t + 16) for the first four stages (registers),
 // elements differing in index bits 4..7 for the next four (their owners sit in the same half-warp:
 // a warp barrier), index bits 8 and up for the rest (CTA barrier); the division by sqrt(K) (32 or
-// 64) is an exact scaling.  Shared-memory slot of element i of a row: i + i / 16.
+// 64) is an exact scaling.  Shared-memory slot of element i of a row: i + i / 16.  The dispatch sends
+// 1024-point rows here (optionally with the LayerNorm of the source row in front: LN) and 4096-point
+// rows to hadamard_4096_quant_kernel below.
 // ---------------------------------------------------------------------------
-template <typename SrcT, int K>
-__global__ void __launch_bounds__(256, 6)
+template <typename SrcT, int K, bool LN>
+__global__ void __launch_bounds__(256, LN ? 4 : 6)
 hadamard_pow4_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, const int32_t* __restrict__ row_map,
-                           const int8_t* __restrict__ signs, float qmax,
+                           const int8_t* __restrict__ signs, const __half* __restrict__ gamma,
+                           const __half* __restrict__ beta, float ln_eps, float qmax,
                            int8_t* __restrict__ q_out, float* __restrict__ scale_out)
 {
     static_assert(K == 1024 || K == 4096, "lengths whose square root is a power of two");
@@ -939,16 +942,64 @@ hadamard_pow4_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, c
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[i * 8 + e] = f[e];
         }
-        if (signs != nullptr) {
-            const uint4 sg = *reinterpret_cast<const uint4*>(signs + 16 * t);
-            const uint32_t w[4] = {sg.x, sg.y, sg.z, sg.w};
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if ((w[j >> 2] >> (8 * (j & 3))) & 0x80u) v[j] = -v[j];
-        }
     } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] = 0.f;
+    }
+    if constexpr (LN) {
+        // LayerNorm of the row before the transform, in the same pass (the two-kernel route writes the
+        // normalised fp16 tensor and reads it back): fp32 two-pass statistics over the NT threads of the
+        // row, y = half(gamma * (rstd * (x - mean)) + beta) as in quant_rows_fast_kernel; a gathered zero
+        // row stays zero (the padding of window_partition comes after the norm)
+        constexpr int WPR = NT / 32;
+        __shared__ float ln_red[2][8];
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) sum += v[j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if ((threadIdx.x & 31) == 0) ln_red[0][threadIdx.x >> 5] = sum;
+        __syncthreads();
+        sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < WPR; ++w) sum += ln_red[0][r_in * WPR + w];
+        const float mean = sum / (float)K;
+        float var = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { v[j] -= mean; var = fmaf(v[j], v[j], var); }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+        if ((threadIdx.x & 31) == 0) ln_red[1][threadIdx.x >> 5] = var;
+        __syncthreads();
+        var = 0.f;
+#pragma unroll
+        for (int w = 0; w < WPR; ++w) var += ln_red[1][r_in * WPR + w];
+        const float rstd = rsqrtf(var / (float)K + ln_eps);
+        if (src >= 0) {
+            float g[16], b[16];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                float f[8];
+                unpack<__half>(*reinterpret_cast<const uint4*>(gamma + 16 * t + 8 * i), f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) g[i * 8 + e] = f[e];
+                unpack<__half>(*reinterpret_cast<const uint4*>(beta + 16 * t + 8 * i), f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) b[i * 8 + e] = f[e];
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __half2float(__float2half_rn(fmaf(g[j], rstd * v[j], b[j])));
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+    }
+    if (src >= 0 && signs != nullptr) {
+        const uint4 sg = *reinterpret_cast<const uint4*>(signs + 16 * t);
+        const uint32_t w[4] = {sg.x, sg.y, sg.z, sg.w};
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if ((w[j >> 2] >> (8 * (j & 3))) & 0x80u) v[j] = -v[j];
     }
     butterfly16(v);                                        // index bits 0..3
 #pragma unroll
@@ -1024,6 +1075,111 @@ hadamard_pow4_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, c
     *reinterpret_cast<uint4*>(q_out + row * K + 16 * t) =
         make_uint4(__byte_perm(hb[0], hb[1], 0x6420), __byte_perm(hb[2], hb[3], 0x6420),
                    __byte_perm(hb[4], hb[5], 0x6420), __byte_perm(hb[6], hb[7], 0x6420));
+}
+
+// ---------------------------------------------------------------------------
+// The 4096-point transform again (ViT-L `lin2` input, the largest K1 of the QuaRot configuration), with
+// the three regroupings of the row between its register passes done with 16-byte shared-memory
+// accesses wherever the data allows it: 57 shared-memory instructions per thread instead of 96.  Same
+// butterflies on the same values in the same order as the generic kernel and as hadamard_pow4_quant_kernel<., 1024, .>.  256 threads per row, one row per CTA.
+//   pass A  thread t = 16 g + l owns elements 16 t + j            (index bits 0..3 in registers)
+//   X1      rows of 16 floats, 20-float pitch, written with 4 x STS.128; column l read back
+//   pass B  thread (g, l) owns elements 256 g + 16 j + l           (bits 4..7)
+//   X2      element 256 g + c goes to slot 20 c + g; thread c reads its row with 4 x LDS.128
+//   pass C  thread c owns elements 256 g + c                       (bits 8..11), then scale, round, absmax
+//   X3      codes as bytes at 256 g + c; thread t reads its 16 consecutive codes with one LDS.128
+// ---------------------------------------------------------------------------
+template <typename SrcT>
+__global__ void __launch_bounds__(256, 5)
+hadamard_4096_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, const int32_t* __restrict__ row_map,
+                           const int8_t* __restrict__ signs, float qmax,
+                           int8_t* __restrict__ q_out, float* __restrict__ scale_out)
+{
+    constexpr int K = 4096;
+    constexpr int BLK = 336;                                   // 16 rows x 20 floats + 16: half-warps land 16 banks apart
+    __shared__ __align__(16) float x1[16 * BLK];               // also the byte codes of X3
+    __shared__ __align__(16) float x2[256 * 20];
+    __shared__ float red[8];
+    const int t = threadIdx.x, g = t >> 4, l = t & 15;
+    const int64_t row = blockIdx.x;
+    int64_t src = row_map != nullptr ? (int64_t)row_map[row] : row;
+    float v[16];
+    if (src >= 0) {
+        const SrcT* xr = x + src * ldx + 16 * t;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float f[8];
+            unpack<SrcT>(ld_stream(xr + i * 8), f);
+            if (!std::is_same<SrcT, __half>::value) RoundVec<__half, 8>::run(f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[i * 8 + e] = f[e];
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+    }
+    if (src >= 0 && signs != nullptr) {
+        const uint4 sg = *reinterpret_cast<const uint4*>(signs + 16 * t);
+        const uint32_t w[4] = {sg.x, sg.y, sg.z, sg.w};
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if ((w[j >> 2] >> (8 * (j & 3))) & 0x80u) v[j] = -v[j];
+    }
+    butterfly16(v);                                            // pass A: index bits 0..3
+    {
+        float* blk = x1 + g * BLK;                             // X1: the 16 threads of a half-warp transpose their 16 x 16 block
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<float4*>(blk + l * 20 + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = blk[j * 20 + l];
+    }
+    butterfly16(v);                                            // pass B: bits 4..7; v[j] is element 256 g + 16 j + l
+#pragma unroll
+    for (int j = 0; j < 16; ++j) x2[(16 * j + l) * 20 + g] = v[j];   // X2
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float4 f = *reinterpret_cast<const float4*>(x2 + t * 20 + 4 * q);
+        v[4 * q] = f.x; v[4 * q + 1] = f.y; v[4 * q + 2] = f.z; v[4 * q + 3] = f.w;
+    }
+    butterfly16(v);                                            // pass C: bits 8..11; v[gg] is element 256 gg + t
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {                          // divide by sqrt(4096) (exact), round once to fp16, absolute maximum
+        const __half2 h = __floats2half2_rn(v[i] * 0.015625f, v[i + 1] * 0.015625f);
+        const __half2 a = __habs2(h);
+        m = fmaxf(m, fmaxf(__low2float(a), __high2float(a)));
+        const float2 f = __half22float2(h);
+        v[i] = f.x; v[i + 1] = f.y;
+    }
+    m = warp_max(m);
+    if ((t & 31) == 0) red[t >> 5] = m;
+    __syncthreads();
+    m = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) m = fmaxf(m, red[w]);
+    const float sc = scale_from_absmax<__half>(m, qmax);
+    if (t == 0 && scale_out != nullptr) scale_out[row] = sc;
+    const float inv = __frcp_rn(sc);
+    const float2 inv2 = make_float2(inv, inv), ns2 = make_float2(-sc, -sc);
+    const __half2 hi2 = __float2half2_rn(qmax), lo2 = __float2half2_rn(-qmax), magic = __float2half2_rn(1536.0f);
+    uint8_t* codes = reinterpret_cast<uint8_t*>(x1);           // X3 (every thread is past its X1 reads: two barriers ago)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float2 f = make_float2(v[2 * j], v[2 * j + 1]);
+        const float2 y0 = __fmul2_rn(f, inv2);
+        const float2 e = __ffma2_rn(y0, ns2, f);
+        const float2 y = __ffma2_rn(e, inv2, y0);
+        __half2 h = __floats2half2_rn(y.x, y.y);
+        h = __hadd2(__hmin2(__hmax2(h, lo2), hi2), magic);
+        const uint32_t hb = *reinterpret_cast<uint32_t*>(&h);
+        codes[256 * (2 * j) + t] = (uint8_t)(hb & 0xFFu);
+        codes[256 * (2 * j + 1) + t] = (uint8_t)((hb >> 16) & 0xFFu);
+    }
+    __syncthreads();
+    *reinterpret_cast<uint4*>(q_out + row * K + 16 * t) = *reinterpret_cast<const uint4*>(codes + 16 * t);
 }
 
 // ---------------------------------------------------------------------------
@@ -1223,8 +1379,8 @@ static int quant_typed(const SrcT* x, int64_t M, int K, int64_t ldx, const Prolo
     if (had != nullptr && had->mode != SAMQ_HAD_NONE) {
         if (gran != SAMQ_GRAN_ROW)
             return fail(SAMQ_ERR_UNSUPPORTED, "an online Hadamard is only combined with per-token quantization");
-        if (pro.ln_gamma != nullptr)
-            return fail(SAMQ_ERR_UNSUPPORTED, "LayerNorm and an online Hadamard are not combined in one call");
+        // LayerNorm + transform in one call exists for the kernel specialised for 1024 points (fp16, codes only)
+        const bool ln_had = pro.ln_gamma != nullptr;
         int inner, axis;
         if (had->mode == SAMQ_HAD_FULL) { inner = 1; axis = K; }
         else if (had->mode == SAMQ_HAD_PARTIAL) {
@@ -1259,15 +1415,23 @@ static int quant_typed(const SrcT* x, int64_t M, int K, int64_t ldx, const Prolo
         if constexpr (std::is_same<T, __half>::value) {
             // the 1024- and 4096-point transforms with codes only have a kernel of their own
             if (had->mode == SAMQ_HAD_FULL && hk == 1 && (K == 4096 || K == 1024) && vec && divisor == nullptr && fq == nullptr &&
-                tx == nullptr && q != nullptr) {
-                if (K == 4096)
-                    hadamard_pow4_quant_kernel<SrcT, 4096><<<(unsigned)M, 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, qmax, q, scale);
-                else
-                    hadamard_pow4_quant_kernel<SrcT, 1024><<<(unsigned)((M + 3) / 4), 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, qmax, q, scale);
+                tx == nullptr && q != nullptr &&
+                (!ln_had || (K == 1024 && std::is_same<SrcT, __half>::value && al16(pro.ln_gamma) && al16(pro.ln_beta)))) {
+                const __half* g = static_cast<const __half*>(pro.ln_gamma);
+                const __half* b = static_cast<const __half*>(pro.ln_beta);
+                if (K == 4096) {
+                    hadamard_4096_quant_kernel<SrcT><<<(unsigned)M, 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, qmax, q, scale);
+                } else {
+                    const unsigned grid = (unsigned)((M + 3) / 4);
+                    if (ln_had) hadamard_pow4_quant_kernel<SrcT, 1024, true><<<grid, 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, g, b, pro.ln_eps, qmax, q, scale);
+                    else hadamard_pow4_quant_kernel<SrcT, 1024, false><<<grid, 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, g, b, 0.f, qmax, q, scale);
+                }
                 SAMQ_CUDA_TRY(cudaGetLastError());
                 return SAMQ_OK;
             }
         }
+        if (ln_had)
+            return fail(SAMQ_ERR_UNSUPPORTED, "LayerNorm and an online Hadamard are combined only for fp16 rows of 1024 elements with codes as the one output");
         if constexpr (std::is_same<T, __half>::value) {
             // so has the transform across 16 heads
             if (had->mode == SAMQ_HAD_PARTIAL && hk == 1 && axis == 16 && (inner & 7) == 0 && inner <= 128 && vec &&

@@ -176,6 +176,13 @@ def _spec(had: Optional[Hadamard], keep: list) -> Optional[HadamardSpec]:
                         0 if signs is None else signs.data_ptr())
 
 
+def hadamard_layer_norm_fused(x: torch.Tensor, hadamard: "Hadamard", as_dtype: Optional[torch.dtype] = None) -> bool:
+    """True when ``quantize(x, GRAN_ROW, hadamard=..., layer_norm=...)`` runs as one kernel: a full
+    power-of-two transform over fp16 rows of 1024 elements (codes and scales only)."""
+    return (hadamard is not None and hadamard.mode == "full" and int(hadamard.had_k) == 1 and x.dtype == torch.float16 and
+            (as_dtype is None or as_dtype == torch.float16) and x.shape[-1] == 1024)
+
+
 def quantize(x: torch.Tensor, granularity: int = GRAN_ROW, group_size: Optional[int] = None,
              divisor: Optional[torch.Tensor] = None, hadamard: Optional[Hadamard] = None,
              codes: bool = True, fake_quant: bool = False, transformed: bool = False, n_bits: int = 8,

@@ -205,11 +205,13 @@ class ActQuantWrapper(torch.nn.Module):
     @torch.no_grad()
     def forward_fused(self, x, row_map=None, layer_norm=None, as_dtype=None, residual=None,
                       activation=None, out_dtype=None):
-        """Same contract as ``W8A8Linear.forward_fused``.  An online Hadamard and a LayerNorm are
-        two passes of K1 (normalise + gather, then transform + quantize); otherwise one."""
+        """Same contract as ``W8A8Linear.forward_fused``.  An online Hadamard and a LayerNorm are one
+        pass of K1 for fp16 rows of 1024 or 4096 elements (power-of-two transform, per-token codes) and
+        two passes otherwise (normalise + gather, then transform + quantize)."""
         spec = self._hadamard_spec(x)
         tdtype = as_dtype or x.dtype
-        if spec is not None and (layer_norm is not None):
+        if spec is not None and (layer_norm is not None) and not (
+                self.act_quant_name == "per_token" and ops.hadamard_layer_norm_fused(x, spec, as_dtype)):
             x = ops.quantize(x, ops.GRAN_ROW, codes=False, transformed=True, row_map=row_map,
                              layer_norm=layer_norm, as_dtype=as_dtype)["tx"]
             row_map, layer_norm, as_dtype = None, None, None

@@ -413,3 +413,39 @@ def test_hadamard_across_16_heads_kernel_matches_general_kernel(cuda_device, had
     a = ops.quantize(xb, 0, hadamard=had, as_dtype=torch.float16, row_map=rm)
     b = ops.quantize(xb, 0, hadamard=had, as_dtype=torch.float16, row_map=rm, transformed=True)
     assert torch.equal(a["q"], b["q"]) and torch.equal(a["scale"], b["scale"])
+
+
+def test_layer_norm_and_hadamard_in_one_kernel(cuda_device, K=1024):
+    """LayerNorm + sign flip + 1024-point Walsh-Hadamard + per-token quantization as one launch against
+    the two-launch route (normalise and gather to an fp16 tensor, then transform and quantize).  The two
+    LayerNorms sum in different orders, so a normalised value may differ in its last fp16 bit; codes
+    then agree except where such a value sat on a rounding boundary."""
+    from sam_quantization_b200 import ops
+    g = torch.Generator().manual_seed(K)
+    M = 777
+    x = (torch.randn(M, K, generator=g) * 2 + 0.3).half().to(cuda_device)
+    w = (1 + 0.1 * torch.randn(K, generator=g)).half().to(cuda_device)
+    b = (0.1 * torch.randn(K, generator=g)).half().to(cuda_device)
+    signs = (torch.randint(0, 2, (K,), generator=g) * 2 - 1).to(torch.int8).to(cuda_device)
+    row_map = torch.randperm(M, generator=g)[:700].to(torch.int32)
+    row_map[::13] = -1                                         # padding rows of a window gather
+    row_map = row_map.to(cuda_device)
+    spec = ops.Hadamard("full", signs=signs)
+    assert ops.hadamard_layer_norm_fused(x, spec)
+    one = ops.quantize(x, ops.GRAN_ROW, hadamard=spec, layer_norm=(w, b, 1e-6), row_map=row_map)
+    tx = ops.quantize(x, ops.GRAN_ROW, codes=False, transformed=True, layer_norm=(w, b, 1e-6), row_map=row_map)["tx"]
+    two = ops.quantize(tx, ops.GRAN_ROW, hadamard=spec)
+    assert one["q"].shape == (700, K)
+    pad = (row_map < 0)
+    assert int(one["q"][pad].abs().max()) == 0                 # zero rows stay zero: the padding comes after the norm
+    diff = (one["q"].int() - two["q"].int()).abs()
+    assert int(diff.max()) <= 1 and float((diff > 0).float().mean()) < 0.02
+    assert torch.allclose(one["scale"], two["scale"], rtol=2e-3)
+    # exact when the normalised tensor is the same: no LayerNorm, same kernel family
+    assert torch.equal(ops.quantize(tx, ops.GRAN_ROW, hadamard=spec)["q"], two["q"])
+    # and against torch's LayerNorm followed by the reference transform in fp32
+    ln = torch.nn.functional.layer_norm(x.float(), (K,), w.float(), b.float(), 1e-6).half()
+    ln = torch.where(pad[:, None], torch.zeros((), dtype=ln.dtype, device=ln.device), ln[row_map.clamp(min=0).long()])
+    ref = ops.quantize(ln, ops.GRAN_ROW, hadamard=spec)
+    d2 = (one["q"].int() - ref["q"].int()).abs()
+    assert int(d2.max()) <= 2 and float((d2 > 0).float().mean()) < 0.05
