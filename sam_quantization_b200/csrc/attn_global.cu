@@ -15,9 +15,10 @@
 //   warps 0-3  softmax: thread r owns query row r (= TMEM lane r).  Per key block: load the 64
 //              scores from tensor memory, t = s * scale * log2e + bias, row maximum, p = 2^(t - m),
 //              row sum, P as bf16/fp16 into shared memory in the 128-byte-swizzled operand layout.
-//              A block is one pass with the maximum m in use; only when a row exceeds it by more
-//              than 8 (p stays below 2^8 otherwise) is m raised, the pass repeated from the scores
-//              still in tensor memory, and the output accumulator rescaled in place.
+//              A block is one pass with the maximum m in use and no maximum taken; only when a row
+//              sum shows that some p passed 2^8 (p stays below 2^14 otherwise) is m raised, the pass
+//              repeated from the scores still in tensor memory, and the output accumulator rescaled
+//              in place.
 //   warp 4     TMA producer: Q once, then per block the K rows and the matching V^T columns
 //              (two stages).
 //   warp 5     MMA issuer: S = Q K^T (M128 N64 K=D) into one of two score buffers, and
@@ -259,9 +260,11 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             tcgen05_fence_after();
             // One pass over the block's 64 scores with a given reference maximum:
             //   e = s * scale * log2e + (rel_h + rel_w) * log2e - m_ref,  p = 2^e,
-            // two columns per instruction; returns max e, leaves P packed in pk and the row sum in `sum`.
+            // two columns per instruction; leaves P packed in pk and returns the row sum.  `row_max` is the
+            // same walk without the exponentials: it returns max e.
             uint32_t pk[BKEY / 2];
-            auto sweep = [&](float m_ref, float& sum) -> float {
+            auto walk = [&](auto with_exp, float m_ref) -> float {
+                constexpr bool EXP = decltype(with_exp)::value;
                 uint32_t s0[32], s1[32];
                 tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY), s0);
                 tmem_ld32(lane_base + (uint32_t)((i & 1) * BKEY + 32), s1);
@@ -281,31 +284,47 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     const float2 e0 = __ffma2_rn(make_float2(__uint_as_float(s0[j]), __uint_as_float(s0[j + 1])), c2, b0);
                     const float2 e1 = __ffma2_rn(make_float2(__uint_as_float(s1[j]), __uint_as_float(s1[j + 1])), c2, b1);
                     const int a = (j >> 1) & 1;
-                    mx[2 * a] = fmaxf(mx[2 * a], fmaxf(e0.x, e0.y));
-                    mx[2 * a + 1] = fmaxf(mx[2 * a + 1], fmaxf(e1.x, e1.y));
-                    const float2 p0 = make_float2(ex2(e0.x), ex2(e0.y));
-                    const float2 p1 = make_float2(ex2(e1.x), ex2(e1.y));
-                    ls2[2 * a] = __fadd2_rn(ls2[2 * a], p0);
-                    ls2[2 * a + 1] = __fadd2_rn(ls2[2 * a + 1], p1);
-                    pk[j >> 1] = AtOps<T>::pack(p0.x, p0.y);
-                    pk[16 + (j >> 1)] = AtOps<T>::pack(p1.x, p1.y);
+                    if constexpr (EXP) {
+                        const float2 p0 = make_float2(ex2(e0.x), ex2(e0.y));
+                        const float2 p1 = make_float2(ex2(e1.x), ex2(e1.y));
+                        ls2[2 * a] = __fadd2_rn(ls2[2 * a], p0);
+                        ls2[2 * a + 1] = __fadd2_rn(ls2[2 * a + 1], p1);
+                        pk[j >> 1] = AtOps<T>::pack(p0.x, p0.y);
+                        pk[16 + (j >> 1)] = AtOps<T>::pack(p1.x, p1.y);
+                    } else {
+                        mx[2 * a] = fmaxf(mx[2 * a], fmaxf(e0.x, e0.y));
+                        mx[2 * a + 1] = fmaxf(mx[2 * a + 1], fmaxf(e1.x, e1.y));
+                    }
                 }
-                const float2 a2 = __fadd2_rn(__fadd2_rn(ls2[0], ls2[1]), __fadd2_rn(ls2[2], ls2[3]));
-                sum = a2.x + a2.y;
-                return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                if constexpr (EXP) {
+                    const float2 a2 = __fadd2_rn(__fadd2_rn(ls2[0], ls2[1]), __fadd2_rn(ls2[2], ls2[3]));
+                    return a2.x + a2.y;
+                } else {
+                    return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                }
             };
-            // Optimistic pass with the maximum in use.  Only when some row of the warp exceeds it by
-            // more than 8 (p would pass 2^8), and on the first block, the maximum is raised and the
-            // pass repeated from the scores still in tensor memory.
-            float bsum;
-            const float e_max = sweep(m_used, bsum);
-            const bool raise = __any_sync(0xffffffffu, i == 0 || e_max > 8.0f);
+            auto sweep = [&](float m_ref) -> float { return walk(std::true_type{}, m_ref); };
+            auto row_max = [&](float m_ref) -> float { return walk(std::false_type{}, m_ref); };
+            // Optimistic pass with the maximum in use and no maximum taken: the row sum bounds the largest
+            // p from above (max p <= sum <= 64 max p), so a sum beyond 2^14 (an overflowed one included)
+            // tells that some p passed 2^8.  Only then, and on the first block, the true maximum is taken
+            // from the scores still in tensor memory, the reference raised and the pass repeated; P stays
+            // below 2^14 otherwise, inside the range of either 16-bit type.
+            float bsum = 0.f;
+            bool raise;
+            if (i == 0) {
+                raise = true;
+            } else {
+                bsum = sweep(m_used);
+                raise = __any_sync(0xffffffffu, !(bsum <= 16384.0f));
+            }
             float alpha = 1.0f;
             if (raise) {                                           // warp-uniform
+                const float e_max = row_max(m_used);
                 const float m_new = (i == 0) ? m_used + e_max : m_used + fmaxf(e_max, 0.f);
                 alpha = (i == 0) ? 0.f : ex2(m_used - m_new);     // nothing has been accumulated before the first block
                 m_used = m_new;
-                (void)sweep(m_used, bsum);
+                bsum = sweep(m_used);
                 l_sum *= alpha;
             }
             l_sum += bsum;

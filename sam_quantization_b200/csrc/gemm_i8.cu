@@ -214,6 +214,31 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if constexpr (!std::is_same<OutT, int32_t>::value) {
                 if (p.a_scale != nullptr && row_ok) a_s = p.a_scale[(int64_t)row * p.a_stride];
             }
+            // The residual block of a 32-column chunk is read coalesced (16 bytes per lane, whole row segments
+            // per instruction group) one chunk ahead of its use: chunk 0 before the wait for the MMAs, chunk
+            // c + 1 while chunk c is dequantised, so that the L2 latency is never on the epilogue's path.
+            constexpr int PER16_R = 16 / (int)sizeof(OutT);         // elements per 16-byte vector
+            constexpr int SEG = 32 / PER16_R;                       // 16-byte segments per 32-column row: 4 or 8
+            constexpr int ROWS_PER_LD = 32 / SEG;                   // rows covered by one warp-wide load
+            constexpr int NSEG = RES ? SEG : 1;
+            uint4 seg[2][NSEG];
+            auto res_chunk_fast = [&](int c) -> bool {              // warp-uniform: the chunk takes the coalesced route
+                return p.tma_store && p.vec_ok && n0 + half_n * 128 + c * 32 + 32 <= p.N;
+            };
+            auto load_res = [&](int c, uint4 (&sg)[NSEG]) {
+                const OutT* res_base = reinterpret_cast<const OutT*>(p.residual);
+                const int n_first = n0 + half_n * 128 + c * 32;
+#pragma unroll
+                for (int k = 0; k < NSEG; ++k) {
+                    const int grow = m0 + quad * 32 + k * ROWS_PER_LD + lane / SEG;
+                    sg[k] = grow < p.M
+                        ? *reinterpret_cast<const uint4*>(res_base + (int64_t)grow * p.ldr + n_first + (lane % SEG) * PER16_R)
+                        : make_uint4(0, 0, 0, 0);
+                }
+            };
+            if constexpr (RES) {
+                if (res_chunk_fast(0)) load_res(0, seg[0]);
+            }
             // after a failed wait keep visiting the named barrier above so no warp is left behind
             if (ok && !mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag, p.wait_limit)) ok = false;
             if (!ok) continue;
@@ -235,6 +260,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tmem_ld_wait();
                 if (c + 1 < 4) {
                     tmem_ld32(tmem_row + (uint32_t)((c + 1) * 32), rbuf[(c + 1) & 1]);
+                    if constexpr (RES) {
+                        if (res_chunk_fast(c + 1)) load_res(c + 1, seg[(c + 1) & 1]);
+                    }
                 } else {
                     tcgen05_fence_before();
                     __syncwarp();
@@ -255,22 +283,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if constexpr (GELU) gelu32(y);
                     if constexpr (RES) {
                         const OutT* res_base = reinterpret_cast<const OutT*>(p.residual);
-                        if (p.tma_store && p.vec_ok && n_valid == 32) {
-                            // coalesced: the warp reads its 32 x 32 residual block row-segment by
-                            // row-segment (16 bytes per lane, whole rows per instruction group), parks
-                            // it in the staging buffer in the swizzled layout, and every lane then
-                            // picks up its own row from there
-                            constexpr int SEG = 32 / PER16;                      // 16-byte segments per row: 4 or 8
-                            constexpr int ROWS_PER_LD = 32 / SEG;                // rows covered by one warp-wide load
-                            uint4 seg[SEG];
-#pragma unroll
-                            for (int k = 0; k < SEG; ++k) {
-                                const int rrow = k * ROWS_PER_LD + lane / SEG;
-                                const int grow = m0 + quad * 32 + rrow;
-                                seg[k] = grow < p.M
-                                    ? *reinterpret_cast<const uint4*>(res_base + (int64_t)grow * p.ldr + n_first + (lane % SEG) * PER16)
-                                    : make_uint4(0, 0, 0, 0);
-                            }
+                        if (res_chunk_fast(c)) {
+                            // the block fetched one chunk ago is parked in the staging buffer in the swizzled
+                            // layout, and every lane then picks up its own row from there
+                            uint4 (&sgc)[NSEG] = seg[c & 1];
                             if (lane == 0) bulk_wait_read0();                    // staging is free again
                             __syncwarp();
 #pragma unroll
@@ -282,7 +298,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                     const int sg = lane % SEG;
                                     if (sg / 4 == part)
                                         *reinterpret_cast<uint4*>(stage_ptr + rrow * 64 +
-                                            ((((uint32_t)(sg & 3)) ^ (uint32_t)((rrow >> 1) & 3)) << 4)) = seg[k];
+                                            ((((uint32_t)(sg & 3)) ^ (uint32_t)((rrow >> 1) & 3)) << 4)) = sgc[k];
                                 }
                                 __syncwarp();
 #pragma unroll
