@@ -5,7 +5,6 @@ import ctypes
 import os
 import re
 
-
 from sam_quantization_b200 import _lib
 
 HEADER = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "samq.h")
@@ -28,8 +27,17 @@ def test_header_and_binding_list_the_same_entry_points():
     assert set(names) == set(_lib.EXPORTED_SYMBOLS)
 
 
+def built_library():
+    """Path of libsamq.so, compiled first when a fresh checkout has not built it yet (nvcc cross-
+    compiles without a GPU; a few minutes, once)."""
+    if not os.path.exists(_lib.LIB_PATH):
+        from sam_quantization_b200.build import build_library
+        build_library()
+    return _lib.LIB_PATH
+
+
 def test_library_loads_and_exports_every_declared_symbol():
-    assert os.path.exists(_lib.LIB_PATH), "build it with `python -m sam_quantization_b200.build`"
+    assert os.path.exists(built_library())
     raw = ctypes.CDLL(_lib.LIB_PATH)                             # no argtypes: the dynamic symbol table only
     for name in declared_functions():
         assert hasattr(raw, name), name
@@ -52,6 +60,7 @@ def test_no_torch_types_cross_the_boundary():
 def test_argument_checks_answer_without_a_device():
     """Entry points validate before they launch: a null operand or a bad enum comes back as a
     non-zero status with a message, not as a crash (none of these calls reaches the GPU)."""
+    built_library()
     lib = _lib.load()
     assert lib.samq_quant_workspace_bytes(1) >= 4               # per_tensor needs its absmax slot
     assert lib.samq_quant_workspace_bytes(0) == 0
