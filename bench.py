@@ -303,7 +303,10 @@ def run_ours(args):
         model, twin = build_quantized_encoder(args.model, dev, recipe=args.recipe, with_twin=True)
     else:
         model = build_quantized_encoder(args.model, dev, recipe=args.recipe)
-    enc = EncoderRunner(model, chunk, device=dev, use_graph=not args.no_graph)
+    lanes = max(1, args.lanes)
+    while chunk % lanes:                                          # every lane takes the same number of images
+        lanes -= 1
+    enc = EncoderRunner(model, chunk, device=dev, use_graph=not args.no_graph, lanes=lanes)
 
     # this rank's shard of the global batch: images [rank*local_n, (rank+1)*local_n), seeded per image
     host = torch.empty((local_n, 3, 1024, 1024), dtype=torch.float16).pin_memory()
@@ -423,7 +426,8 @@ def run_ours(args):
             "warmup": args.warmup, "warmup_steps_run": warm_steps, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": workload_name(args.model, args.recipe),
-                       "step": f"the global batch sharded by image over {world} rank(s), {chunk} images per forward",
+                       "step": f"the global batch sharded by image over {world} rank(s), {chunk} images per forward"
+                               + (f" on {enc.lanes} concurrent streams" if enc.lanes > 1 else ""),
                        "l2": "inputs and activations per forward exceed the 126 MB L2", "parallelism": f"dp{world}",
                        "cuda_graph": not args.no_graph},
             "e2e": {"value": e2e_value, "unit": "images/s",
@@ -480,6 +484,7 @@ def main():
     ap.add_argument("--recipe", default="smoothquant", choices=list(RECIPES),
                     help="what precedes W8A8 (the headline configuration is vit_h + smoothquant)")
     ap.add_argument("--chunk", type=int, default=32, help="images per encoder forward (capped by the rank's share of the batch)")
+    ap.add_argument("--lanes", type=int, default=1, help="concurrent streams a forward's images are split over inside the CUDA graph")
     ap.add_argument("--ref-budget", dest="ref_budget", type=float, default=25.0, help="seconds of CPU work per reference sample")
     ap.add_argument("--no-cpu-baseline", dest="no_cpu_baseline", action="store_true")
     ap.add_argument("--no-graph", dest="no_graph", action="store_true", help="run the encoder eagerly instead of replaying a CUDA graph")

@@ -21,21 +21,28 @@ class EncoderRunner:
     output: it is overwritten by the next call, so copy it if it must outlive that call.
 
     The GEMM and attention kernels give up on a stalled pipeline after a bounded wait and raise a
-    device status word instead of hanging; their output is then incomplete.  ``check_status=True``
+    device status word instead of hanging; their output is then incomplete.  ``lanes`` > 1 (graph mode
+    only) encodes the batch as that many independent sub-batches on concurrent streams inside the one
+    graph; results are identical, image by image.  ``check_status=True``
     makes every call synchronise and raise ``RuntimeError`` in that case; otherwise call
     ``runner.check()`` (or ``ops.check_status``) wherever the caller synchronises anyway."""
 
     def __init__(self, model: torch.nn.Module, batch: int, img_size: int = 1024, dtype: torch.dtype = torch.float16,
-                 device: Optional[torch.device] = None, use_graph: bool = True, warmup: int = 3, check_status: bool = False):
+                 device: Optional[torch.device] = None, use_graph: bool = True, warmup: int = 3, check_status: bool = False,
+                 lanes: int = 1):
         self.check_status = bool(check_status)
         self.encoder = getattr(model, "image_encoder", model)
         self.device = torch.device(device) if device is not None else next(self.encoder.parameters()).device
         if self.device.type != "cuda":
             raise RuntimeError("EncoderRunner needs a CUDA device")
+        self.lanes = int(lanes) if use_graph else 1
+        if self.lanes < 1 or batch % self.lanes:
+            raise ValueError(f"batch {batch} is not a multiple of lanes {lanes}")
         self.batch = batch
         self._copy_stream = None
         self.static_in = torch.zeros((batch, 3, img_size, img_size), dtype=dtype, device=self.device)
         self.graph = None
+        per_lane = batch // self.lanes
         with torch.no_grad(), torch.cuda.device(self.device):
             side = torch.cuda.Stream(device=self.device)
             side.wait_stream(torch.cuda.current_stream(self.device))
@@ -44,10 +51,36 @@ class EncoderRunner:
                     self.static_out = self.encoder(self.static_in)
             torch.cuda.current_stream(self.device).wait_stream(side)
             torch.cuda.synchronize(self.device)
+            lane_streams = []
+            if self.lanes > 1:
+                # every lane once outside the capture: per-stream library workspaces and the caches keyed
+                # by the lane's batch size exist before the graph is recorded
+                lane_streams = [torch.cuda.Stream(device=self.device) for _ in range(self.lanes)]
+                for k, st in enumerate(lane_streams):
+                    with torch.cuda.stream(st):
+                        self.static_out[k * per_lane:(k + 1) * per_lane].copy_(
+                            self.encoder(self.static_in[k * per_lane:(k + 1) * per_lane]))
+                torch.cuda.synchronize(self.device)
             if use_graph:
                 self.graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(self.graph):
-                    self.static_out = self.encoder(self.static_in)
+                    if self.lanes == 1:
+                        self.static_out = self.encoder(self.static_in)
+                    else:
+                        # The batch is split over `lanes` streams that fork from and join the capturing
+                        # stream.  The lanes run the same kernel sequence on different images; a
+                        # persistent GEMM fills every SM, so two GEMMs take turns, and the memory-bound
+                        # kernels of one lane (quantization, LayerNorm) find room beside the GEMM of the
+                        # other instead of leaving the tensor cores idle while they run.
+                        main = torch.cuda.current_stream(self.device)
+                        self.static_out = torch.empty_like(self.static_out)
+                        for k, st in enumerate(lane_streams):
+                            st.wait_stream(main)
+                            with torch.cuda.stream(st):
+                                self.static_out[k * per_lane:(k + 1) * per_lane].copy_(
+                                    self.encoder(self.static_in[k * per_lane:(k + 1) * per_lane]))
+                        for st in lane_streams:
+                            main.wait_stream(st)
 
     @torch.no_grad()
     def __call__(self, images: torch.Tensor) -> torch.Tensor:

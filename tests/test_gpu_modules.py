@@ -559,3 +559,30 @@ def test_encoder_runner_encode_overlaps_copies_and_matches_direct_calls(cuda_dev
     assert torch.equal(dev_out, want)
     with pytest.raises(ValueError):
         runner.encode(host_in[:3], host_out[:3])
+
+
+def test_runner_lanes_give_the_same_embeddings(cuda_device):
+    """``EncoderRunner(lanes=2)`` records the forward of a batch as two sub-batches on concurrent
+    streams inside one graph: image by image the embeddings equal the single-stream runner's and the
+    eager model's, call after call."""
+    from sam_quantization_b200.RTN_quantization import W8A8Linear, replace_linear_with_target_and_quantize
+    from sam_quantization_b200.engine import EncoderRunner
+    dev = cuda_device
+    mine, _ = _tiny_pair(dev, torch.float16, torch.bfloat16)
+    replace_linear_with_target_and_quantize(mine, W8A8Linear, 8, [])
+    size = TINY["img_size"]
+    imgs = torch.cat([tiny_images(seed=400 + i) for i in range(4)], 0)[:8].half().to(dev)     # 8 images
+    with torch.no_grad():
+        want = torch.cat([mine(imgs[i:i + 2]) for i in range(0, 8, 2)], 0)
+    one = EncoderRunner(mine, 4, img_size=size, device=dev)
+    two = EncoderRunner(mine, 4, img_size=size, device=dev, lanes=2, check_status=True)
+    assert two.lanes == 2
+    for _ in range(3):
+        for i in (0, 4):
+            a = one(imgs[i:i + 4]).clone()
+            b = two(imgs[i:i + 4]).clone()
+            torch.cuda.synchronize()
+            assert torch.equal(a, want[i:i + 4]) and torch.equal(b, want[i:i + 4])
+    with pytest.raises(ValueError):
+        EncoderRunner(mine, 3, img_size=size, device=dev, lanes=2)
+    assert EncoderRunner(mine, 4, img_size=size, device=dev, lanes=2, use_graph=False).lanes == 1
