@@ -303,6 +303,9 @@ def run_ours(args):
         model, twin = build_quantized_encoder(args.model, dev, recipe=args.recipe, with_twin=True)
     else:
         model = build_quantized_encoder(args.model, dev, recipe=args.recipe)
+    if args.pair_mode is not None:
+        from sam_quantization_b200 import ops as _ops
+        _ops.set_gemm_pair_mode(args.pair_mode)
     lanes = max(1, args.lanes)
     while chunk % lanes:                                          # every lane takes the same number of images
         lanes -= 1
@@ -484,6 +487,8 @@ def main():
     ap.add_argument("--recipe", default="smoothquant", choices=list(RECIPES),
                     help="what precedes W8A8 (the headline configuration is vit_h + smoothquant)")
     ap.add_argument("--chunk", type=int, default=32, help="images per encoder forward (capped by the rank's share of the batch)")
+    ap.add_argument("--pair-mode", dest="pair_mode", type=int, default=None, choices=[0, 1, 2],
+                    help="int8 GEMM implementation: 0 single CTAs, 1 by size (the library's default), 2 CTA pairs everywhere")
     ap.add_argument("--lanes", type=int, default=1, help="concurrent streams a forward's images are split over inside the CUDA graph")
     ap.add_argument("--ref-budget", dest="ref_budget", type=float, default=25.0, help="seconds of CPU work per reference sample")
     ap.add_argument("--no-cpu-baseline", dest="no_cpu_baseline", action="store_true")
