@@ -950,45 +950,61 @@ hadamard_pow4_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, c
         // LayerNorm of the row before the transform, in the same pass (the two-kernel route writes the
         // normalised fp16 tensor and reads it back): fp32 two-pass statistics over the NT threads of the
         // row, y = half(gamma * (rstd * (x - mean)) + beta) as in quant_rows_fast_kernel; a gathered zero
-        // row stays zero (the padding of window_partition comes after the norm)
+        // row stays zero (the padding of window_partition comes after the norm).  gamma / beta sit in
+        // shared memory as fp32 quads, converted once per CTA: quad c of thread t at index c * NT + t, so
+        // that the threads of a row read neighbouring 16-byte slots.  The statistics cross the WPR warps
+        // of a row through shared memory and a barrier of their own (id 1 + row), not a CTA barrier.
         constexpr int WPR = NT / 32;
+        __shared__ float4 ln_gb[2][4 * NT];
         __shared__ float ln_red[2][8];
-        float sum = 0.f;
+        for (int q = threadIdx.x; q < 2 * (K / 8); q += 256) {          // one 16-byte load of 8 halves each
+            const int which = q / (K / 8), o = q - which * (K / 8);     // 0: gamma, 1: beta; o: which eight columns
+            float f[8];
+            unpack<__half>(*reinterpret_cast<const uint4*>((which ? beta : gamma) + 8 * o), f);
+            const int tt = o >> 1, c0 = (o & 1) * 2;                    // owner thread of the columns, its first quad
+            ln_gb[which][c0 * NT + tt] = make_float4(f[0], f[1], f[2], f[3]);
+            ln_gb[which][(c0 + 1) * NT + tt] = make_float4(f[4], f[5], f[6], f[7]);
+        }
+        float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) sum += v[j];
+        for (int j = 0; j < 16; j += 2) acc = __fadd2_rn(acc, make_float2(v[j], v[j + 1]));
+        float sum = acc.x + acc.y;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         if ((threadIdx.x & 31) == 0) ln_red[0][threadIdx.x >> 5] = sum;
-        __syncthreads();
+        __syncthreads();                                                 // also publishes ln_gb
         sum = 0.f;
 #pragma unroll
         for (int w = 0; w < WPR; ++w) sum += ln_red[0][r_in * WPR + w];
         const float mean = sum / (float)K;
-        float var = 0.f;
+        const float2 nmean = make_float2(-mean, -mean);
+        float2 d[8];
+        acc = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) { v[j] -= mean; var = fmaf(v[j], v[j], var); }
+        for (int j = 0; j < 8; ++j) {
+            d[j] = __fadd2_rn(make_float2(v[2 * j], v[2 * j + 1]), nmean);
+            acc = __ffma2_rn(d[j], d[j], acc);
+        }
+        float var = acc.x + acc.y;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
         if ((threadIdx.x & 31) == 0) ln_red[1][threadIdx.x >> 5] = var;
-        __syncthreads();
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + r_in), "r"(NT) : "memory");
         var = 0.f;
 #pragma unroll
         for (int w = 0; w < WPR; ++w) var += ln_red[1][r_in * WPR + w];
         const float rstd = rsqrtf(var / (float)K + ln_eps);
         if (src >= 0) {
-            float g[16], b[16];
+            const float2 rstd2 = make_float2(rstd, rstd);
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                float f[8];
-                unpack<__half>(*reinterpret_cast<const uint4*>(gamma + 16 * t + 8 * i), f);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) g[i * 8 + e] = f[e];
-                unpack<__half>(*reinterpret_cast<const uint4*>(beta + 16 * t + 8 * i), f);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) b[i * 8 + e] = f[e];
+            for (int c = 0; c < 4; ++c) {
+                const float4 g = ln_gb[0][c * NT + t], bb = ln_gb[1][c * NT + t];
+                const float2 y0 = __ffma2_rn(make_float2(g.x, g.y), __fmul2_rn(rstd2, d[2 * c]), make_float2(bb.x, bb.y));
+                const float2 y1 = __ffma2_rn(make_float2(g.z, g.w), __fmul2_rn(rstd2, d[2 * c + 1]), make_float2(bb.z, bb.w));
+                const float2 r0 = __half22float2(__floats2half2_rn(y0.x, y0.y));
+                const float2 r1 = __half22float2(__floats2half2_rn(y1.x, y1.y));
+                v[4 * c] = r0.x; v[4 * c + 1] = r0.y; v[4 * c + 2] = r1.x; v[4 * c + 3] = r1.y;
             }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = __half2float(__float2half_rn(fmaf(g[j], rstd * v[j], b[j])));
         } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = 0.f;
