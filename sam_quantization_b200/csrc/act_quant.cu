@@ -907,7 +907,7 @@ hadamard_quant_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx,
 // a warp barrier), index bits 8 and up for the rest (CTA barrier); the division by sqrt(K) (32 or
 // 64) is an exact scaling.  Shared-memory slot of element i of a row: i + i / 16.  The dispatch sends
 // 1024-point rows here (optionally with the LayerNorm of the source row in front: LN) and 4096-point
-// rows to hadamard_4096_quant_kernel below.
+// rows to hadamard_4096_r64_kernel below.
 // ---------------------------------------------------------------------------
 template <typename SrcT, int K, bool LN>
 __global__ void __launch_bounds__(256, LN ? 4 : 6)
@@ -1094,108 +1094,167 @@ hadamard_pow4_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, c
 }
 
 // ---------------------------------------------------------------------------
-// The 4096-point transform again (ViT-L `lin2` input, the largest K1 of the QuaRot configuration), with
-// the three regroupings of the row between its register passes done with 16-byte shared-memory
-// accesses wherever the data allows it: 57 shared-memory instructions per thread instead of 96.  Same
-// butterflies on the same values in the same order as the generic kernel and as hadamard_pow4_quant_kernel<., 1024, .>.  256 threads per row, one row per CTA.
-//   pass A  thread t = 16 g + l owns elements 16 t + j            (index bits 0..3 in registers)
-//   X1      rows of 16 floats, 20-float pitch, written with 4 x STS.128; column l read back
-//   pass B  thread (g, l) owns elements 256 g + 16 j + l           (bits 4..7)
-//   X2      element 256 g + c goes to slot 20 c + g; thread c reads its row with 4 x LDS.128
-//   pass C  thread c owns elements 256 g + c                       (bits 8..11), then scale, round, absmax
-//   X3      codes as bytes at 256 g + c; thread t reads its 16 consecutive codes with one LDS.128
+// The 4096-point transform with 64 points per thread: 4096 = 64 x 64, so the twelve butterfly stages
+// are two register passes (index bits 0..5, then 6..11, the reference's stage order) with ONE
+// regrouping of the row through shared memory between them, instead of three passes and two
+// regroupings at 16 points per thread.  A CTA is 64 threads (two warps) and walks rows in a loop:
+//   load    the row arrives through cp.async, 16 bytes per thread and instruction, coalesced in global
+//           memory and scattered to a padded layout (144-byte pitch per owner thread) so that every
+//           thread then reads its own 64 consecutive values with conflict-free 16-byte loads; the
+//           next row's copies are issued as soon as pass A has left the staging buffer, and travel
+//           during the rest of the row (27 KB of shared memory and 121 registers: 8 CTAs per SM)
+//   pass A  thread t owns elements 64 t + j
+//   X       rows of 64 floats at a 68-float pitch, written with 16 x STS.128, column u read back
+//   pass B  thread u owns elements 64 j + u, then the exact scaling by 1/64, one rounding to fp16,
+//           the row maximum, the codes
+//   codes   as bytes at 64 j + u, read back 16 bytes per thread in row order and stored coalesced
+// Same values in the same order as every other kernel of the family: bit-identical results.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ void butterfly64(float (&v)[64]) {
+    float2 p[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) p[i] = make_float2(v[i], v[i + 32]);
+    const float2 neg1 = make_float2(-1.f, -1.f);
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if ((i & s) == 0) {
+                const float2 a = p[i], c = p[i | s];
+                p[i] = __fadd2_rn(a, c);
+                p[i | s] = __ffma2_rn(c, neg1, a);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) { v[i] = p[i].x + p[i].y; v[i + 32] = p[i].x - p[i].y; }
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                 ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+
+// SMs of the current device (a grid of resident CTAs is sized from it)
+inline int device_sm_count() {
+    static thread_local int cached_dev = -1;
+    static thread_local int cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev != cached_dev) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached = n; cached_dev = dev;
+    }
+    return cached;
+}
+
 template <typename SrcT>
-__global__ void __launch_bounds__(256, 5)
-hadamard_4096_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, const int32_t* __restrict__ row_map,
-                           const int8_t* __restrict__ signs, float qmax,
-                           int8_t* __restrict__ q_out, float* __restrict__ scale_out)
+__global__ void __launch_bounds__(64, 8)
+hadamard_4096_r64_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, const int32_t* __restrict__ row_map,
+                         const int8_t* __restrict__ signs, float qmax,
+                         int8_t* __restrict__ q_out, float* __restrict__ scale_out)
 {
     constexpr int K = 4096;
-    constexpr int BLK = 336;                                   // 16 rows x 20 floats + 16: half-warps land 16 banks apart
-    __shared__ __align__(16) float x1[16 * BLK];               // also the byte codes of X3
-    __shared__ __align__(16) float x2[256 * 20];
-    __shared__ float red[8];
-    const int t = threadIdx.x, g = t >> 4, l = t & 15;
-    const int64_t row = blockIdx.x;
-    int64_t src = row_map != nullptr ? (int64_t)row_map[row] : row;
-    float v[16];
-    if (src >= 0) {
-        const SrcT* xr = x + src * ldx + 16 * t;
+    constexpr int SPITCH = 144;                                 // bytes per owner thread in the staging buffer: 128 + 16
+    constexpr int XPITCH = 68;                                  // floats per row of X
+    __shared__ __align__(16) uint8_t stage[64 * SPITCH];
+    __shared__ __align__(16) float xs[64 * XPITCH];             // X, then the byte codes
+    __shared__ float red[2][2];
+    const int t = threadIdx.x;
+    auto source_row = [&](int64_t row) -> int64_t { return row_map != nullptr ? (int64_t)row_map[row] : row; };
+    auto fetch = [&](int64_t src) {                             // one row into the staging buffer (nothing for a zero row)
+        if (src >= 0) {
+            const uint8_t* g = reinterpret_cast<const uint8_t*>(x + src * ldx);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            float f[8];
-            unpack<SrcT>(ld_stream(xr + i * 8), f);
-            if (!std::is_same<SrcT, __half>::value) RoundVec<__half, 8>::run(f);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[i * 8 + e] = f[e];
+            for (int i = 0; i < 8; ++i) {
+                const int c = i * 64 + t;                       // 16-byte chunk of the row; owner c / 8, position c % 8
+                cp_async16(&stage[(c >> 3) * SPITCH + (c & 7) * 16], g + 16 * c);
+            }
         }
-    } else {
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    int64_t row = blockIdx.x;
+    int64_t src = row < M ? source_row(row) : -1;
+    if (row < M) fetch(src);
+    for (int it = 0; row < M; ++it, row += gridDim.x) {
+        const int64_t next = row + gridDim.x;
+        const int64_t next_src = next < M ? source_row(next) : -1;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                        // the row is in the staging buffer; xs is free
+        float v[64];
+        if (src >= 0) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+            for (int k = 0; k < 8; ++k) {
+                float f[8];
+                unpack<SrcT>(*reinterpret_cast<const uint4*>(&stage[t * SPITCH + k * 16]), f);
+                if (!std::is_same<SrcT, __half>::value) RoundVec<__half, 8>::run(f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[k * 8 + e] = f[e];
+            }
+            if (signs != nullptr) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint4 sg = *reinterpret_cast<const uint4*>(signs + 64 * t + 16 * k);
+                    const uint32_t w[4] = {sg.x, sg.y, sg.z, sg.w};
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if ((w[j >> 2] >> (8 * (j & 3))) & 0x80u) v[k * 16 + j] = -v[k * 16 + j];
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = 0.f;
+        }
+        butterfly64(v);                                         // pass A: index bits 0..5
+#pragma unroll
+        for (int q = 0; q < 16; ++q)
+            *reinterpret_cast<float4*>(xs + t * XPITCH + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        __syncthreads();                                        // X is complete, and nobody reads the staging buffer any more:
+        if (next < M) fetch(next_src);                          // the next row travels while this one is transformed
+#pragma unroll
+        for (int j = 0; j < 64; ++j) v[j] = xs[j * XPITCH + t];
+        butterfly64(v);                                         // pass B: bits 6..11; v[j] is element 64 j + t
+        float m = 0.f;
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {                       // divide by sqrt(4096) (exact), round once to fp16, absolute maximum
+            const __half2 h = __floats2half2_rn(v[i] * 0.015625f, v[i + 1] * 0.015625f);
+            const __half2 a = __habs2(h);
+            m = fmaxf(m, fmaxf(__low2float(a), __high2float(a)));
+            const float2 f = __half22float2(h);
+            v[i] = f.x; v[i + 1] = f.y;
+        }
+        m = warp_max(m);
+        if ((t & 31) == 0) red[it & 1][t >> 5] = m;
+        __syncthreads();                                        // also: every thread is past its reads of X
+        m = fmaxf(red[it & 1][0], red[it & 1][1]);
+        const float sc = scale_from_absmax<__half>(m, qmax);
+        if (t == 0 && scale_out != nullptr) scale_out[row] = sc;
+        const float inv = __frcp_rn(sc);
+        const float2 inv2 = make_float2(inv, inv), ns2 = make_float2(-sc, -sc);
+        const __half2 hi2 = __float2half2_rn(qmax), lo2 = __float2half2_rn(-qmax), magic = __float2half2_rn(1536.0f);
+        uint8_t* codes = reinterpret_cast<uint8_t*>(xs);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float2 f = make_float2(v[2 * j], v[2 * j + 1]);
+            const float2 y0 = __fmul2_rn(f, inv2);
+            const float2 e = __ffma2_rn(y0, ns2, f);
+            const float2 y = __ffma2_rn(e, inv2, y0);
+            __half2 h = __floats2half2_rn(y.x, y.y);
+            h = __hadd2(__hmin2(__hmax2(h, lo2), hi2), magic);
+            const uint32_t hb = *reinterpret_cast<uint32_t*>(&h);
+            codes[64 * (2 * j) + t] = (uint8_t)(hb & 0xFFu);
+            codes[64 * (2 * j + 1) + t] = (uint8_t)((hb >> 16) & 0xFFu);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = i * 64 + t;                           // 16 consecutive codes of the row
+            *reinterpret_cast<uint4*>(q_out + row * K + 16 * c) = *reinterpret_cast<const uint4*>(codes + 16 * c);
+        }
+        src = next_src;
+        // the next iteration's first barrier orders these reads of the codes before X is written again
     }
-    if (src >= 0 && signs != nullptr) {
-        const uint4 sg = *reinterpret_cast<const uint4*>(signs + 16 * t);
-        const uint32_t w[4] = {sg.x, sg.y, sg.z, sg.w};
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-            if ((w[j >> 2] >> (8 * (j & 3))) & 0x80u) v[j] = -v[j];
-    }
-    butterfly16(v);                                            // pass A: index bits 0..3
-    {
-        float* blk = x1 + g * BLK;                             // X1: the 16 threads of a half-warp transpose their 16 x 16 block
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<float4*>(blk + l * 20 + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = blk[j * 20 + l];
-    }
-    butterfly16(v);                                            // pass B: bits 4..7; v[j] is element 256 g + 16 j + l
-#pragma unroll
-    for (int j = 0; j < 16; ++j) x2[(16 * j + l) * 20 + g] = v[j];   // X2
-    __syncthreads();
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const float4 f = *reinterpret_cast<const float4*>(x2 + t * 20 + 4 * q);
-        v[4 * q] = f.x; v[4 * q + 1] = f.y; v[4 * q + 2] = f.z; v[4 * q + 3] = f.w;
-    }
-    butterfly16(v);                                            // pass C: bits 8..11; v[gg] is element 256 gg + t
-    float m = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; i += 2) {                          // divide by sqrt(4096) (exact), round once to fp16, absolute maximum
-        const __half2 h = __floats2half2_rn(v[i] * 0.015625f, v[i + 1] * 0.015625f);
-        const __half2 a = __habs2(h);
-        m = fmaxf(m, fmaxf(__low2float(a), __high2float(a)));
-        const float2 f = __half22float2(h);
-        v[i] = f.x; v[i + 1] = f.y;
-    }
-    m = warp_max(m);
-    if ((t & 31) == 0) red[t >> 5] = m;
-    __syncthreads();
-    m = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) m = fmaxf(m, red[w]);
-    const float sc = scale_from_absmax<__half>(m, qmax);
-    if (t == 0 && scale_out != nullptr) scale_out[row] = sc;
-    const float inv = __frcp_rn(sc);
-    const float2 inv2 = make_float2(inv, inv), ns2 = make_float2(-sc, -sc);
-    const __half2 hi2 = __float2half2_rn(qmax), lo2 = __float2half2_rn(-qmax), magic = __float2half2_rn(1536.0f);
-    uint8_t* codes = reinterpret_cast<uint8_t*>(x1);           // X3 (every thread is past its X1 reads: two barriers ago)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float2 f = make_float2(v[2 * j], v[2 * j + 1]);
-        const float2 y0 = __fmul2_rn(f, inv2);
-        const float2 e = __ffma2_rn(y0, ns2, f);
-        const float2 y = __ffma2_rn(e, inv2, y0);
-        __half2 h = __floats2half2_rn(y.x, y.y);
-        h = __hadd2(__hmin2(__hmax2(h, lo2), hi2), magic);
-        const uint32_t hb = *reinterpret_cast<uint32_t*>(&h);
-        codes[256 * (2 * j) + t] = (uint8_t)(hb & 0xFFu);
-        codes[256 * (2 * j + 1) + t] = (uint8_t)((hb >> 16) & 0xFFu);
-    }
-    __syncthreads();
-    *reinterpret_cast<uint4*>(q_out + row * K + 16 * t) = *reinterpret_cast<const uint4*>(codes + 16 * t);
 }
 
 // ---------------------------------------------------------------------------
@@ -1436,7 +1495,9 @@ static int quant_typed(const SrcT* x, int64_t M, int K, int64_t ldx, const Prolo
                 const __half* g = static_cast<const __half*>(pro.ln_gamma);
                 const __half* b = static_cast<const __half*>(pro.ln_beta);
                 if (K == 4096) {
-                    hadamard_4096_quant_kernel<SrcT><<<(unsigned)M, 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, qmax, q, scale);
+                    const int64_t resident = (int64_t)device_sm_count() * 8;                 // 27 KB of shared memory, 121 registers per thread
+                    hadamard_4096_r64_kernel<SrcT><<<(unsigned)(M < resident ? M : resident), 64, 0, st>>>(
+                        x, M, ldx, pro.row_map, had->signs, qmax, q, scale);
                 } else {
                     const unsigned grid = (unsigned)((M + 3) / 4);
                     if (ln_had) hadamard_pow4_quant_kernel<SrcT, 1024, true><<<grid, 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, g, b, pro.ln_eps, qmax, q, scale);
