@@ -899,201 +899,6 @@ hadamard_quant_kernel(const SrcT* __restrict__ x, int64_t M, int K, int64_t ldx,
 }
 
 // ---------------------------------------------------------------------------
-// The 1024- and 4096-point transforms on their own (ViT-L `qkv` / `lin1` / `lin2` inputs): fp16
-// arithmetic, codes only.  Same arithmetic and stage order as hadamard_quant_kernel, with every
-// address a compile-time constant: K / 16 threads per row (a CTA of 256 threads holds 256 * 16 / K
-// rows), thread t of a row owns elements [16t, 16t + 16) for the first four stages (registers),
-// elements differing in index bits 4..7 for the next four (their owners sit in the same half-warp:
-// a warp barrier), index bits 8 and up for the rest (CTA barrier); the division by sqrt(K) (32 or
-// 64) is an exact scaling.  Shared-memory slot of element i of a row: i + i / 16.  The dispatch sends
-// 1024-point rows here (optionally with the LayerNorm of the source row in front: LN) and 4096-point
-// rows to hadamard_4096_r64_kernel below.
-// ---------------------------------------------------------------------------
-template <typename SrcT, int K, bool LN>
-__global__ void __launch_bounds__(256, LN ? 4 : 6)
-hadamard_pow4_quant_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, const int32_t* __restrict__ row_map,
-                           const int8_t* __restrict__ signs, const __half* __restrict__ gamma,
-                           const __half* __restrict__ beta, float ln_eps, float qmax,
-                           int8_t* __restrict__ q_out, float* __restrict__ scale_out)
-{
-    static_assert(K == 1024 || K == 4096, "lengths whose square root is a power of two");
-    constexpr int NT = K / 16;                                 // threads per row
-    constexpr int ROWS = 256 / NT;                             // rows per CTA
-    constexpr int R = K / 256;                                 // points of the last pass: 4 or 16
-    constexpr int PITCH = K + K / 16 + 8;
-    constexpr float INV_ROOT = K == 4096 ? 0.015625f : 0.03125f;
-    __shared__ float sm_all[ROWS * PITCH];
-    __shared__ float red[8];
-    const int r_in = threadIdx.x / NT;                         // row inside the CTA
-    const int t = threadIdx.x - r_in * NT;                     // thread inside the row
-    float* sm = sm_all + r_in * PITCH;
-    const int64_t row = (int64_t)blockIdx.x * ROWS + r_in;
-    const bool active = row < M;
-    int64_t src = -1;
-    if (active) src = row_map != nullptr ? (int64_t)row_map[row] : row;
-    float v[16];
-    if (src >= 0) {
-        const SrcT* xr = x + src * ldx + 16 * t;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            float f[8];
-            unpack<SrcT>(ld_stream(xr + i * 8), f);
-            if (!std::is_same<SrcT, __half>::value) RoundVec<__half, 8>::run(f);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[i * 8 + e] = f[e];
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = 0.f;
-    }
-    if constexpr (LN) {
-        // LayerNorm of the row before the transform, in the same pass (the two-kernel route writes the
-        // normalised fp16 tensor and reads it back): fp32 two-pass statistics over the NT threads of the
-        // row, y = half(gamma * (rstd * (x - mean)) + beta) as in quant_rows_fast_kernel; a gathered zero
-        // row stays zero (the padding of window_partition comes after the norm).  gamma / beta sit in
-        // shared memory as fp32 quads, converted once per CTA: quad c of thread t at index c * NT + t, so
-        // that the threads of a row read neighbouring 16-byte slots.  The statistics cross the WPR warps
-        // of a row through shared memory and a barrier of their own (id 1 + row), not a CTA barrier.
-        constexpr int WPR = NT / 32;
-        __shared__ float4 ln_gb[2][4 * NT];
-        __shared__ float ln_red[2][8];
-        for (int q = threadIdx.x; q < 2 * (K / 8); q += 256) {          // one 16-byte load of 8 halves each
-            const int which = q / (K / 8), o = q - which * (K / 8);     // 0: gamma, 1: beta; o: which eight columns
-            float f[8];
-            unpack<__half>(*reinterpret_cast<const uint4*>((which ? beta : gamma) + 8 * o), f);
-            const int tt = o >> 1, c0 = (o & 1) * 2;                    // owner thread of the columns, its first quad
-            ln_gb[which][c0 * NT + tt] = make_float4(f[0], f[1], f[2], f[3]);
-            ln_gb[which][(c0 + 1) * NT + tt] = make_float4(f[4], f[5], f[6], f[7]);
-        }
-        float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int j = 0; j < 16; j += 2) acc = __fadd2_rn(acc, make_float2(v[j], v[j + 1]));
-        float sum = acc.x + acc.y;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if ((threadIdx.x & 31) == 0) ln_red[0][threadIdx.x >> 5] = sum;
-        __syncthreads();                                                 // also publishes ln_gb
-        sum = 0.f;
-#pragma unroll
-        for (int w = 0; w < WPR; ++w) sum += ln_red[0][r_in * WPR + w];
-        const float mean = sum / (float)K;
-        const float2 nmean = make_float2(-mean, -mean);
-        float2 d[8];
-        acc = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            d[j] = __fadd2_rn(make_float2(v[2 * j], v[2 * j + 1]), nmean);
-            acc = __ffma2_rn(d[j], d[j], acc);
-        }
-        float var = acc.x + acc.y;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
-        if ((threadIdx.x & 31) == 0) ln_red[1][threadIdx.x >> 5] = var;
-        asm volatile("bar.sync %0, %1;" ::"r"(1 + r_in), "r"(NT) : "memory");
-        var = 0.f;
-#pragma unroll
-        for (int w = 0; w < WPR; ++w) var += ln_red[1][r_in * WPR + w];
-        const float rstd = rsqrtf(var / (float)K + ln_eps);
-        if (src >= 0) {
-            const float2 rstd2 = make_float2(rstd, rstd);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float4 g = ln_gb[0][c * NT + t], bb = ln_gb[1][c * NT + t];
-                const float2 y0 = __ffma2_rn(make_float2(g.x, g.y), __fmul2_rn(rstd2, d[2 * c]), make_float2(bb.x, bb.y));
-                const float2 y1 = __ffma2_rn(make_float2(g.z, g.w), __fmul2_rn(rstd2, d[2 * c + 1]), make_float2(bb.z, bb.w));
-                const float2 r0 = __half22float2(__floats2half2_rn(y0.x, y0.y));
-                const float2 r1 = __half22float2(__floats2half2_rn(y1.x, y1.y));
-                v[4 * c] = r0.x; v[4 * c + 1] = r0.y; v[4 * c + 2] = r1.x; v[4 * c + 3] = r1.y;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = 0.f;
-        }
-    }
-    if (src >= 0 && signs != nullptr) {
-        const uint4 sg = *reinterpret_cast<const uint4*>(signs + 16 * t);
-        const uint32_t w[4] = {sg.x, sg.y, sg.z, sg.w};
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-            if ((w[j >> 2] >> (8 * (j & 3))) & 0x80u) v[j] = -v[j];
-    }
-    butterfly16(v);                                        // index bits 0..3
-#pragma unroll
-    for (int j = 0; j < 16; ++j) sm[17 * t + j] = v[j];
-    __syncwarp();
-    {                                                      // index bits 4..7: elements b + 16 j, b = 256 (t / 16) + t % 16
-        float* s = sm + (t >> 4) * 272 + (t & 15);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = s[17 * j];
-        butterfly16(v);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) s[17 * j] = v[j];
-    }
-    __syncthreads();
-    float m = 0.f;
-    {
-        // index bits 8 and up: R-point transforms over elements g + 256 j; a thread takes the 16 / R
-        // groups g = t + NT u.  With v[u R + j] the butterflies act on the low bits of the register index.
-#pragma unroll
-        for (int u = 0; u < 16 / R; ++u)
-#pragma unroll
-            for (int j = 0; j < R; ++j) v[u * R + j] = sm[t + NT * u + ((t + NT * u) >> 4) + 272 * j];
-        if (R == 16) {
-            butterfly16(v);
-        } else {
-#pragma unroll
-            for (int s = 1; s < R; s <<= 1)
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if ((j & s) == 0) { const float a = v[j], c = v[j | s]; v[j] = a + c; v[j | s] = a - c; }
-        }
-        // divide by sqrt(K) (exact), round once to fp16, track the absolute maximum
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-            const __half2 h = __floats2half2_rn(v[i] * INV_ROOT, v[i + 1] * INV_ROOT);
-            const __half2 a = __habs2(h);
-            m = fmaxf(m, fmaxf(__low2float(a), __high2float(a)));
-            const float2 f = __half22float2(h);
-            v[i] = f.x; v[i + 1] = f.y;
-        }
-#pragma unroll
-        for (int u = 0; u < 16 / R; ++u)
-#pragma unroll
-            for (int j = 0; j < R; ++j) sm[t + NT * u + ((t + NT * u) >> 4) + 272 * j] = v[u * R + j];
-    }
-    m = warp_max(m);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
-    __syncthreads();
-    {
-        constexpr int WPR = NT / 32;                           // warps per row
-        float t2 = 0.f;
-#pragma unroll
-        for (int w = 0; w < WPR; ++w) t2 = fmaxf(t2, red[r_in * WPR + w]);
-        m = t2;
-    }
-    if (!active) return;
-    const float sc = scale_from_absmax<__half>(m, qmax);
-    if (t == 0 && scale_out != nullptr) scale_out[row] = sc;
-    const float inv = __frcp_rn(sc);
-    const float2 inv2 = make_float2(inv, inv), ns2 = make_float2(-sc, -sc);
-    const __half2 hi2 = __float2half2_rn(qmax), lo2 = __float2half2_rn(-qmax), magic = __float2half2_rn(1536.0f);
-    uint32_t hb[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {                          // this thread's 16 consecutive elements again
-        const float2 f = make_float2(sm[17 * t + 2 * j], sm[17 * t + 2 * j + 1]);
-        const float2 y0 = __fmul2_rn(f, inv2);
-        const float2 e = __ffma2_rn(y0, ns2, f);
-        const float2 y = __ffma2_rn(e, inv2, y0);
-        __half2 h = __floats2half2_rn(y.x, y.y);
-        h = __hadd2(__hmin2(__hmax2(h, lo2), hi2), magic);
-        hb[j] = *reinterpret_cast<uint32_t*>(&h);
-    }
-    *reinterpret_cast<uint4*>(q_out + row * K + 16 * t) =
-        make_uint4(__byte_perm(hb[0], hb[1], 0x6420), __byte_perm(hb[2], hb[3], 0x6420),
-                   __byte_perm(hb[4], hb[5], 0x6420), __byte_perm(hb[6], hb[7], 0x6420));
-}
-
-// ---------------------------------------------------------------------------
 // The 4096-point transform with 64 points per thread: 4096 = 64 x 64, so the twelve butterfly stages
 // are two register passes (index bits 0..5, then 6..11, the reference's stage order) with ONE
 // regrouping of the row through shared memory between them, instead of three passes and two
@@ -1254,6 +1059,201 @@ hadamard_4096_r64_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, con
         }
         src = next_src;
         // the next iteration's first barrier orders these reads of the codes before X is written again
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The 1024-point transform the same way: 1024 = 64 x 16.  A row belongs to 16 threads (half a warp), so
+// nothing in the loop needs a CTA barrier; a CTA of 64 threads walks groups of four rows.
+//   pass A  thread t of the row owns elements 64 t + j (bits 0..5), as in the 4096-point kernel
+//   X       16 rows of 64 floats (68-float pitch), written with 16 x STS.128
+//   pass B  thread u takes columns 4 u .. 4 u + 3 of all 16 rows with 16 x LDS.128: four independent
+//           16-point butterflies (bits 6..9) on packed pairs, scaling by 1/32, rounding, row maximum
+//           (shuffles inside the half-warp), codes; the four codes of a row of X are one 32-bit store
+// LN: the LayerNorm of the source row in front (norm1 -> qkv, norm2 -> lin1 of a rotated ViT-L in one
+// launch), fp32 two-pass statistics, y = half(gamma * (rstd * (x - mean)) + beta) as in
+// quant_rows_fast_kernel, gamma / beta as fp32 quads in shared memory (quad q of thread t at q * 16 + t);
+// a gathered zero row stays zero (the padding of window_partition comes after the norm).
+// ---------------------------------------------------------------------------
+template <typename SrcT, bool LN>
+__global__ void __launch_bounds__(64, LN ? 6 : 8)
+hadamard_1024_r64_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, const int32_t* __restrict__ row_map,
+                         const int8_t* __restrict__ signs, const __half* __restrict__ gamma,
+                         const __half* __restrict__ beta, float ln_eps, float qmax,
+                         int8_t* __restrict__ q_out, float* __restrict__ scale_out)
+{
+    constexpr int K = 1024;
+    constexpr int SPITCH = 144;                                 // bytes per owner thread in the staging buffer: 128 + 16
+    constexpr int XPITCH = 68;                                  // floats per row of X
+    __shared__ __align__(16) uint8_t stage_all[4 * 16 * SPITCH];
+    __shared__ __align__(16) float xs_all[4 * 16 * XPITCH];     // X, then the byte codes
+    __shared__ float4 ln_gb[LN ? 2 : 1][LN ? 256 : 1];
+    const int r_in = threadIdx.x >> 4, u = threadIdx.x & 15;    // row inside the group, thread inside the row
+    uint8_t* stage = stage_all + r_in * 16 * SPITCH;
+    float* xs = xs_all + r_in * 16 * XPITCH;
+    if constexpr (LN) {
+        for (int o = threadIdx.x; o < 256; o += 64) {           // 16-byte loads of 8 halves: 128 of gamma, 128 of beta
+            const int which = o >> 7, c = o & 127;              // columns 8 c .. 8 c + 7: owner c / 8, quads 2 (c % 8), + 1
+            float f[8];
+            unpack<__half>(*reinterpret_cast<const uint4*>((which ? beta : gamma) + 8 * c), f);
+            ln_gb[which][((c & 7) * 2) * 16 + (c >> 3)] = make_float4(f[0], f[1], f[2], f[3]);
+            ln_gb[which][((c & 7) * 2 + 1) * 16 + (c >> 3)] = make_float4(f[4], f[5], f[6], f[7]);
+        }
+        __syncthreads();
+    }
+    auto source_row = [&](int64_t row) -> int64_t {
+        if (row >= M) return -1;
+        return row_map != nullptr ? (int64_t)row_map[row] : row;
+    };
+    auto fetch = [&](int64_t src) {                             // this thread's share of its row (nothing for a zero row)
+        if (src >= 0) {
+            const uint8_t* g = reinterpret_cast<const uint8_t*>(x + src * ldx);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int c = i * 16 + u;                       // 16-byte chunk of the row; owner c / 8, position c % 8
+                cp_async16(&stage[(c >> 3) * SPITCH + (c & 7) * 16], g + 16 * c);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int64_t groups = (M + 3) >> 2;
+    int64_t grp = blockIdx.x;
+    int64_t src = grp < groups ? source_row(4 * grp + r_in) : -1;
+    if (grp < groups) fetch(src);
+    for (; grp < groups; grp += gridDim.x) {
+        const int64_t row = 4 * grp + r_in;
+        const int64_t next = grp + gridDim.x;
+        const int64_t next_src = next < groups ? source_row(4 * next + r_in) : -1;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();                                           // the row is in the staging buffer; its X is free
+        float v[64];
+        if (src >= 0) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                float f[8];
+                unpack<SrcT>(*reinterpret_cast<const uint4*>(&stage[u * SPITCH + k * 16]), f);
+                if (!std::is_same<SrcT, __half>::value) RoundVec<__half, 8>::run(f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[k * 8 + e] = f[e];
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = 0.f;
+        }
+        if constexpr (LN) {
+            float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 64; j += 2) acc = __fadd2_rn(acc, make_float2(v[j], v[j + 1]));
+            float sum = acc.x + acc.y;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const float mean = sum / (float)K;
+            const float2 nmean = make_float2(-mean, -mean);
+            acc = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 64; j += 2) {
+                const float2 d = __fadd2_rn(make_float2(v[j], v[j + 1]), nmean);
+                v[j] = d.x; v[j + 1] = d.y;
+                acc = __ffma2_rn(d, d, acc);
+            }
+            float var = acc.x + acc.y;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+            const float rstd = rsqrtf(var / (float)K + ln_eps);
+            const float2 rstd2 = make_float2(rstd, rstd);
+            if (src >= 0) {
+#pragma unroll
+                for (int q = 0; q < 16; ++q) {
+                    const float4 g = ln_gb[0][q * 16 + u], bb = ln_gb[LN ? 1 : 0][q * 16 + u];
+                    const float2 y0 = __ffma2_rn(make_float2(g.x, g.y), __fmul2_rn(rstd2, make_float2(v[4 * q], v[4 * q + 1])), make_float2(bb.x, bb.y));
+                    const float2 y1 = __ffma2_rn(make_float2(g.z, g.w), __fmul2_rn(rstd2, make_float2(v[4 * q + 2], v[4 * q + 3])), make_float2(bb.z, bb.w));
+                    const float2 r0 = __half22float2(__floats2half2_rn(y0.x, y0.y));
+                    const float2 r1 = __half22float2(__floats2half2_rn(y1.x, y1.y));
+                    v[4 * q] = r0.x; v[4 * q + 1] = r0.y; v[4 * q + 2] = r1.x; v[4 * q + 3] = r1.y;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 64; ++j) v[j] = 0.f;
+            }
+        }
+        if (src >= 0 && signs != nullptr) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint4 sg = *reinterpret_cast<const uint4*>(signs + 64 * u + 16 * k);
+                const uint32_t w[4] = {sg.x, sg.y, sg.z, sg.w};
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if ((w[j >> 2] >> (8 * (j & 3))) & 0x80u) v[k * 16 + j] = -v[k * 16 + j];
+            }
+        }
+        butterfly64(v);                                         // pass A: index bits 0..5
+#pragma unroll
+        for (int q = 0; q < 16; ++q)
+            *reinterpret_cast<float4*>(xs + u * XPITCH + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        __syncwarp();                                           // X is complete, and nobody reads the staging buffer any more:
+        if (next < groups) fetch(next_src);                     // the next row travels while this one is transformed
+        float2 a[16], b[16];                                    // a[j] / b[j]: columns 4 u, 4 u + 1 / 4 u + 2, 4 u + 3 of row j of X
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float4 f = *reinterpret_cast<const float4*>(xs + j * XPITCH + 4 * u);
+            a[j] = make_float2(f.x, f.y); b[j] = make_float2(f.z, f.w);
+        }
+        const float2 neg1 = make_float2(-1.f, -1.f);
+#pragma unroll
+        for (int s2 = 1; s2 < 16; s2 <<= 1) {                   // pass B: index bits 6..9
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if ((j & s2) == 0) {
+                    const float2 a0 = a[j], a1 = a[j | s2], b0 = b[j], b1 = b[j | s2];
+                    a[j] = __fadd2_rn(a0, a1); a[j | s2] = __ffma2_rn(a1, neg1, a0);
+                    b[j] = __fadd2_rn(b0, b1); b[j | s2] = __ffma2_rn(b1, neg1, b0);
+                }
+            }
+        }
+        __half2 m2 = __float2half2_rn(0.f);
+        const float2 root2 = make_float2(0.03125f, 0.03125f);   // 1 / sqrt(1024), an exact scaling
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float2 sa = __fmul2_rn(a[j], root2), sb = __fmul2_rn(b[j], root2);
+            const __half2 ha = __floats2half2_rn(sa.x, sa.y), hb = __floats2half2_rn(sb.x, sb.y);
+            m2 = __hmax2(m2, __hmax2(__habs2(ha), __habs2(hb)));
+            a[j] = __half22float2(ha); b[j] = __half22float2(hb);
+        }
+        float m = fmaxf(__low2float(m2), __high2float(m2));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float sc = scale_from_absmax<__half>(m, qmax);
+        if (u == 0 && row < M && scale_out != nullptr) scale_out[row] = sc;
+        const float inv = __frcp_rn(sc);
+        const float2 inv2 = make_float2(inv, inv), ns2 = make_float2(-sc, -sc);
+        const __half2 hi2 = __float2half2_rn(qmax), lo2 = __float2half2_rn(-qmax), magic = __float2half2_rn(1536.0f);
+        uint8_t* codes = reinterpret_cast<uint8_t*>(xs);
+        __syncwarp();                                           // every thread of the row is past its reads of X
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            uint32_t hw[2];
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+                const float2 f = h2 ? b[j] : a[j];
+                const float2 y0 = __fmul2_rn(f, inv2);
+                const float2 e = __ffma2_rn(y0, ns2, f);
+                const float2 y = __ffma2_rn(e, inv2, y0);
+                __half2 h = __floats2half2_rn(y.x, y.y);
+                h = __hadd2(__hmin2(__hmax2(h, lo2), hi2), magic);
+                hw[h2] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint32_t*>(codes + 64 * j + 4 * u) = __byte_perm(hw[0], hw[1], 0x6420);
+        }
+        __syncwarp();
+        if (row < M) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int c = i * 16 + u;                       // 16 consecutive codes of the row
+                *reinterpret_cast<uint4*>(q_out + row * K + 16 * c) = *reinterpret_cast<const uint4*>(codes + 16 * c);
+            }
+        }
+        src = next_src;
+        // the __syncwarp at the top of the next iteration orders these reads before X is written again
     }
 }
 
@@ -1499,9 +1499,11 @@ static int quant_typed(const SrcT* x, int64_t M, int K, int64_t ldx, const Prolo
                     hadamard_4096_r64_kernel<SrcT><<<(unsigned)(M < resident ? M : resident), 64, 0, st>>>(
                         x, M, ldx, pro.row_map, had->signs, qmax, q, scale);
                 } else {
-                    const unsigned grid = (unsigned)((M + 3) / 4);
-                    if (ln_had) hadamard_pow4_quant_kernel<SrcT, 1024, true><<<grid, 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, g, b, pro.ln_eps, qmax, q, scale);
-                    else hadamard_pow4_quant_kernel<SrcT, 1024, false><<<grid, 256, 0, st>>>(x, M, ldx, pro.row_map, had->signs, g, b, 0.f, qmax, q, scale);
+                    const int64_t groups = (M + 3) / 4;
+                    const int64_t resident = (int64_t)device_sm_count() * (ln_had ? 6 : 8);
+                    const unsigned grid = (unsigned)(groups < resident ? groups : resident);
+                    if (ln_had) hadamard_1024_r64_kernel<SrcT, true><<<grid, 64, 0, st>>>(x, M, ldx, pro.row_map, had->signs, g, b, pro.ln_eps, qmax, q, scale);
+                    else hadamard_1024_r64_kernel<SrcT, false><<<grid, 64, 0, st>>>(x, M, ldx, pro.row_map, had->signs, g, b, 0.f, qmax, q, scale);
                 }
                 SAMQ_CUDA_TRY(cudaGetLastError());
                 return SAMQ_OK;
