@@ -385,6 +385,30 @@ def test_hadamard_4096_kernel_matches_general_kernel(cuda_device, with_signs, n)
     assert torch.equal(a["q"], b["q"]) and torch.equal(a["scale"], b["scale"])
 
 
+@pytest.mark.parametrize("n", [4096, 1024])
+def test_hadamard_kernels_walk_many_rows(cuda_device, n):
+    """More rows than one resident wave of CTAs holds: every CTA of the specialised kernels walks
+    several rows (the next row's copies in flight while the current one is transformed), through a
+    gather with padding rows; codes and scales equal the general kernel's bit for bit."""
+    from sam_quantization_b200 import ops
+    g = torch.Generator().manual_seed(n)
+    M = 9001 if n == 4096 else 19003
+    x = (torch.randn(M, n, generator=g) * 2).half()
+    x[:, torch.randperm(n, generator=g)[: n // 100]] *= 20
+    x[5] = 0
+    x = x.to(cuda_device)
+    signs = (torch.randint(0, 2, (n,), generator=g) * 2 - 1).to(torch.int8).to(cuda_device)
+    had = ops.Hadamard("full", signs=signs)
+    rm = torch.randperm(M, generator=g).to(torch.int32)
+    rm[::17] = -1
+    rm = rm.to(cuda_device)
+    for kw in ({}, {"row_map": rm}):
+        fast = ops.quantize(x, 0, hadamard=had, **kw)
+        general = ops.quantize(x, 0, hadamard=had, transformed=True, **kw)
+        assert torch.equal(fast["q"], general["q"]) and torch.equal(fast["scale"], general["scale"])
+    assert int(fast["q"][0].abs().max()) == 0              # a padding row of the gather
+
+
 @pytest.mark.parametrize("had_dim", [64, 80, 8, 128])
 def test_hadamard_across_16_heads_kernel_matches_general_kernel(cuda_device, had_dim):
     """The register-only kernel for the transform across 16 heads (codes only) against the general
@@ -422,12 +446,12 @@ def test_layer_norm_and_hadamard_in_one_kernel(cuda_device, K=1024):
     then agree except where such a value sat on a rounding boundary."""
     from sam_quantization_b200 import ops
     g = torch.Generator().manual_seed(K)
-    M = 777
+    M = 8000                                                   # more row groups than resident CTAs: the kernel's loop runs
     x = (torch.randn(M, K, generator=g) * 2 + 0.3).half().to(cuda_device)
     w = (1 + 0.1 * torch.randn(K, generator=g)).half().to(cuda_device)
     b = (0.1 * torch.randn(K, generator=g)).half().to(cuda_device)
     signs = (torch.randint(0, 2, (K,), generator=g) * 2 - 1).to(torch.int8).to(cuda_device)
-    row_map = torch.randperm(M, generator=g)[:700].to(torch.int32)
+    row_map = torch.randperm(M, generator=g)[:7000].to(torch.int32)
     row_map[::13] = -1                                         # padding rows of a window gather
     row_map = row_map.to(cuda_device)
     spec = ops.Hadamard("full", signs=signs)
@@ -435,7 +459,7 @@ def test_layer_norm_and_hadamard_in_one_kernel(cuda_device, K=1024):
     one = ops.quantize(x, ops.GRAN_ROW, hadamard=spec, layer_norm=(w, b, 1e-6), row_map=row_map)
     tx = ops.quantize(x, ops.GRAN_ROW, codes=False, transformed=True, layer_norm=(w, b, 1e-6), row_map=row_map)["tx"]
     two = ops.quantize(tx, ops.GRAN_ROW, hadamard=spec)
-    assert one["q"].shape == (700, K)
+    assert one["q"].shape == (7000, K)
     pad = (row_map < 0)
     assert int(one["q"][pad].abs().max()) == 0                 # zero rows stay zero: the padding comes after the norm
     diff = (one["q"].int() - two["q"].int()).abs()
