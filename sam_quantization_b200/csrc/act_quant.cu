@@ -1020,15 +1020,17 @@ hadamard_4096_r64_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, con
 #pragma unroll
         for (int j = 0; j < 64; ++j) v[j] = xs[j * XPITCH + t];
         butterfly64(v);                                         // pass B: bits 6..11; v[j] is element 64 j + t
-        float m = 0.f;
+        __half2 m2 = __float2half2_rn(0.f);
+        const float2 root2 = make_float2(0.015625f, 0.015625f); // 1 / sqrt(4096), an exact scaling
 #pragma unroll
-        for (int i = 0; i < 64; i += 2) {                       // divide by sqrt(4096) (exact), round once to fp16, absolute maximum
-            const __half2 h = __floats2half2_rn(v[i] * 0.015625f, v[i + 1] * 0.015625f);
-            const __half2 a = __habs2(h);
-            m = fmaxf(m, fmaxf(__low2float(a), __high2float(a)));
+        for (int i = 0; i < 64; i += 2) {                       // scale, round once to fp16, absolute maximum
+            const float2 sv = __fmul2_rn(make_float2(v[i], v[i + 1]), root2);
+            const __half2 h = __floats2half2_rn(sv.x, sv.y);
+            m2 = __hmax2(m2, __habs2(h));
             const float2 f = __half22float2(h);
             v[i] = f.x; v[i + 1] = f.y;
         }
+        float m = fmaxf(__low2float(m2), __high2float(m2));
         m = warp_max(m);
         if ((t & 31) == 0) red[it & 1][t >> 5] = m;
         __syncthreads();                                        // also: every thread is past its reads of X
@@ -1039,6 +1041,9 @@ hadamard_4096_r64_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, con
         const float2 inv2 = make_float2(inv, inv), ns2 = make_float2(-sc, -sc);
         const __half2 hi2 = __float2half2_rn(qmax), lo2 = __float2half2_rn(-qmax), magic = __float2half2_rn(1536.0f);
         uint8_t* codes = reinterpret_cast<uint8_t*>(xs);
+        // A normal fp16 scale is within 2^-11 of absmax / qmax, so no quotient rounds beyond qmax and the
+        // clamp can go; a subnormal scale (absmax below ~8e-3) keeps it (as in quant_rows_fast_kernel).
+        const bool clamp = !(sc >= 6.103515625e-05f);
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
             const float2 f = make_float2(v[2 * j], v[2 * j + 1]);
@@ -1046,10 +1051,11 @@ hadamard_4096_r64_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, con
             const float2 e = __ffma2_rn(y0, ns2, f);
             const float2 y = __ffma2_rn(e, inv2, y0);
             __half2 h = __floats2half2_rn(y.x, y.y);
-            h = __hadd2(__hmin2(__hmax2(h, lo2), hi2), magic);
+            if (clamp) h = __hmin2(__hmax2(h, lo2), hi2);       // CTA-uniform
+            h = __hadd2(h, magic);
             const uint32_t hb = *reinterpret_cast<uint32_t*>(&h);
-            codes[64 * (2 * j) + t] = (uint8_t)(hb & 0xFFu);
-            codes[64 * (2 * j + 1) + t] = (uint8_t)((hb >> 16) & 0xFFu);
+            codes[64 * (2 * j) + t] = (uint8_t)hb;
+            codes[64 * (2 * j + 1) + t] = (uint8_t)(hb >> 16);
         }
         __syncthreads();
 #pragma unroll
@@ -1228,6 +1234,7 @@ hadamard_1024_r64_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, con
         const float2 inv2 = make_float2(inv, inv), ns2 = make_float2(-sc, -sc);
         const __half2 hi2 = __float2half2_rn(qmax), lo2 = __float2half2_rn(-qmax), magic = __float2half2_rn(1536.0f);
         uint8_t* codes = reinterpret_cast<uint8_t*>(xs);
+        const bool clamp = !(sc >= 6.103515625e-05f);           // only a subnormal fp16 scale lets a quotient round beyond qmax
         __syncwarp();                                           // every thread of the row is past its reads of X
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -1239,7 +1246,8 @@ hadamard_1024_r64_kernel(const SrcT* __restrict__ x, int64_t M, int64_t ldx, con
                 const float2 e = __ffma2_rn(y0, ns2, f);
                 const float2 y = __ffma2_rn(e, inv2, y0);
                 __half2 h = __floats2half2_rn(y.x, y.y);
-                h = __hadd2(__hmin2(__hmax2(h, lo2), hi2), magic);
+                if (clamp) h = __hmin2(__hmax2(h, lo2), hi2);   // uniform over the row's half-warp
+                h = __hadd2(h, magic);
                 hw[h2] = *reinterpret_cast<uint32_t*>(&h);
             }
             *reinterpret_cast<uint32_t*>(codes + 64 * j + 4 * u) = __byte_perm(hw[0], hw[1], 0x6420);
