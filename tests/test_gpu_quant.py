@@ -407,6 +407,14 @@ def test_hadamard_kernels_walk_many_rows(cuda_device, n):
         general = ops.quantize(x, 0, hadamard=had, transformed=True, **kw)
         assert torch.equal(fast["q"], general["q"]) and torch.equal(fast["scale"], general["scale"])
     assert int(fast["q"][0].abs().max()) == 0              # a padding row of the gather
+    # rows with a pitch: a column slice of a wider tensor
+    wide = torch.zeros((1500, n + 64), dtype=torch.float16, device=cuda_device)
+    wide[:, 32:32 + n] = x[:1500]
+    view = wide[:, 32:32 + n]
+    assert not view.is_contiguous()
+    a = ops.quantize(view, 0, hadamard=had)
+    b = ops.quantize(x[:1500].contiguous(), 0, hadamard=had)
+    assert torch.equal(a["q"], b["q"]) and torch.equal(a["scale"], b["scale"])
 
 
 @pytest.mark.parametrize("had_dim", [64, 80, 8, 128])
