@@ -100,8 +100,9 @@ class EncoderRunner:
     def encode(self, images: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """Encode ``images`` [n * batch, 3, S, S] into ``out`` [n * batch, C, h, w], ``batch`` images per
         forward.  With host tensors (pinned memory) the copy of chunk i + 1 to the device runs on a
-        second stream while chunk i is being encoded, and the embeddings of chunk i leave for the host
-        while chunk i + 1 is encoded; device tensors are encoded in place.  Returns ``out``; the work is
+        second stream while chunk i is being encoded, and the embeddings of chunk i leave for the host on a
+        third while chunk i + 1 is encoded; the first copy of a call may already run under the last
+        forward of the call before it.  Device tensors are encoded in place.  Returns ``out``; the work is
         ordered on the current stream (synchronise it before reading a host ``out``)."""
         n, b = images.shape[0], self.batch
         if n % b or out.shape[0] != n:
@@ -112,27 +113,38 @@ class EncoderRunner:
                 out[i:i + b].copy_(self(images[i:i + b]), non_blocking=True)
             return out
         if self._copy_stream is None:
-            self._copy_stream = torch.cuda.Stream(device=self.device)
+            self._copy_stream = torch.cuda.Stream(device=self.device)      # host -> device
+            self._back_stream = torch.cuda.Stream(device=self.device)      # device -> host (its own stream: a copy back that
+            #                                                                waits for a forward must not hold up the next copy in)
             self._stage = [torch.empty_like(self.static_in) for _ in range(2)]
             self._stage_free = [torch.cuda.Event() for _ in range(2)]
+            self._stage_used = [False, False]
             self._out_stage = [torch.empty_like(self.static_out) for _ in range(2)]
             self._out_free = [torch.cuda.Event() for _ in range(2)]
-        side = self._copy_stream
-        side.wait_stream(cur)                                   # earlier users of the staging buffers
-        ready = []
-        with torch.cuda.stream(side):                           # first chunk
-            self._stage[0].copy_(images[0:b], non_blocking=True)
-            ev = torch.cuda.Event(); ev.record(side); ready.append(ev)
+            self._out_used = [False, False]
+        side, back = self._copy_stream, self._back_stream
+        # The staging buffers are guarded by events of their own, not by the whole current stream: the
+        # first copy of this call may therefore run while the last forward of the previous call is
+        # still in flight (calls in a row pipeline across their boundaries).
+
+        def stage_in(slot, lo):                                 # host -> staging buffer `slot`, on the copy stream
+            with torch.cuda.stream(side):
+                if self._stage_used[slot]:
+                    side.wait_event(self._stage_free[slot])     # the forward that last read this slot has taken its copy
+                self._stage[slot].copy_(images[lo:lo + b], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(side)
+            return ev
+
+        ready = [stage_in(0, 0)]
         for k, i in enumerate(range(0, n, b)):
             slot = k & 1
             if i + b < n:                                       # prefetch the next chunk while this one runs
-                with torch.cuda.stream(side):
-                    side.wait_event(self._stage_free[slot ^ 1]) if k >= 1 else None
-                    self._stage[slot ^ 1].copy_(images[i + b:i + 2 * b], non_blocking=True)
-                    ev = torch.cuda.Event(); ev.record(side); ready.append(ev)
+                ready.append(stage_in(slot ^ 1, i + b))
             cur.wait_event(ready[k])
             self.static_in.copy_(self._stage[slot], non_blocking=True)
             self._stage_free[slot].record(cur)
+            self._stage_used[slot] = True
             if self.graph is not None:
                 self.graph.replay()
             else:
@@ -140,15 +152,16 @@ class EncoderRunner:
             if out.is_cuda:
                 out[i:i + b].copy_(self.static_out, non_blocking=True)
             else:
-                if k >= 2:
+                if self._out_used[slot]:
                     cur.wait_event(self._out_free[slot])        # the copy that last read this slot has finished
                 self._out_stage[slot].copy_(self.static_out, non_blocking=True)
                 done = torch.cuda.Event(); done.record(cur)
-                with torch.cuda.stream(side):
-                    side.wait_event(done)
+                with torch.cuda.stream(back):
+                    back.wait_event(done)
                     out[i:i + b].copy_(self._out_stage[slot], non_blocking=True)
-                    self._out_free[slot].record(side)
-        cur.wait_stream(side)
+                    self._out_free[slot].record(back)
+                self._out_used[slot] = True
+        cur.wait_stream(back)
         if self.check_status:
             self.check()
         return out
