@@ -324,9 +324,12 @@ int samq_attn_rel_bias(const void* rel_all, int dtype, int64_t images, int rel_p
  *                         qkv [units * H * W, 3C].  keys = H * W for images; for windows the key
  *                         (kh, kw) sits at kh * 16 + kw and the row is zero-padded to a multiple
  *                         of 64.  vt is [units * heads * head_dim, keys].
- * samq_attn_global      : out [units * H * W, C] (same 16-bit dtype) from qkv, vt and
+ * samq_attn_global      : out [units * H * W, C] (same 16-bit dtype) from qkv and
  *                         rel_all [heads, units * H * W, rel_pitch] (see samq_attn_window_prep).
- *                         head_dim 64 or 80.
+ *                         head_dim 64 or 80.  V is read where the qkv GEMM left it (as the
+ *                         MN-major operand of the P V product); `vt` is ignored and may be NULL
+ *                         (the argument remains for callers built against the earlier interface,
+ *                         which needed samq_attn_transpose_v first).
  * status : optional device int32, set non-zero if a bounded wait inside the kernel ran out. */
 int samq_attn_transpose_v(const void* qkv, int dtype, int64_t units, int H, int W, int num_heads, int head_dim,
                           void* vt, void* stream);

@@ -60,6 +60,26 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// K-major operand in 32-byte-swizzled strips: a row is 32 bytes (16 elements = one MMA K step),
+// groups of 8 rows are 256 bytes apart.
+__device__ __forceinline__ uint64_t desc_sw32_k(uint32_t addr) {
+    uint64_t d = (uint64_t)((addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(256 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)6 << 61;                  // 32-byte swizzle
+    return d;
+}
+// MN-major operand in the same strips: 16 consecutive MN elements are one 32-byte row of a strip,
+// the next 16 live one strip (`strip_bytes`) further; 8 K rows are 256 bytes.
+__device__ __forceinline__ uint64_t desc_sw32_mn(uint32_t addr, uint32_t strip_bytes) {
+    uint64_t d = (uint64_t)((addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((strip_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)(256 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)6 << 61;
+    return d;
+}
 // kind::f16 instruction descriptor: fp32 accumulator, A and B of format `fmt` (0 fp16, 1 bf16),
 // both K-major, N >> 3 at bit 17, M >> 4 at bit 24
 __host__ __device__ constexpr uint32_t f16_idesc(uint32_t fmt, int M, int N) {

@@ -19,11 +19,12 @@
 //              sum shows that some p passed 2^8 (p stays below 2^14 otherwise) is m raised, the pass
 //              repeated from the scores still in tensor memory, and the output accumulator rescaled
 //              in place.
-//   warp 4     TMA producer: Q once, then per block the K rows and the matching V^T columns
-//              (two stages).
+//   warp 4     TMA producer: Q once, then per block the K rows and the V rows of the same keys, both
+//              straight from qkv (two stages).
 //   warp 5     MMA issuer: S = Q K^T (M128 N64 K=D) into one of two score buffers, and
 //              O += P V (M128 N=D K64), both tcgen05.mma kind::f16 with fp32 accumulation.
-// V is consumed K-major (V^T [D, L] per head), written by attn_transpose_v below.
+// V is consumed MN-major, as D / 16 strips of [64 keys x 16 values] in the 32-byte swizzle: no transposed
+// copy of V exists (attn_transpose_v below is kept for callers that want V^T for another purpose).
 // Every wait is bounded; a wait that runs out sets the abort flag, the roles drain, and the
 // status word is set.
 #include "attn_common.cuh"
@@ -62,8 +63,9 @@ template <int D> struct AtSmem {
     static constexpr int NATOM = (D + 63) / 64;            // 128-byte swizzle rows per operand row
     static constexpr int Q_BYTES = NATOM * BQ * 128;
     static constexpr int K_BYTES = NATOM * BKEY * 128;
-    static constexpr int DV = D;                           // V^T rows
-    static constexpr int VT_BYTES = DV * 128;              // DV rows of 64 keys
+    static constexpr int DV = D;
+    static constexpr int V_STRIP = BKEY * 32;              // one strip of V: 64 keys x 16 values (32 bytes), 32-byte swizzle
+    static constexpr int VT_BYTES = (D / 16) * V_STRIP;    // D / 16 strips
     static constexpr int STAGE_BYTES = K_BYTES + VT_BYTES;
     static constexpr int P_BYTES = BQ * 128;
     static constexpr int TOTAL = 1024 + Q_BYTES + 2 * STAGE_BYTES + P_BYTES + (int)sizeof(AttnControl) + 64;
@@ -135,7 +137,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
             for (int a = 0; a < SM::NATOM; ++a)
                 tma_load_2d(smem_u32(q_tile + a * BQ * 128), &map_q, qbar, head * D + a * 64, (int)token0);
-            // K rows are released as soon as their score product has run, V^T columns only after the
+            // K rows are released as soon as their score product has run, V rows only after the
             // P V product two blocks later: K is fetched first and runs further ahead
             bool ok = true;
             auto load_k = [&](int i) -> bool {
@@ -155,8 +157,13 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const int st = i & 1;
                 if (!mbar_wait(smem_u32(&ctl->v_empty[st]), ((i >> 1) & 1) ^ 1u, abort_flag)) return false;
                 const uint32_t bar = smem_u32(&ctl->v_full[st]);
+                const uint32_t vdst = smem_u32(stages + st * SM::STAGE_BYTES + SM::K_BYTES);
                 mbar_expect_tx(bar, SM::VT_BYTES);
-                tma_load_2d(smem_u32(stages + st * SM::STAGE_BYTES + SM::K_BYTES), &map_vt, bar, i * BKEY, bh * SM::DV);
+#pragma unroll
+                for (int a = 0; a < D / 16; ++a) {              // V straight from qkv, 16 values of the head width per strip
+                    if (WINDOW) tma_load_4d(vdst + a * SM::V_STRIP, &map_vt, bar, 2 * C + head * D + a * 16, 0, 4 * i, image);
+                    else tma_load_2d(vdst + a * SM::V_STRIP, &map_vt, bar, 2 * C + head * D + a * 16, image * p.L + i * BKEY);
+                }
                 return true;
             };
             for (int i = 0; i < nblocks && ok; ++i) {
@@ -173,7 +180,7 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc_s = f16_idesc(AtOps<T>::kFormat, BQ, BKEY);
-            constexpr uint32_t idesc_o = f16_idesc(AtOps<T>::kFormat, BQ, SM::DV);
+            constexpr uint32_t idesc_o = f16_idesc(AtOps<T>::kFormat, BQ, SM::DV) | (1u << 16);   // B (= V) is MN-major
             bool ok = mbar_wait(smem_u32(&ctl->q_full), 0, abort_flag);
             auto issue_s = [&](int j) -> bool {
                 const int st = j & 1;
@@ -204,10 +211,10 @@ attn_global_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
                 for (int ks = 0; ks < BKEY / 16; ++ks) {
                     const uint64_t adesc = make_smem_desc(smem_u32(p_tile)) + (uint64_t)(ks * 2);
-                    const uint64_t bdesc = make_smem_desc(vb) + (uint64_t)(ks * 2);
+                    const uint64_t bdesc = desc_sw32_mn(vb + (uint32_t)(ks * 512), (uint32_t)SM::V_STRIP);   // 16 keys = 512 bytes of a strip
                     mma_f16(tmem_base + (uint32_t)O_COL, adesc, bdesc, idesc_o, (i | ks) != 0 ? 1u : 0u);
                 }
-                tcgen05_commit(smem_u32(&ctl->v_empty[i & 1]));       // the V^T columns may be refilled
+                tcgen05_commit(smem_u32(&ctl->v_empty[i & 1]));       // the V rows may be refilled
                 tcgen05_commit(smem_u32(&ctl->pv_done));              // P may be overwritten, O is current
             }
         }
@@ -426,39 +433,43 @@ transpose_v_kernel(const uint16_t* __restrict__ qkv, int H, int W, int key_pitch
 
 CUtensorMapDataType map_type(bool bf16) { return bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16; }
 
-// bf16 / fp16 [rows, cols] row-major, box = box_rows x 64 elements (128 bytes), 128-byte swizzle
-int make_map_16bit(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t pitch_elems, int box_rows, bool bf16) {
+// bf16 / fp16 [rows, cols] row-major; box = box_rows x 64 elements with the 128-byte swizzle, or
+// box_rows x 16 elements with the 32-byte swizzle (strips)
+int make_map_16bit(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t pitch_elems, int box_rows, bool bf16,
+                   bool strips = false) {
     gemm::EncodeTiledFn fn = gemm::encode_tiled_fn();
     if (fn == nullptr) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)(pitch_elems * 2)};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {strips ? 16u : 64u, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, map_type(bf16), 2, const_cast<void*>(base),
-                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    strips ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return SAMQ_OK;
 }
 
-// qkv [units * H * W, cols] seen as [units, H, W, cols]; box = 64 columns x 16 key columns x 4 key
-// rows of one unit: key columns W..15 and key rows >= H lie outside the view and read as zeros
-int make_map_window_keys(CUtensorMap* map, const void* base, int64_t units, int H, int W, int64_t cols, bool bf16) {
+// qkv [units * H * W, cols] seen as [units, H, W, cols]; box = 64 (or, as strips, 16) columns x 16 key
+// columns x 4 key rows of one unit: key columns W..15 and key rows >= H lie outside the view and read as zeros
+int make_map_window_keys(CUtensorMap* map, const void* base, int64_t units, int H, int W, int64_t cols, bool bf16, bool strips = false) {
     gemm::EncodeTiledFn fn = gemm::encode_tiled_fn();
     if (fn == nullptr) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)units};
     cuuint64_t strides[3] = {(cuuint64_t)(cols * 2), (cuuint64_t)(cols * 2 * W), (cuuint64_t)(cols * 2 * W * H)};
-    cuuint32_t box[4] = {64u, 16u, 4u, 1u};
+    cuuint32_t box[4] = {strips ? 16u : 64u, 16u, 4u, 1u};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(map, map_type(bf16), 4, const_cast<void*>(base),
-                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    strips ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SAMQ_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed with CUresult %d", (int)r);
     return SAMQ_OK;
 }
 
 template <typename T, int D, bool WINDOW>
-int launch_attn(const void* qkv, const void* vt, const AttnParams& p, int64_t units, int vt_len, cudaStream_t st) {
+int launch_attn(const void* qkv, const AttnParams& p, int64_t units, cudaStream_t st) {
     const bool bf16 = std::is_same<T, __nv_bfloat16>::value;
     const int C = p.heads * D;
     CUtensorMap mq, mk, mv;
@@ -467,7 +478,9 @@ int launch_attn(const void* qkv, const void* vt, const AttnParams& p, int64_t un
     rc = WINDOW ? make_map_window_keys(&mk, qkv, units, p.H, p.W, 3 * C, bf16)
                 : make_map_16bit(&mk, qkv, p.tokens, 3 * C, 3 * C, BKEY, bf16);
     if (rc != SAMQ_OK) return rc;
-    rc = make_map_16bit(&mv, vt, units * p.heads * D, vt_len, vt_len, D, bf16);
+    // V is read where the qkv GEMM left it, as strips of 16 values: the MN-major B operand of O += P V
+    rc = WINDOW ? make_map_window_keys(&mv, qkv, units, p.H, p.W, 3 * C, bf16, true)
+                : make_map_16bit(&mv, qkv, p.tokens, 3 * C, 3 * C, BKEY, bf16, true);
     if (rc != SAMQ_OK) return rc;
     auto kernel = attn_global_kernel<T, D, WINDOW>;
     SAMQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AtSmem<D>::TOTAL));
@@ -502,14 +515,15 @@ int attn_transpose_v_dispatch(const void* qkv, int dtype, int64_t units, int H, 
 int attn_global_dispatch(const void* qkv, const void* vt, const void* rel_all, int dtype, int64_t units, int rel_pitch,
                          int H, int W, int heads, int head_dim, float scale, void* out, int32_t* status, void* stream)
 {
-    if (qkv == nullptr || vt == nullptr || rel_all == nullptr || out == nullptr) return fail(SAMQ_ERR_BAD_ARG, "null pointer");
+    (void)vt;                                   // V is read from qkv; the argument stays for callers built against the earlier interface
+    if (qkv == nullptr || rel_all == nullptr || out == nullptr) return fail(SAMQ_ERR_BAD_ARG, "null pointer");
     const bool window = W != BKEY;
     if (window ? !(W <= 16 && H <= 16 && W >= 1 && H >= 1) : ((H * W) % BQ != 0 || H <= 0))
         return fail(SAMQ_ERR_UNSUPPORTED, "the attention kernel takes images of H x %d tokens or windows of at most 16 x 16 (H=%d W=%d)", BKEY, H, W);
     if (units < 0 || heads <= 0 || rel_pitch < 2 * H - 1 + 2 * W - 1)
         return fail(SAMQ_ERR_BAD_ARG, "bad shape units=%lld H=%d W=%d heads=%d rel_pitch=%d", (long long)units, H, W, heads, rel_pitch);
-    if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(vt) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
-        return fail(SAMQ_ERR_ALIGNMENT, "qkv, vt and out must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+        return fail(SAMQ_ERR_ALIGNMENT, "qkv and out must be 16-byte aligned");
     if (dtype != SAMQ_F16 && dtype != SAMQ_BF16) return fail(SAMQ_ERR_UNSUPPORTED, "attention takes fp16 or bf16");
     if (units == 0) return SAMQ_OK;
     AttnParams p;
@@ -521,10 +535,10 @@ int attn_global_dispatch(const void* qkv, const void* vt, const void* rel_all, i
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool bf = dtype == SAMQ_BF16;
 #define SAMQ_ATTN(DV)                                                                                                   \
-    (window ? (bf ? launch_attn<__nv_bfloat16, DV, true>(qkv, vt, p, units, vt_len, st)                                  \
-                  : launch_attn<__half, DV, true>(qkv, vt, p, units, vt_len, st))                                        \
-            : (bf ? launch_attn<__nv_bfloat16, DV, false>(qkv, vt, p, units, vt_len, st)                                 \
-                  : launch_attn<__half, DV, false>(qkv, vt, p, units, vt_len, st)))
+    (window ? (bf ? launch_attn<__nv_bfloat16, DV, true>(qkv, p, units, st)                                  \
+                  : launch_attn<__half, DV, true>(qkv, p, units, st))                                        \
+            : (bf ? launch_attn<__nv_bfloat16, DV, false>(qkv, p, units, st)                                 \
+                  : launch_attn<__half, DV, false>(qkv, p, units, st)))
     switch (head_dim) {
     case 64: return SAMQ_ATTN(64);
     case 80: return SAMQ_ATTN(80);

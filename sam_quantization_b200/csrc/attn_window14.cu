@@ -85,26 +85,6 @@ struct W14Params {
     int32_t* status;
 };
 
-// K-major operand in 32-byte-swizzled strips: a row is 32 bytes (16 elements = one MMA K step),
-// groups of 8 rows are 256 bytes apart.
-__device__ __forceinline__ uint64_t desc_sw32_k(uint32_t addr) {
-    uint64_t d = (uint64_t)((addr >> 4) & 0x3FFFu);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(256 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)6 << 61;                  // 32-byte swizzle
-    return d;
-}
-// MN-major operand in the same strips: 16 consecutive MN elements are one 32-byte row of a strip,
-// the next 16 live one strip (`strip_bytes`) further; 8 K rows are 256 bytes.
-__device__ __forceinline__ uint64_t desc_sw32_mn(uint32_t addr, uint32_t strip_bytes) {
-    uint64_t d = (uint64_t)((addr >> 4) & 0x3FFFu);
-    d |= (uint64_t)((strip_bytes >> 4) & 0x3FFFu) << 16;
-    d |= (uint64_t)(256 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)6 << 61;
-    return d;
-}
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])

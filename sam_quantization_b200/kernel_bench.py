@@ -216,7 +216,7 @@ def bench_global_attention(images, H, heads, head_dim, dtype=torch.bfloat16, ite
     ms = _time(run, iters, warmup)
     ops.check_status()
     flops = 4.0 * images * heads * L * L * head_dim
-    return {"kernel": "attn_global (+ transpose_v + rel products)", "images": images, "H": H, "W": W, "heads": heads,
+    return {"kernel": "attn_global (+ rel products)", "images": images, "H": H, "W": W, "heads": heads,
             "head_dim": head_dim, "ms": round(ms, 5), "tflops": round(flops / ms / 1e9, 1)}
 
 

@@ -527,15 +527,11 @@ def attn_global(qkv: torch.Tensor, units: int, H: int, W: int, num_heads: int, r
     rel_all = rel_pos_products(qkv, num_heads, table)
     if not rel_all.is_contiguous():
         rel_all = rel_all.contiguous()
-    keys = L if W == 64 else (H * 16 + 63) // 64 * 64
-    vt = torch.empty((units * num_heads * d, keys), dtype=qkv.dtype, device=qkv.device)
     out = torch.empty((tokens, C), dtype=qkv.dtype, device=qkv.device)
     esz = qkv.element_size()
     with torch.cuda.device(qkv.device):
-        with _Timed("attn_transpose_v", 2 * tokens * C * esz):
-            _lib.check(lib.samq_attn_transpose_v(_ptr(qkv), _DTYPE_CODE[qkv.dtype], units, H, W, num_heads, d, _ptr(vt), _stream()))
         with _Timed("attn_global", 4 * tokens * C * esz):
-            _lib.check(lib.samq_attn_global(_ptr(qkv), _ptr(vt), _ptr(rel_all), _DTYPE_CODE[qkv.dtype], units, rel_all.shape[-1],
+            _lib.check(lib.samq_attn_global(_ptr(qkv), None, _ptr(rel_all), _DTYPE_CODE[qkv.dtype], units, rel_all.shape[-1],
                                             H, W, num_heads, d, float(scale), _ptr(out), _ptr(status_word(qkv.device)), _stream()))
     return out
 
