@@ -97,13 +97,15 @@ class EncoderRunner:
         return self.static_out
 
     @torch.no_grad()
-    def encode(self, images: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    def encode(self, images: torch.Tensor, out: torch.Tensor, wait: bool = True) -> torch.Tensor:
         """Encode ``images`` [n * batch, 3, S, S] into ``out`` [n * batch, C, h, w], ``batch`` images per
         forward.  With host tensors (pinned memory) the copy of chunk i + 1 to the device runs on a
         second stream while chunk i is being encoded, and the embeddings of chunk i leave for the host on a
         third while chunk i + 1 is encoded; the first copy of a call may already run under the last
         forward of the call before it.  Device tensors are encoded in place.  Returns ``out``; the work is
-        ordered on the current stream (synchronise it before reading a host ``out``)."""
+        ordered on the current stream (synchronise it before reading a host ``out``).  ``wait=False`` leaves
+        the last copies back to the host unordered with the current stream, so that the next call's forward
+        does not wait for them: call ``runner.synchronize()`` before reading ``out``."""
         n, b = images.shape[0], self.batch
         if n % b or out.shape[0] != n:
             raise ValueError(f"images and out must hold a multiple of {b} images")
@@ -161,10 +163,17 @@ class EncoderRunner:
                     out[i:i + b].copy_(self._out_stage[slot], non_blocking=True)
                     self._out_free[slot].record(back)
                 self._out_used[slot] = True
-        cur.wait_stream(back)
+        if wait:
+            cur.wait_stream(back)
         if self.check_status:
             self.check()
         return out
+
+    def synchronize(self) -> None:
+        """Block until everything ``encode`` has queued, the copies back to the host included, is done."""
+        torch.cuda.current_stream(self.device).synchronize()
+        if self._copy_stream is not None:
+            self._back_stream.synchronize()
 
     def check(self) -> None:
         """Synchronise and raise if a kernel of this device reported a timed-out wait."""

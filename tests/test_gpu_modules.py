@@ -557,6 +557,12 @@ def test_encoder_runner_encode_overlaps_copies_and_matches_direct_calls(cuda_dev
     runner.encode(host_in, dev_out.zero_())
     torch.cuda.synchronize()
     assert torch.equal(dev_out, want)
+    # calls in a row without ordering the copies back on the current stream, one synchronize at the end
+    for _ in range(3):
+        host_out.zero_()
+        runner.encode(host_in, host_out, wait=False)
+    runner.synchronize()
+    assert torch.equal(host_out, want.cpu())
     with pytest.raises(ValueError):
         runner.encode(host_in[:3], host_out[:3])
 
