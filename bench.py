@@ -367,6 +367,12 @@ def run_ours(args):
         step_e2e()
     e2e_ms = timed(step_e2e, args.steps)
     e2e_value = GLOBAL_BATCH * args.steps / (e2e_ms / 1000.0)
+    if os.environ.get("SAMQ_BENCH_REPEAT"):                      # diagnostic: the device-resident loop once more, after the end-to-end one
+        again_ms = timed(step_resident, args.steps)
+        e2e_again_ms = timed(step_e2e, args.steps)
+        if rank == 0:
+            print(f"[bench] resident {total_ms:.1f} ms, end to end {e2e_ms:.1f} ms, resident again {again_ms:.1f} ms, "
+                  f"end to end again {e2e_again_ms:.1f} ms for {args.steps} steps", file=sys.stderr)
 
     # per-kernel timing of the dominant kernel (the int8 GEMM): one more step, run eagerly (not
     # through the graph) with CUDA events around every launch on the launching stream.
